@@ -1,0 +1,415 @@
+#!/usr/bin/env python
+"""Benchmark of the paged-KV batched decode hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (N=1 and every rank at N>1): a Llama-3-8B-shaped model with random weights — 32 layers, d_model 4096,
+32 query x 128 / 8 KV heads, SwiGLU FFN 14336, vocabulary 128256, RoPE theta 500000; projections and head
+~N(0, 0.02) quantized to Q4_0 (token embedding and norms f32); f16 paged KV with 16-token pages; batch 32 prompts of
+512 random token ids (fed one token per step through the decode path), then greedy decode. One "step" is one
+decode step of the whole batch (32 tokens). All inputs are synthetic (seeded); there is no dataset.
+
+Printed JSON line (rank 0):
+  value     decode tokens/s with ids, tables and weights resident in HBM: K steps replayed as one CUDA graph per step
+            (etc_decoder_generate_greedy), timed with CUDA events, max over ranks
+  e2e       the same metric through the reference-facing call (Executable.executeSampled): every step copies the
+            step's token ids / lane descriptors / page tables host->device and reads the sampled tokens back
+  roofline  the dominant kernel (tiled Q4_0 linear, fused gate/up shape [28672 x 4096], 32 vectors) timed alone with
+            CUDA events on the launching stream over weight sets larger than L2
+  cpu_baseline  the CPU oracle (restatement of the reference CPU backend) on a bounded sample, host cores stated
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+MODEL = dict(layers=32, d_model=4096, q_heads=32, kv_heads=8, head_dim=128, ffn=14336, vocab=128256, rms_eps=1e-5,
+             rope_theta=500000.0)
+BATCH, PROMPT, BLOCK = 32, 512, 16
+Q4_0 = 2
+METRIC = "decode tokens/s, Llama-3-8B-shape Q4_0 batch 32; kernel HBM GB/s vs peak"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+def algorithmic_bytes_per_step(model, batch, mean_ctx):
+    """Weights read once per step + KV read once per KV head per step (bytes)."""
+    d, qw, kvw, ffn, V, L = (model["d_model"], model["q_heads"] * model["head_dim"], model["kv_heads"] * model["head_dim"],
+                             model["ffn"], model["vocab"], model["layers"])
+    per_layer = (qw + 2 * kvw) * d + d * qw + 2 * ffn * d + d * ffn
+    weights = (L * per_layer + V * d) * 18 / 32
+    kv = batch * mean_ctx * L * 2 * kvw * 2
+    return weights + kv
+
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index):
+        self.device_index = device_index
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.device_index}", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"], stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.file.flush()
+        self.file.seek(0)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.file.read().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.file.name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------ CPU reference arm
+def cpu_sample(model, batch, ctx, threads, fraction, seed=3):
+    """Times the CPU oracle on a bounded sample of one decode step and scales it to the whole step.
+
+    Every projection of one layer and the head are timed on a row slice (`fraction` of the rows, all columns,
+    all `batch` vectors); paged attention is timed on `fraction` of the lanes at context `ctx`; norms, RoPE and
+    SwiGLU are timed at full size. Slice times are divided by their fraction and the layer time is multiplied by
+    the layer count. Returns (tokens/s, seconds of CPU work done, description)."""
+    import oracle as orc
+    rng = np.random.default_rng(seed)
+    d, qw, kvw, ffn, V, L = (model["d_model"], model["q_heads"] * model["head_dim"], model["kv_heads"] * model["head_dim"],
+                             model["ffn"], model["vocab"], model["layers"])
+    work = 0.0
+
+    def linear_seconds(rows, cols):
+        nonlocal work
+        r = min(rows, max(32, int(rows * fraction) // 32 * 32))
+        w = rng.standard_normal((r, cols), dtype=np.float32) * np.float32(0.02)
+        packed = orc.quantize(orc.Q4_0, w)
+        x = rng.standard_normal((batch, cols), dtype=np.float32)
+        t0 = time.perf_counter()
+        orc.qlinear(orc.Q4_0, x, packed, r, cols, threads=threads)
+        dt = time.perf_counter() - t0
+        work += dt
+        return dt * rows / r
+
+    layer = sum(linear_seconds(r, c) for r, c in ((qw, d), (kvw, d), (kvw, d), (d, qw), (ffn, d), (ffn, d), (d, ffn)))
+    head = linear_seconds(V, d)
+    lanes = max(1, int(round(batch * fraction)))
+    max_tokens = lanes * ((ctx + 1 + BLOCK - 1) // BLOCK) * BLOCK
+    pool = orc.Pool(1, model["kv_heads"], model["head_dim"], max_tokens, BLOCK, orc.F16)
+    seqs = [pool.make_sequence() for _ in range(lanes)]
+    for s_ in seqs:  # context written straight into the pages: the prefill is not part of the decode sample
+        for _ in range((ctx + BLOCK - 1) // BLOCK):
+            s_.push_block(pool.alloc_block())
+        rows = np.concatenate([np.arange(BLOCK) + int(b) * BLOCK for b in s_.blocks])[:ctx]
+        pool.write_rows(0, 0, rows, rng.standard_normal((ctx, kvw), dtype=np.float32))
+        pool.write_rows(0, 1, rows, rng.standard_normal((ctx, kvw), dtype=np.float32))
+        s_.set_cursor(ctx)
+        s_.set_advance(1)
+    q = rng.standard_normal((lanes, model["q_heads"], 1, model["head_dim"]), dtype=np.float32)
+    k = rng.standard_normal((lanes, model["kv_heads"], 1, model["head_dim"]), dtype=np.float32)
+    t0 = time.perf_counter()
+    orc.kv_attention(pool, 0, seqs, lanes, q, k, k, 1.0 / np.sqrt(model["head_dim"]), mode=1, threads=threads)
+    dt = time.perf_counter() - t0
+    work += dt
+    layer += dt * batch / lanes
+    h = rng.standard_normal((batch, d), dtype=np.float32)
+    g = rng.standard_normal((batch, ffn), dtype=np.float32)
+    t0 = time.perf_counter()
+    orc.rms_norm(h, np.ones(d, np.float32), model["rms_eps"])
+    orc.rms_norm(h, np.ones(d, np.float32), model["rms_eps"])
+    orc.rotary(rng.standard_normal((batch, model["q_heads"] + model["kv_heads"], 1, model["head_dim"]), dtype=np.float32),
+               np.full(batch, ctx), model["rope_theta"])
+    orc.silu_mul(g, g)
+    dt = time.perf_counter() - t0
+    work += dt
+    layer += dt
+    step_seconds = layer * L + head
+    sample = (f"one batch-{batch} decode step at context {ctx} of the CPU oracle (restatement of the reference CPU backend; fair "
+              f"variant: every block decoded once per row, attention scores cached) on {threads} threads: {fraction:.4f} of the "
+              f"rows of each projection and of the lanes of paged attention in 1 of {L} layers, plus the head slice, scaled to "
+              f"the full step (extrapolated)")
+    return batch / step_seconds, work, sample
+
+
+def calibrated_fraction(model, batch, threads, budget_seconds):
+    """Fraction of one layer's rows whose CPU time fits `budget_seconds` (probed on a 1/64 slice)."""
+    _, work, _ = cpu_sample(model, batch, PROMPT, threads, 1.0 / 64)
+    return float(min(1.0, max(1.0 / 256, (1.0 / 64) * budget_seconds / max(work, 1e-6))))
+
+
+def run_reference_arm(args, rank):
+    if rank != 0:
+        return
+    import oracle as orc
+    threads = orc.max_threads()
+    total = args.warmup + args.steps
+    fraction = calibrated_fraction(MODEL, BATCH, threads, 150.0 / max(total, 1))
+    values, sample = [], ""
+    for i in range(total):
+        v, _, sample = cpu_sample(MODEL, BATCH, PROMPT + i, threads, fraction, seed=3 + i)
+        if i >= args.warmup:
+            values.append(v)
+    value = float(np.mean(values))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1000.0 * BATCH / value, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "llama3-8b-shape Q4_0 paged decode, batch 32, prompt 512 (bounded CPU sample per step)",
+                   "global_batch": BATCH, "parallelism": "cpu"},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------ GPU arm
+def build_decoder(rt, et, torch, model, batch, max_tokens, seed):
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(seed)
+    dec = et.Executable(rt, layers=model["layers"], d_model=model["d_model"], q_heads=model["q_heads"], kv_heads=model["kv_heads"],
+                        head_dim=model["head_dim"], ffn=model["ffn"], vocab=model["vocab"], rms_eps=model["rms_eps"],
+                        rope_theta=model["rope_theta"], batch=batch, max_tokens=max_tokens, block_size=BLOCK, kv_dtype=et.KV_F16,
+                        exact=False, max_advance=1)
+    d, qw, kvw, ffn, V = (model["d_model"], model["q_heads"] * model["head_dim"], model["kv_heads"] * model["head_dim"], model["ffn"],
+                          model["vocab"])
+
+    def normal(rows, cols):
+        w = torch.randn((rows, cols), generator=gen, device="cuda", dtype=torch.float32)
+        w.mul_(0.02)
+        return w
+
+    def quantized(rows, cols):
+        w = normal(rows, cols)
+        packed = torch.empty((rows, cols // 32 * 18), dtype=torch.uint8, device="cuda")
+        torch.cuda.synchronize()
+        rt.quantize_into(Q4_0, w, rows, cols, packed)
+        rt.synchronize()
+        return packed
+
+    def bind(slot, layer, tensor, codec=0, rows=None, cols=None):
+        torch.cuda.synchronize()
+        dec.set_weight(slot, layer, tensor, codec=codec, rows=rows, columns=cols)
+
+    bind(et.W_TOK_EMBD, 0, normal(V, d))
+    ones = torch.ones(d, device="cuda", dtype=torch.float32)
+    for l in range(model["layers"]):
+        bind(et.W_ATTN_NORM, l, ones)
+        bind(et.W_FFN_NORM, l, ones)
+        for slot, (r, c) in ((et.W_Q, (qw, d)), (et.W_K, (kvw, d)), (et.W_V, (kvw, d)), (et.W_O, (d, qw)), (et.W_GATE, (ffn, d)),
+                             (et.W_UP, (ffn, d)), (et.W_DOWN, (d, ffn))):
+            bind(slot, l, quantized(r, c), Q4_0, r, c)
+    bind(et.W_OUT_NORM, 0, ones)
+    bind(et.W_HEAD, 0, quantized(V, d), Q4_0, V, d)
+    dec.finalize()
+    torch.cuda.empty_cache()
+    return dec
+
+
+def time_dominant_kernel(rt, et, torch, model, vectors, iters=40):
+    """The fused gate/up linear [2*ffn x d_model] at `vectors` input rows, alone, over more weight copies than L2 holds."""
+    d, ffn = model["d_model"], model["ffn"]
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(99)
+    copies = []
+    for _ in range(4):  # 4 x 66 MB > 126 MB L2
+        parts = []
+        for _ in range(2):
+            w = torch.randn((ffn, d), generator=gen, device="cuda", dtype=torch.float32) * 0.02
+            packed = torch.empty((ffn, d // 32 * 18), dtype=torch.uint8, device="cuda")
+            torch.cuda.synchronize()
+            rt.quantize_into(Q4_0, w, ffn, d, packed)
+            rt.synchronize()
+            parts.append(packed)
+        copies.append(et.QWeight(rt, Q4_0, parts, [ffn, ffn], d, interleave8=True))
+        del parts
+    x = torch.randn((vectors, d), device="cuda", dtype=torch.float32)
+    out = torch.empty((vectors, ffn), device="cuda", dtype=torch.float32)
+    scratch_bytes = copies[0].scratch_bytes(vectors)
+    scratch = torch.empty(max(scratch_bytes, 4), dtype=torch.uint8, device="cuda")
+    torch.cuda.synchronize()
+    stream = torch.cuda.ExternalStream(rt.stream)
+    for i in range(8):
+        copies[i % 4].linear_into(x, vectors, out, epilogue=et.EPILOGUE_SWIGLU, scratch=scratch, scratch_bytes=scratch_bytes)
+    rt.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        start.record()
+        for i in range(iters):
+            copies[i % 4].linear_into(x, vectors, out, epilogue=et.EPILOGUE_SWIGLU, scratch=scratch, scratch_bytes=scratch_bytes)
+        stop.record()
+    rt.synchronize()
+    ms = start.elapsed_time(stop) / iters
+    algorithmic = 2 * ffn * (d // 32) * 18 + 4 * vectors * d + 4 * vectors * ffn
+    for c in copies:
+        c.close()
+    return ms, algorithmic
+
+
+def run_gpu_arm(args, rank, world):
+    import torch
+    import torch.distributed as dist
+    import effect_torch_b200 as et
+
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    rt = et.Runtime(local)
+    model = dict(MODEL)
+    if args.layers:
+        model["layers"] = args.layers
+    K, W = args.steps, args.warmup
+    # every sequence: prompt + warm-up + timed steps, twice (end-to-end leg, then device-resident leg)
+    per_seq = ((PROMPT + W + K + BLOCK) // BLOCK + 1) * BLOCK
+    max_tokens = 2 * BATCH * per_seq
+    dec = build_decoder(rt, et, torch, model, BATCH, max_tokens, seed=3 + rank)
+    pool = et.NativeKvPool(rt, model["layers"], model["kv_heads"], model["head_dim"], max_tokens, BLOCK, et.KV_F16)
+    rng = np.random.default_rng(3 + rank)
+    prompts = rng.integers(0, model["vocab"], size=(BATCH, PROMPT)).astype(np.uint32)
+
+    def prefill():
+        seqs = [pool.makeSequence() for _ in range(BATCH)]
+        tok = None
+        for t in range(PROMPT):  # the prompt goes through the decode path one token per step
+            tok = dec.executeSampled(pool, seqs, prompts[:, t:t + 1])
+        return seqs, tok
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    # ---- leg 1: end to end through executeSampled (host token ids in, sampled ids out, every step)
+    seqs, tok = prefill()
+    for _ in range(W):
+        tok = dec.executeSampled(pool, seqs, tok[:, None])
+    barrier()
+    sampler.start()
+    t0 = time.perf_counter()
+    for _ in range(K):
+        tok = dec.executeSampled(pool, seqs, tok[:, None])
+    barrier()
+    e2e_seconds = time.perf_counter() - t0
+    launches_per_step = dec.diagnostics()["launches_per_step"]
+    for s in seqs:
+        s.release()
+    # ---- leg 2: device resident (ids, tables and cursors stay in HBM; one CUDA graph replay per step)
+    seqs, tok = prefill()
+    if W:
+        out, _ = dec.generate_greedy(pool, seqs, tok, W)
+        tok = out[-1]
+    barrier()
+    out, device_ms = dec.generate_greedy(pool, seqs, tok, K)
+    barrier()
+    clocks = sampler.stop()
+    times = torch.tensor([device_ms / 1000.0, e2e_seconds], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    device_seconds, e2e_seconds = [float(v) for v in times.cpu()]
+    graph_launches = dec.diagnostics()["launches_per_step"]
+    mean_ctx = PROMPT + W + (K + 1) / 2.0
+    step_bytes = algorithmic_bytes_per_step(model, BATCH, mean_ctx)
+    peaks, peak_kind = measured_peaks()
+
+    line = None
+    if rank == 0:
+        kernel_ms, kernel_bytes = time_dominant_kernel(rt, et, torch, model, BATCH)
+        achieved = kernel_bytes / (kernel_ms * 1e-3) / 1e9
+        value = world * BATCH * K / device_seconds
+        e2e_value = world * BATCH * K / e2e_seconds
+        max_blocks = max_tokens // BLOCK + 3
+        h2d = BATCH * 4 + BATCH * 16 + BATCH * 8 + BATCH * max_blocks * 4
+        d2h = BATCH * 4 + 32
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            import oracle as orc
+            threads = orc.max_threads()
+            fraction = calibrated_fraction(MODEL, BATCH, threads, 15.0)
+            v, seconds, sample = cpu_sample(MODEL, BATCH, PROMPT, threads, fraction)
+            cpu = {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample, "cpu_seconds": seconds}
+        line = {
+            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": 1000.0 * device_seconds / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f16 MMA operands, f32 accumulate (Q4_0 weights, f16 KV)", "data": "synthetic",
+            "config": {"workload": f"llama3-8b-shape Q4_0 paged decode: {model['layers']} layers, batch {BATCH}, prompt {PROMPT}, "
+                                   f"{K} greedy steps, f16 KV 16-token pages",
+                       "global_batch": BATCH * world, "parallelism": "single GPU" if world == 1 else f"{world} independent replicas",
+                       "l2": "per-step working set (weights 4.2 GB + KV) exceeds the 126 MB L2; no flush needed"},
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": 1000.0 * e2e_seconds / K, "launches_per_step": launches_per_step},
+            "gpu_launches": graph_launches * K,
+            "step_roofline": {"algorithmic_bytes_per_step": step_bytes, "achieved_gbs": step_bytes * K / device_seconds / 1e9,
+                              "frac_of_" + peak_kind: step_bytes * K / device_seconds / 1e9 / peaks["hbm_gbs"]},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                         "traffic": None, "peak_kind": peak_kind,
+                         "kernel": "qlinear_tiled_kernel<Q4_0> fused gate/up [28672x4096], 32 vectors, SwiGLU epilogue",
+                         "ms_per_launch": kernel_ms, "algorithmic_bytes_per_launch": kernel_bytes},
+            "cpu_baseline": cpu,
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return line
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--layers", type=int, default=0, help="debug: fewer layers than the 8B shape (the result is then not a bench value)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+    run_gpu_arm(args, rank, world)
+
+
+if __name__ == "__main__":
+    main()

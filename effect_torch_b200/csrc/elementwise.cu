@@ -1,0 +1,303 @@
+// Dense and elementwise kernels of the decode graph for sm_100a: exact-order dense linear,
+// RMSNorm, RoPE, SwiGLU, residual add, greedy argmax, dense embedding gather and the layout
+// shuffles around attention. All are HBM/latency-bound single-pass kernels.
+//
+// Replaces, for the CUDA backend: crates/runtime-cpu/src/matmul.rs:192-231 (naive_into),
+// crates/runtime-cpu/src/composed.rs:1457-1487 (rms_norm_forward_into_impl) and :2683-2729
+// (rotary_forward_into_impl), the FusedElementwise regions evaluating
+// packages/core/src/Tensor.ts:1240-1245,1537-1540 (sigmoid/silu), and the greedy branch of
+// crates/runtime/src/sampling.rs:88-105.
+#include <cuda_fp16.h>
+
+#include <algorithm>
+
+#include "kernels.h"
+
+namespace etc {
+
+// --------------------------------------------------------------------------------------------
+// Dense linear, bit-exact with the reference: every output element is one sequential fmaf chain
+// over k (out = fma(x[m,k], W[n,k], out)). A CTA computes 32 outputs x 8 input rows; W is staged
+// 32 columns at a time through shared memory so global reads stay coalesced.
+// --------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) linear_f32_kernel(const float* __restrict__ x, int64_t m, int64_t k,
+                                                         const float* __restrict__ w, int64_t n,
+                                                         const float* __restrict__ bias, float* __restrict__ out) {
+  __shared__ float ws[32][33];
+  __shared__ float xs[8][32];
+  const int tx = threadIdx.x, ty = threadIdx.y;  // tx: output column within tile, ty: input row within tile
+  const int64_t n0 = (int64_t)blockIdx.x * 32, m0 = (int64_t)blockIdx.y * 8;
+  float acc = 0.0f;
+  for (int64_t k0 = 0; k0 < k; k0 += 32) {
+    // W tile: rows n0..n0+31, columns k0..k0+31 (coalesced along k)
+    for (int r = ty; r < 32; r += 8) {
+      const int64_t nn = n0 + r, kk = k0 + tx;
+      ws[r][tx] = (nn < n && kk < k) ? w[nn * k + kk] : 0.0f;
+    }
+    {
+      const int64_t mm = m0 + ty, kk = k0 + tx;
+      xs[ty][tx] = (mm < m && kk < k) ? x[mm * k + kk] : 0.0f;
+    }
+    __syncthreads();
+    const int len = (int)min((int64_t)32, k - k0);
+    for (int kk = 0; kk < len; ++kk) acc = fmaf(xs[ty][kk], ws[tx][kk], acc);
+    __syncthreads();
+  }
+  const int64_t mm = m0 + ty, nn = n0 + tx;
+  if (mm < m && nn < n) out[mm * n + nn] = bias ? acc + bias[nn] : acc;
+}
+
+cudaError_t launch_linear_f32(const float* x, int64_t m, int64_t k, const float* w, int64_t n, const float* bias,
+                              float* out, cudaStream_t stream) {
+  if (m == 0 || n == 0) return cudaSuccess;
+  dim3 block(32, 8), grid((unsigned)((n + 31) / 32), (unsigned)((m + 7) / 8));
+  linear_f32_kernel<<<grid, block, 0, stream>>>(x, m, k, w, n, bias, out);
+  return cudaGetLastError();
+}
+
+// --------------------------------------------------------------------------------------------
+// RMSNorm: one CTA per row, sum of squares and the scaling in f64 like the reference
+// (scale = 1/sqrt(ms/n + eps); out = f32(x * scale * w)). The f64 block reduction is a tree, so
+// the sum can differ from the reference's sequential sum in the last f64 bits only.
+// --------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ weight,
+                                                      double eps, int64_t n, float* __restrict__ out) {
+  __shared__ double partial[8];
+  __shared__ double scale_s;
+  const float* src = x + (int64_t)blockIdx.x * n;
+  double sum = 0.0;
+  for (int64_t i = threadIdx.x; i < n; i += blockDim.x) {
+    const double v = (double)src[i];
+    sum += v * v;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+  if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = sum;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double total = 0.0;
+    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) total += partial[i];
+    scale_s = 1.0 / sqrt(total / (double)n + eps);
+  }
+  __syncthreads();
+  const double scale = scale_s;
+  float* dst = out + (int64_t)blockIdx.x * n;
+  for (int64_t i = threadIdx.x; i < n; i += blockDim.x) {
+    const double w = weight ? (double)weight[i] : 1.0;
+    dst[i] = (float)(__dmul_rn(__dmul_rn((double)src[i], scale), w));
+  }
+}
+
+cudaError_t launch_rmsnorm(const float* x, const float* weight, double eps, int64_t rows, int64_t n, float* out,
+                           cudaStream_t stream) {
+  if (rows == 0) return cudaSuccess;
+  rmsnorm_kernel<<<(unsigned)rows, 256, 0, stream>>>(x, weight, eps, n, out);
+  return cudaGetLastError();
+}
+
+// --------------------------------------------------------------------------------------------
+// RoPE on [batch, heads, steps, head_dim] with per-lane cursor offsets. inv_freq[j] =
+// theta^(-2j/D) is precomputed on the host in f64 with the same pow() the reference calls;
+// angle, sin/cos and the rotation are f64, results are rounded to f32 once.
+// --------------------------------------------------------------------------------------------
+__global__ void rope_kernel(const float* __restrict__ x, const int64_t* __restrict__ offsets, int64_t n_offsets,
+                            const double* __restrict__ inv_freq, int layout, int64_t batch, int64_t heads,
+                            int64_t steps, int64_t head_dim, float* __restrict__ out) {
+  const int64_t half = head_dim / 2;
+  const int64_t total = batch * heads * steps * half;
+  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t j = idx % half;
+    const int64_t row_step = idx / half;  // (batch*heads + head)*steps + step
+    const int64_t step = row_step % steps;
+    const int64_t b = row_step / (steps * heads);
+    const int64_t offset = n_offsets == 1 ? offsets[0] : offsets[b];
+    const double angle = (double)(offset + step) * inv_freq[j];
+    double s, c;
+    sincos(angle, &s, &c);
+    const int64_t base = row_step * head_dim;
+    const int64_t i0 = layout == 0 ? base + j : base + 2 * j;
+    const int64_t i1 = layout == 0 ? base + half + j : base + 2 * j + 1;
+    const double first = (double)x[i0], second = (double)x[i1];
+    out[i0] = (float)__dsub_rn(__dmul_rn(first, c), __dmul_rn(second, s));
+    out[i1] = (float)__dadd_rn(__dmul_rn(second, c), __dmul_rn(first, s));
+  }
+}
+
+cudaError_t launch_rope(const float* x, const int64_t* offsets, int64_t n_offsets, const double* inv_freq, int layout,
+                        int64_t batch, int64_t heads, int64_t steps, int64_t head_dim, float* out, cudaStream_t stream) {
+  const int64_t total = batch * heads * steps * (head_dim / 2);
+  if (total == 0) return cudaSuccess;
+  const unsigned grid = (unsigned)std::min<int64_t>((total + 255) / 256, 148 * 8);
+  rope_kernel<<<grid, 256, 0, stream>>>(x, offsets, n_offsets, inv_freq, layout, batch, heads, steps, head_dim, out);
+  return cudaGetLastError();
+}
+
+// --------------------------------------------------------------------------------------------
+// silu(gate) * up with the reference's definition sigmoid(x) = tanh(x/2)/2 + 1/2, evaluated in
+// f32 like the reference's expression interpreter. exact != 0 takes tanh in f64 and rounds, which
+// tracks a correctly rounded tanhf more closely than the device tanhf.
+// --------------------------------------------------------------------------------------------
+__global__ void swiglu_kernel(const float* __restrict__ gate, const float* __restrict__ up, int64_t n,
+                              float* __restrict__ out, int exact) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const float g = gate[i];
+    const float half_g = __fdiv_rn(g, 2.0f);
+    const float th = exact ? (float)tanh((double)half_g) : tanhf(half_g);
+    const float sig = __fadd_rn(__fdiv_rn(th, 2.0f), 0.5f);
+    out[i] = __fmul_rn(__fmul_rn(g, sig), up[i]);
+  }
+}
+cudaError_t launch_swiglu(const float* gate, const float* up, int64_t n, float* out, int exact, cudaStream_t stream) {
+  if (n == 0) return cudaSuccess;
+  const unsigned grid = (unsigned)std::min<int64_t>((n + 255) / 256, 148 * 8);
+  swiglu_kernel<<<grid, 256, 0, stream>>>(gate, up, n, out, exact);
+  return cudaGetLastError();
+}
+
+__global__ void add_kernel(const float* __restrict__ a, const float* __restrict__ b, int64_t n, float* __restrict__ out) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    out[i] = __fadd_rn(a[i], b[i]);
+}
+cudaError_t launch_add(const float* a, const float* b, int64_t n, float* out, cudaStream_t stream) {
+  if (n == 0) return cudaSuccess;
+  const unsigned grid = (unsigned)std::min<int64_t>((n + 255) / 256, 148 * 8);
+  add_kernel<<<grid, 256, 0, stream>>>(a, b, n, out);
+  return cudaGetLastError();
+}
+
+// --------------------------------------------------------------------------------------------
+// Greedy argmax per row: the first index of the maximum (strict >, so the lowest index wins
+// ties); a non-finite logit raises the status word with its index.
+// --------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, int64_t vocab,
+                                                      uint32_t* __restrict__ tokens, DeviceStatus* status) {
+  __shared__ float best_v[32];
+  __shared__ long long best_i[32];
+  __shared__ long long bad_s[32];
+  const float* row = logits + (int64_t)blockIdx.x * vocab;
+  float best = -INFINITY;
+  long long arg = 0x7fffffffffffffffll;
+  long long bad = 0x7fffffffffffffffll;
+  for (int64_t i = threadIdx.x; i < vocab; i += blockDim.x) {
+    const float v = row[i];
+    if (!isfinite(v)) bad = min(bad, (long long)i);
+    if (v > best) { best = v; arg = i; }
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, off);
+    const long long oi = __shfl_xor_sync(0xffffffffu, arg, off);
+    const long long ob = __shfl_xor_sync(0xffffffffu, bad, off);
+    if (ov > best || (ov == best && oi < arg)) { best = ov; arg = oi; }
+    bad = min(bad, ob);
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) { best_v[warp] = best; best_i[warp] = arg; bad_s[warp] = bad; }
+  __syncthreads();
+  if (warp == 0) {
+    const int nwarps = blockDim.x >> 5;
+    best = lane < nwarps ? best_v[lane] : -INFINITY;
+    arg = lane < nwarps ? best_i[lane] : 0x7fffffffffffffffll;
+    bad = lane < nwarps ? bad_s[lane] : 0x7fffffffffffffffll;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, off);
+      const long long oi = __shfl_xor_sync(0xffffffffu, arg, off);
+      const long long ob = __shfl_xor_sync(0xffffffffu, bad, off);
+      if (ov > best || (ov == best && oi < arg)) { best = ov; arg = oi; }
+      bad = min(bad, ob);
+    }
+    if (lane == 0) {
+      // a row of only -inf keeps index 0 like the reference's loop would before it errors
+      tokens[blockIdx.x] = arg == 0x7fffffffffffffffll ? 0u : (uint32_t)arg;
+      if (bad != 0x7fffffffffffffffll && atomicCAS(&status->code, kStatusNone, kStatusNonFiniteLogit) == kStatusNone) {
+        status->value = bad;
+        status->bound = vocab;
+      }
+    }
+  }
+}
+cudaError_t launch_argmax(const float* logits, int64_t rows, int64_t vocab, uint32_t* tokens, DeviceStatus* status,
+                          cudaStream_t stream) {
+  if (rows == 0) return cudaSuccess;
+  argmax_kernel<<<(unsigned)rows, 1024, 0, stream>>>(logits, vocab, tokens, status);
+  return cudaGetLastError();
+}
+
+// Dense f32 embedding gather with the same bounds rule as the quantized embedding.
+template <typename Index>
+__global__ void embedding_f32_kernel(const Index* __restrict__ indexes, int64_t count, const float* __restrict__ table,
+                                     int64_t rows, int64_t columns, float* __restrict__ out, DeviceStatus* status) {
+  const int64_t i = blockIdx.y;
+  const long long row = (long long)indexes[i];
+  if (row < 0 || row >= rows) {
+    if (threadIdx.x == 0 && blockIdx.x == 0 && atomicCAS(&status->code, kStatusNone, kStatusIndexOutOfRange) == kStatusNone) {
+      status->value = row;
+      status->bound = rows;
+    }
+    return;
+  }
+  for (int64_t c = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; c < columns; c += (int64_t)gridDim.x * blockDim.x)
+    out[i * columns + c] = table[row * columns + c];
+}
+cudaError_t launch_embedding_f32(const void* indexes, int index_is_i64, int64_t count, const float* table, int64_t rows,
+                                 int64_t columns, float* out, DeviceStatus* status, cudaStream_t stream) {
+  if (count == 0) return cudaSuccess;
+  dim3 grid((unsigned)std::min<int64_t>((columns + 255) / 256, 32), (unsigned)count);
+  if (index_is_i64)
+    embedding_f32_kernel<long long><<<grid, 256, 0, stream>>>((const long long*)indexes, count, table, rows, columns, out, status);
+  else
+    embedding_f32_kernel<unsigned int><<<grid, 256, 0, stream>>>((const unsigned int*)indexes, count, table, rows, columns, out, status);
+  return cudaGetLastError();
+}
+
+// [B,T,H*D] (row stride src_row_stride floats) -> [B,H,T,D]
+__global__ void heads_first_kernel(const float* __restrict__ src, float* __restrict__ dst, int64_t B, int64_t T, int64_t H,
+                                   int64_t D, int64_t src_row_stride) {
+  const int64_t total = B * H * T * D;
+  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t d = idx % D, t = (idx / D) % T, h = (idx / (D * T)) % H, b = idx / (D * T * H);
+    dst[idx] = src[(b * T + t) * src_row_stride + h * D + d];
+  }
+}
+cudaError_t launch_heads_first(const float* src, float* dst, int64_t B, int64_t T, int64_t H, int64_t D,
+                               int64_t src_row_stride, cudaStream_t stream) {
+  const int64_t total = B * H * T * D;
+  if (total == 0) return cudaSuccess;
+  heads_first_kernel<<<(unsigned)std::min<int64_t>((total + 255) / 256, 148 * 8), 256, 0, stream>>>(src, dst, B, T, H, D, src_row_stride);
+  return cudaGetLastError();
+}
+// [B,H,T,D] -> [B,T,H*D]
+__global__ void heads_last_kernel(const float* __restrict__ src, float* __restrict__ dst, int64_t B, int64_t T, int64_t H,
+                                  int64_t D) {
+  const int64_t total = B * H * T * D;
+  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t d = idx % D, h = (idx / D) % H, t = (idx / (D * H)) % T, b = idx / (D * H * T);
+    dst[idx] = src[((b * H + h) * T + t) * D + d];
+  }
+}
+cudaError_t launch_heads_last(const float* src, float* dst, int64_t B, int64_t T, int64_t H, int64_t D, cudaStream_t stream) {
+  const int64_t total = B * H * T * D;
+  if (total == 0) return cudaSuccess;
+  heads_last_kernel<<<(unsigned)std::min<int64_t>((total + 255) / 256, 148 * 8), 256, 0, stream>>>(src, dst, B, T, H, D);
+  return cudaGetLastError();
+}
+
+// LastTokenRow (crates/runtime-cpu/src/napi/mod.rs:3053-3075) for every lane at once.
+__global__ void last_token_rows_kernel(const float* __restrict__ src, int64_t lanes, int64_t steps, int64_t width,
+                                       int64_t advance, float* __restrict__ out) {
+  const int64_t total = lanes * width;
+  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t lane = idx / width, c = idx - lane * width;
+    out[idx] = src[(lane * steps + (advance - 1)) * width + c];
+  }
+}
+cudaError_t launch_last_token_rows(const float* src, int64_t lanes, int64_t steps, int64_t width, int64_t advance,
+                                   float* out, cudaStream_t stream) {
+  const int64_t total = lanes * width;
+  if (total == 0) return cudaSuccess;
+  last_token_rows_kernel<<<(unsigned)std::min<int64_t>((total + 255) / 256, 148 * 8), 256, 0, stream>>>(src, lanes, steps, width, advance, out);
+  return cudaGetLastError();
+}
+
+}  // namespace etc

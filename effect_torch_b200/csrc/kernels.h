@@ -1,0 +1,127 @@
+// Host-callable launchers of the CUDA kernels (implemented in the .cu files). All launch on the
+// given stream and return the cudaError_t of the launch. Pointers are device pointers.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+#include "common.h"
+
+namespace etc {
+
+// ---- block-quantized weights (quant_kernels.cu) ------------------------------------------
+cudaError_t launch_dequantize(int codec, const uint8_t* packed, int64_t rows, int64_t columns, float* out,
+                              cudaStream_t stream);
+cudaError_t launch_quantize(int codec, const float* x, int64_t rows, int64_t columns, uint8_t* packed,
+                            cudaStream_t stream);
+cudaError_t launch_qlinear_generic(int codec, const float* x, int64_t vectors, int64_t columns, const uint8_t* weight,
+                                   int64_t rows, const float* bias, float* out, cudaStream_t stream, int* launches);
+cudaError_t launch_qembedding(int codec, const void* indexes, int index_is_i64, int64_t count, const uint8_t* weight,
+                              int64_t rows, int64_t columns, float* out, DeviceStatus* status, cudaStream_t stream);
+
+// Tiled (tensor-core) weight layout: see quant_kernels.cu for the byte map.
+struct TiledWeight {
+  int codec = 0;
+  int64_t rows = 0;         // logical rows (outputs) as seen by the mma tiles (after concatenation/interleave)
+  int64_t rows_padded = 0;  // multiple of 16
+  int64_t columns = 0;      // multiple of 64
+  int interleave8 = 0;
+  uint8_t* quants = nullptr;
+  __half* scales = nullptr;
+  size_t quant_bytes = 0, scale_bytes = 0;
+};
+struct RepackParts {
+  const uint8_t* ptr[4];
+  int64_t rows[4];
+  int n_parts;
+};
+cudaError_t launch_repack(const TiledWeight& w, const RepackParts& parts, cudaStream_t stream);
+
+struct TiledPlan {
+  int nt = 4;        // n-tiles of 8 input vectors held per pass (1, 2 or 4)
+  int splits = 1;    // split-K factor (grid.y)
+  int grid_x = 1;
+  size_t scratch_bytes = 0;  // splits > 1: [splits][nt*8][rows_padded] f32
+};
+TiledPlan plan_tiled(const TiledWeight& w, int64_t vectors, int sm_count);
+// One pass handles up to 32 vectors; the launcher loops passes. epilogue: etc_epilogue.
+// out_half (optional) additionally receives the f16 copy of the result (same shape as out).
+cudaError_t launch_qlinear_tiled(const TiledWeight& w, const float* x, int64_t vectors, const float* bias,
+                                 const float* residual, int epilogue, float* out, float* scratch, int sm_count,
+                                 cudaStream_t stream, int* launches);
+
+// ---- dense / elementwise (elementwise.cu) --------------------------------------------------
+cudaError_t launch_linear_f32(const float* x, int64_t m, int64_t k, const float* w, int64_t n, const float* bias,
+                              float* out, cudaStream_t stream);
+cudaError_t launch_rmsnorm(const float* x, const float* weight, double eps, int64_t rows, int64_t n, float* out,
+                           cudaStream_t stream);
+cudaError_t launch_rope(const float* x, const int64_t* offsets, int64_t n_offsets, const double* inv_freq, int layout,
+                        int64_t batch, int64_t heads, int64_t steps, int64_t head_dim, float* out, cudaStream_t stream);
+cudaError_t launch_swiglu(const float* gate, const float* up, int64_t n, float* out, int exact, cudaStream_t stream);
+cudaError_t launch_add(const float* a, const float* b, int64_t n, float* out, cudaStream_t stream);
+cudaError_t launch_argmax(const float* logits, int64_t rows, int64_t vocab, uint32_t* tokens, DeviceStatus* status,
+                          cudaStream_t stream);
+cudaError_t launch_embedding_f32(const void* indexes, int index_is_i64, int64_t count, const float* table, int64_t rows,
+                                 int64_t columns, float* out, DeviceStatus* status, cudaStream_t stream);
+// [B,T,H*D] <-> [B,H,T,D] (the reshape/transpose pairs around attention)
+cudaError_t launch_heads_first(const float* src, float* dst, int64_t B, int64_t T, int64_t H, int64_t D, int64_t src_row_stride,
+                               cudaStream_t stream);
+cudaError_t launch_heads_last(const float* src, float* dst, int64_t B, int64_t T, int64_t H, int64_t D,
+                              cudaStream_t stream);
+// Copy row (advance-1) of each lane's [T, width] block into [lanes, width] (LastTokenRow).
+cudaError_t launch_last_token_rows(const float* src, int64_t lanes, int64_t steps, int64_t width, int64_t advance,
+                                   float* out, cudaStream_t stream);
+
+// ---- paged KV (attention.cu) -----------------------------------------------------------------
+// Device pool geometry. Page-major layout chosen for the B200: each (page, kv head) holds its
+// block_size token rows contiguously: elem(page, head, slot, d) = ((page*kv_heads + head)*block_size + slot)*head_dim + d.
+struct PoolView {
+  void* k = nullptr;       // this layer's K slab
+  void* v = nullptr;
+  float* k_scale = nullptr;  // u8 tier: [page][head][slot]
+  float* v_scale = nullptr;
+  int dtype = 0, kv_heads = 0, head_dim = 0, block_size = 0;
+};
+// Per-lane step description in device memory.
+struct LaneInfo {
+  int cursor;      // tokens already committed
+  int advance;     // live query rows in this step (0 = padded lane)
+  int start;       // first position still resident (pool window), 0 without
+  int table_offset;  // offset of this lane's block table in the tables array (index 0 = block of position 0)
+};
+cudaError_t launch_kv_append(const PoolView& pool, const float* k, const float* v, const LaneInfo* lanes,
+                             const int* tables, int batch, int tokens, int64_t lane_stride, int64_t head_stride,
+                             int64_t token_stride, cudaStream_t stream);
+// Reference-order attention in f64 (any tier, any block size, window). q/out [B,Hq,T,D] f32.
+// scratch: f64 [B*Hq*T][max_ctx]. op_window < 0: none.
+cudaError_t launch_attention_exact(const PoolView& pool, const float* q, const LaneInfo* lanes, const int* tables,
+                                   int batch, int q_heads, int tokens, double scale, long long op_window, float* out,
+                                   double* scratch, int max_ctx, cudaStream_t stream);
+// Tensor-core flash-decoding over the block table (f16/bf16 tiers, block_size 16, head_dim 64/128,
+// one query token per lane). q [B,Hq,D] f32; out [B,Hq,D] f32. partial scratch for splits > 1.
+struct AttnPlan {
+  int splits = 1;
+  int pages_per_split = 0;
+  size_t scratch_bytes = 0;
+};
+AttnPlan plan_attention(int batch, int q_heads, int kv_heads, int head_dim, int max_pages, int sm_count);
+// Largest scratch plan_attention can ask for with tables of at most max_pages pages.
+size_t plan_attention_max_scratch(int batch, int q_heads, int kv_heads, int head_dim, int max_pages, int sm_count);
+bool attention_mma_supported(const PoolView& pool, int q_heads, int tokens);
+cudaError_t launch_attention_mma(const PoolView& pool, const float* q, const LaneInfo* lanes, const int* tables,
+                                 int batch, int q_heads, double scale, long long op_window, float* out,
+                                 const AttnPlan& plan, float* scratch, cudaStream_t stream, int* launches);
+// Fused RoPE(q), RoPE(k) and KV append for one-token steps: qkv [B, (Hq+2*Hkv)*D] f32 (the fused
+// projection output) -> q_out [B,Hq,D] f32 rotated, K/V rows written to the pool.
+cudaError_t launch_rope_append(const PoolView& pool, const float* qkv, const LaneInfo* lanes, const int* tables,
+                               const double* inv_freq, int layout, int batch, int q_heads, float* q_out,
+                               cudaStream_t stream);
+// Tail of a device-resident greedy step: feeds the sampled tokens back as the next ids, appends
+// them to the history, and advances every live lane's cursor (and window start) by one.
+cudaError_t launch_record_step(const uint32_t* tokens, uint32_t* ids, uint32_t* history, int* step_counter, LaneInfo* lanes,
+                               int64_t* cursors, int batch, long long window, cudaStream_t stream);
+cudaError_t launch_pool_read_rows(const PoolView& pool, const uint32_t* rows, int64_t n, float* out, int which,
+                                  cudaStream_t stream);
+
+}  // namespace etc

@@ -1,0 +1,402 @@
+// Per-op entry points of the C ABI: validation in the style of the reference's `*_requirements`
+// planners, then a launch on the runtime's stream.
+#include <cuda_fp16.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <vector>
+
+#include "common.h"
+#include "kernels.h"
+#include "weights.h"
+
+using namespace etc;
+
+namespace etc {
+
+static etc_status check_codec_geometry(const char* operation, int codec, int64_t rows, int64_t columns, int64_t* row_bytes) {
+  const int64_t rb = codec_row_bytes(codec, columns);
+  if (rb < 0)
+    return fail(ETC_COMPILATION, std::string(operation) + ": logical row width " + std::to_string(columns) +
+                                     " is invalid for " + codec_name(codec));
+  if (rows < 0 || (rb > 0 && rows > INT64_MAX / rb))
+    return fail(ETC_COMPILATION, std::string(operation) + ": packed weight byte size overflow");
+  if (row_bytes) *row_bytes = rb;
+  return ETC_OK;
+}
+
+// sample_logits on the host (crates/runtime/src/sampling.rs:80-206) over a row already read back.
+etc_status sample_logits_host(const float* logits, int64_t length, double temperature, int64_t top_k, double top_p,
+                              uint64_t seed, uint64_t counter, uint32_t* out_token) {
+  if (length == 0) return fail(ETC_EXECUTION, "sample: logits must be non-empty");
+  if (length > 1048576) return fail(ETC_EXECUTION, "sample: vocabulary " + std::to_string(length) + " exceeds limit 1048576");
+  if (!std::isfinite(temperature) || temperature < 0.0)
+    return fail(ETC_EXECUTION, "sample: temperature must be finite and non-negative, got " + std::to_string(temperature));
+  if (!std::isfinite(top_p) || top_p <= 0.0 || top_p > 1.0)
+    return fail(ETC_EXECUTION, "sample: topP must be finite and in (0, 1], got " + std::to_string(top_p));
+  if (top_k > 0 && top_k > length)
+    return fail(ETC_EXECUTION, "sample: topK must be in [1, " + std::to_string(length) + "], got " + std::to_string(top_k));
+  auto non_finite = [&](int64_t t) { return fail(ETC_EXECUTION, "sample: logit " + std::to_string(t) + " is not finite"); };
+  auto random_unit = [&]() {
+    uint64_t value = seed ^ (counter * 0x9e3779b97f4a7c15ull);
+    value += 0x9e3779b97f4a7c15ull;
+    value = (value ^ (value >> 30)) * 0xbf58476d1ce4e5b9ull;
+    value = (value ^ (value >> 27)) * 0x94d049bb133111ebull;
+    value ^= value >> 31;
+    return (double)(value >> 11) * (1.0 / 9007199254740992.0);
+  };
+  if (temperature == 0.0) {
+    int64_t selected = 0;
+    double best = -INFINITY;
+    for (int64_t t = 0; t < length; ++t) {
+      const double v = (double)logits[t];
+      if (!std::isfinite(v)) return non_finite(t);
+      if (v > best) { best = v; selected = t; }
+    }
+    *out_token = (uint32_t)selected;
+    return ETC_OK;
+  }
+  const bool has_top_k = top_k > 0 && top_k < length;
+  if (!has_top_k && top_p >= 1.0) {
+    double max = -INFINITY;
+    for (int64_t t = 0; t < length; ++t) {
+      const double v = (double)logits[t];
+      if (!std::isfinite(v)) return non_finite(t);
+      max = std::fmax(max, v);
+    }
+    double total = 0.0;
+    for (int64_t t = 0; t < length; ++t) total += std::exp(((double)logits[t] - max) / temperature);
+    double draw = random_unit() * total;
+    for (int64_t t = 0; t < length; ++t) {
+      draw -= std::exp(((double)logits[t] - max) / temperature);
+      if (draw < 0.0) { *out_token = (uint32_t)t; return ETC_OK; }
+    }
+    *out_token = (uint32_t)(length - 1);
+    return ETC_OK;
+  }
+  struct Candidate { int64_t token; double value; };
+  std::vector<Candidate> candidates((size_t)length);
+  for (int64_t t = 0; t < length; ++t) {
+    const double v = (double)logits[t];
+    if (!std::isfinite(v)) return non_finite(t);
+    candidates[(size_t)t] = {t, v};
+  }
+  std::sort(candidates.begin(), candidates.end(), [](const Candidate& l, const Candidate& r) {
+    return l.value != r.value ? l.value > r.value : l.token < r.token;
+  });
+  if (has_top_k) candidates.resize((size_t)top_k);
+  const double max = candidates[0].value;
+  double total = 0.0;
+  for (auto& c : candidates) {
+    c.value = std::exp((c.value - max) / temperature);
+    total += c.value;
+  }
+  size_t retained = candidates.size();
+  if (top_p < 1.0) {
+    const double threshold = top_p * total;
+    double cumulative = 0.0;
+    for (size_t i = 0; i < candidates.size(); ++i) {
+      cumulative += candidates[i].value;
+      if (cumulative >= threshold) { retained = i + 1; total = cumulative; break; }
+    }
+  }
+  double draw = random_unit() * total;
+  for (size_t i = 0; i < retained; ++i) {
+    draw -= candidates[i].value;
+    if (draw < 0.0) { *out_token = (uint32_t)candidates[i].token; return ETC_OK; }
+  }
+  *out_token = (uint32_t)candidates[retained - 1].token;
+  return ETC_OK;
+}
+
+etc_status make_inv_freq(etc_runtime* rt, double theta, int head_dim, double** out_device) {
+  // theta^(-2j/D) with the host pow(), as rotary_forward_into_impl evaluates it (composed.rs:2712-2716)
+  const int half = head_dim / 2;
+  std::vector<double> host((size_t)std::max(half, 1));
+  for (int j = 0; j < half; ++j) host[(size_t)j] = std::pow(theta, -2.0 * (double)j / (double)head_dim);
+  void* d = nullptr;
+  ETC_TRY(rt->device_alloc(host.size() * sizeof(double), &d));
+  cudaError_t e = cudaMemcpyAsync(d, host.data(), host.size() * sizeof(double), cudaMemcpyHostToDevice, rt->stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(rt->stream);
+  if (e != cudaSuccess) {
+    rt->device_free(d);
+    return fail(ETC_TRANSFER, std::string("rope table upload failed: ") + cudaGetErrorString(e));
+  }
+  *out_device = (double*)d;
+  return ETC_OK;
+}
+
+etc_status build_qweight(etc_runtime* rt, int codec, const void* const* parts, const int64_t* part_rows, int n_parts,
+                         int64_t columns, int interleave8, int on_device, etc_qweight** out) {
+  if (codec != ETC_CODEC_Q4_0 && codec != ETC_CODEC_Q8_0)
+    return fail(ETC_UNSUPPORTED, std::string("tiled weights support Q4_0 and Q8_0, got ") + codec_name(codec));
+  if (n_parts < 1 || n_parts > 4) return fail(ETC_INVALID_ARGUMENT, "qweight: between 1 and 4 parts are supported");
+  if (columns <= 0 || columns % 64 != 0)
+    return fail(ETC_COMPILATION, "qweight: logical row width " + std::to_string(columns) + " must be a multiple of 64");
+  if (interleave8 && (n_parts != 2 || part_rows[0] != part_rows[1] || part_rows[0] % 8 != 0))
+    return fail(ETC_COMPILATION, "qweight: interleave8 needs two parts of equal row count divisible by 8");
+  int64_t rows = 0;
+  for (int p = 0; p < n_parts; ++p) {
+    if (part_rows[p] <= 0 || !parts[p]) return fail(ETC_INVALID_ARGUMENT, "qweight: empty part");
+    rows += part_rows[p];
+  }
+  const int64_t row_bytes = codec_row_bytes(codec, columns);
+  etc_qweight* w = new etc_qweight();
+  w->rt = rt;
+  w->tiled.codec = codec;
+  w->tiled.rows = rows;
+  w->tiled.rows_padded = (rows + 15) / 16 * 16;
+  w->tiled.columns = columns;
+  w->tiled.interleave8 = interleave8;
+  const int64_t kblocks = columns / 32;
+  w->tiled.quant_bytes = (size_t)w->tiled.rows_padded * kblocks * (codec == ETC_CODEC_Q4_0 ? 16 : 32);
+  w->tiled.scale_bytes = (size_t)w->tiled.rows_padded * kblocks * 2;
+  etc_status st = rt->device_alloc(w->tiled.quant_bytes, (void**)&w->tiled.quants);
+  if (st == ETC_OK) st = rt->device_alloc(w->tiled.scale_bytes, (void**)&w->tiled.scales);
+  RepackParts rp;
+  std::memset(&rp, 0, sizeof(rp));
+  rp.n_parts = n_parts;
+  std::vector<void*> staged;
+  for (int p = 0; p < n_parts && st == ETC_OK; ++p) {
+    rp.rows[p] = part_rows[p];
+    if (on_device) {
+      rp.ptr[p] = (const uint8_t*)parts[p];
+    } else {
+      void* d = nullptr;
+      const size_t bytes = (size_t)part_rows[p] * (size_t)row_bytes;
+      st = rt->device_alloc(bytes, &d);
+      if (st != ETC_OK) break;
+      staged.push_back(d);
+      cudaError_t e = cudaMemcpyAsync(d, parts[p], bytes, cudaMemcpyHostToDevice, rt->stream);
+      if (e != cudaSuccess) st = fail(ETC_TRANSFER, std::string("qweight upload failed: ") + cudaGetErrorString(e));
+      rp.ptr[p] = (const uint8_t*)d;
+    }
+  }
+  if (st == ETC_OK) {
+    cudaError_t e = launch_repack(w->tiled, rp, rt->stream);
+    rt->launches++;
+    if (e == cudaSuccess) e = cudaStreamSynchronize(rt->stream);
+    if (e != cudaSuccess) st = fail(ETC_EXECUTION, std::string("qweight repack failed: ") + cudaGetErrorString(e));
+  }
+  const std::string message = last_error();
+  for (void* d : staged) rt->device_free(d);
+  if (st != ETC_OK) {
+    rt->device_free(w->tiled.quants);
+    rt->device_free(w->tiled.scales);
+    delete w;
+    return fail(st, message);
+  }
+  *out = w;
+  return ETC_OK;
+}
+
+void destroy_qweight(etc_qweight* w) {
+  if (!w) return;
+  w->rt->device_free(w->tiled.quants);
+  w->rt->device_free(w->tiled.scales);
+  w->magic = 0;
+  delete w;
+}
+
+}  // namespace etc
+
+static bool valid_weight(const etc_qweight* w) { return w && w->magic == kWeightMagic; }
+
+extern "C" {
+
+etc_status etc_encoded_row_bytes(etc_codec codec, int64_t columns, int64_t* out_bytes) {
+  int64_t rb = 0;
+  ETC_TRY(check_codec_geometry("quantized", codec, 0, columns, &rb));
+  *out_bytes = rb;
+  return ETC_OK;
+}
+
+etc_status etc_dequantize_into(etc_runtime* rt, etc_codec codec, const void* d_packed, int64_t rows, int64_t columns,
+                               float* d_out) {
+  ETC_TRY(activate(rt));
+  ETC_TRY(check_codec_geometry("dequantize", codec, rows, columns, nullptr));
+  ETC_CUDA(launch_dequantize(codec, (const uint8_t*)d_packed, rows, columns, d_out, rt->stream));
+  rt->launches++;
+  return ETC_OK;
+}
+
+etc_status etc_quantize_into(etc_runtime* rt, etc_codec codec, const float* d_x, int64_t rows, int64_t columns,
+                             void* d_packed) {
+  ETC_TRY(activate(rt));
+  if (codec != ETC_CODEC_Q4_0 && codec != ETC_CODEC_Q8_0)
+    return fail(ETC_UNSUPPORTED, std::string("quantize: only Q4_0 and Q8_0 are supported, got ") + codec_name(codec));
+  ETC_TRY(check_codec_geometry("quantize", codec, rows, columns, nullptr));
+  ETC_CUDA(launch_quantize(codec, d_x, rows, columns, (uint8_t*)d_packed, rt->stream));
+  rt->launches++;
+  return ETC_OK;
+}
+
+etc_status etc_qlinear_requirements(etc_codec codec, int64_t vectors, int64_t rows, int64_t columns, size_t* out_bytes,
+                                    size_t* scratch_bytes) {
+  ETC_TRY(check_codec_geometry("quantized_linear", codec, rows, columns, nullptr));
+  if (vectors < 0 || (rows > 0 && vectors > (int64_t)(SIZE_MAX / 4) / rows))
+    return fail(ETC_COMPILATION, "quantized_linear: output byte size overflow");
+  if (out_bytes) *out_bytes = (size_t)vectors * (size_t)rows * sizeof(float);
+  if (scratch_bytes) *scratch_bytes = 0;
+  return ETC_OK;
+}
+
+etc_status etc_qlinear_into(etc_runtime* rt, etc_codec codec, const float* d_x, int64_t vectors, int64_t columns,
+                            const void* d_weight, int64_t rows, const float* d_bias, float* d_out,
+                            const volatile int* cancelled) {
+  ETC_TRY(activate(rt));
+  ETC_TRY(check_codec_geometry("quantized_linear", codec, rows, columns, nullptr));
+  if (cancelled && *cancelled) return fail(ETC_CANCELLED, "operation aborted");
+  int launches = 0;
+  ETC_CUDA(launch_qlinear_generic(codec, d_x, vectors, columns, (const uint8_t*)d_weight, rows, d_bias, d_out, rt->stream,
+                                  &launches));
+  rt->launches += (uint64_t)launches;
+  return ETC_OK;
+}
+
+etc_status etc_qweight_create(etc_runtime* rt, etc_codec codec, const void* const* parts, const int64_t* part_rows,
+                              int n_parts, int64_t columns, int interleave8, int on_device, etc_qweight** out) {
+  ETC_TRY(activate(rt));
+  if (!out) return fail(ETC_INVALID_ARGUMENT, "out is null");
+  *out = nullptr;
+  return build_qweight(rt, codec, parts, part_rows, n_parts, columns, interleave8, on_device, out);
+}
+
+etc_status etc_qweight_destroy(etc_qweight* w) {
+  if (!valid_weight(w)) return fail(ETC_INVALID_HANDLE, "weight handle is invalid or destroyed");
+  ETC_TRY(activate(w->rt));
+  cudaStreamSynchronize(w->rt->stream);
+  destroy_qweight(w);
+  return ETC_OK;
+}
+
+etc_status etc_qweight_shape(const etc_qweight* w, int64_t* rows, int64_t* columns, etc_codec* codec, uint64_t* device_bytes) {
+  if (!valid_weight(w)) return fail(ETC_INVALID_HANDLE, "weight handle is invalid or destroyed");
+  if (rows) *rows = w->tiled.rows;
+  if (columns) *columns = w->tiled.columns;
+  if (codec) *codec = (etc_codec)w->tiled.codec;
+  if (device_bytes) *device_bytes = w->tiled.quant_bytes + w->tiled.scale_bytes;
+  return ETC_OK;
+}
+
+etc_status etc_qlinear_tiled_scratch_bytes(const etc_qweight* w, int64_t vectors, size_t* scratch_bytes) {
+  if (!valid_weight(w)) return fail(ETC_INVALID_HANDLE, "weight handle is invalid or destroyed");
+  *scratch_bytes = plan_tiled(w->tiled, vectors, w->rt->sm_count).scratch_bytes;
+  return ETC_OK;
+}
+
+etc_status etc_qlinear_tiled_into(etc_runtime* rt, const etc_qweight* w, const float* d_x, int64_t vectors,
+                                  const float* d_bias, const float* d_residual, etc_epilogue epilogue, float* d_out,
+                                  void* d_scratch, size_t scratch_bytes) {
+  ETC_TRY(activate(rt));
+  if (!valid_weight(w) || w->rt != rt) return fail(ETC_INVALID_HANDLE, "weight belongs to a different runtime");
+  if (epilogue == ETC_EPILOGUE_SWIGLU && !w->tiled.interleave8)
+    return fail(ETC_UNSUPPORTED, "quantized_linear: the swiglu epilogue needs a weight built with interleave8");
+  if (epilogue == ETC_EPILOGUE_RESIDUAL && !d_residual)
+    return fail(ETC_INVALID_ARGUMENT, "quantized_linear: the residual epilogue needs a residual input");
+  if (vectors <= 0) return ETC_OK;
+  const size_t need = plan_tiled(w->tiled, vectors, rt->sm_count).scratch_bytes;
+  float* scratch = (float*)d_scratch;
+  if (need > 0) {
+    if (!scratch) {
+      void* ws = nullptr;
+      ETC_TRY(rt->workspace(need, &ws));
+      scratch = (float*)ws;
+    } else if (scratch_bytes < need) {
+      return fail(ETC_INVALID_ARGUMENT, "quantized_linear: scratch holds " + std::to_string(scratch_bytes) + " bytes, " +
+                                            std::to_string(need) + " needed");
+    }
+  }
+  int launches = 0;
+  ETC_CUDA(launch_qlinear_tiled(w->tiled, d_x, vectors, d_bias, d_residual, epilogue, d_out, scratch, rt->sm_count,
+                                rt->stream, &launches));
+  rt->launches += (uint64_t)launches;
+  return ETC_OK;
+}
+
+etc_status etc_qembedding_into(etc_runtime* rt, etc_codec codec, const void* d_indexes, etc_index_dtype index_dtype,
+                               int64_t count, const void* d_weight, int64_t rows, int64_t columns, float* d_out) {
+  ETC_TRY(activate(rt));
+  if (index_dtype != ETC_INDEX_U32 && index_dtype != ETC_INDEX_I64)
+    return fail(ETC_UNSUPPORTED, "quantized_embedding: indexes must be u32 or i64");
+  if (codec == ETC_CODEC_F32) {
+    ETC_CUDA(launch_embedding_f32(d_indexes, index_dtype == ETC_INDEX_I64, count, (const float*)d_weight, rows, columns, d_out,
+                                  rt->d_status, rt->stream));
+  } else {
+    ETC_TRY(check_codec_geometry("quantized_embedding", codec, rows, columns, nullptr));
+    ETC_CUDA(launch_qembedding(codec, d_indexes, index_dtype == ETC_INDEX_I64, count, (const uint8_t*)d_weight, rows, columns,
+                               d_out, rt->d_status, rt->stream));
+  }
+  rt->launches++;
+  return ETC_OK;
+}
+
+etc_status etc_linear_f32_into(etc_runtime* rt, const float* d_x, int64_t m, int64_t k, const float* d_w, int64_t n,
+                               const float* d_bias, float* d_out) {
+  ETC_TRY(activate(rt));
+  ETC_CUDA(launch_linear_f32(d_x, m, k, d_w, n, d_bias, d_out, rt->stream));
+  rt->launches++;
+  return ETC_OK;
+}
+
+etc_status etc_rmsnorm_into(etc_runtime* rt, const float* d_x, const float* d_weight, double eps, int64_t rows, int64_t n,
+                            float* d_out) {
+  ETC_TRY(activate(rt));
+  if (n <= 0) return fail(ETC_COMPILATION, "rms_norm: normalized dimension must be positive");
+  ETC_CUDA(launch_rmsnorm(d_x, d_weight, eps, rows, n, d_out, rt->stream));
+  rt->launches++;
+  return ETC_OK;
+}
+
+etc_status etc_rope_into(etc_runtime* rt, const float* d_x, const int64_t* d_offsets, int64_t n_offsets, double theta,
+                         etc_rope_layout layout, int64_t batch, int64_t heads, int64_t steps, int64_t head_dim, float* d_out) {
+  ETC_TRY(activate(rt));
+  if (head_dim <= 0 || head_dim % 2 != 0) return fail(ETC_COMPILATION, "rotary: expected rank >= 2 and an even head dimension");
+  if (n_offsets != 1 && n_offsets != batch)
+    return fail(ETC_EXECUTION, "rotary embedding: " + std::to_string(n_offsets) + " offsets for batch " + std::to_string(batch));
+  double* inv_freq = nullptr;
+  ETC_TRY(make_inv_freq(rt, theta, (int)head_dim, &inv_freq));
+  cudaError_t e = launch_rope(d_x, d_offsets, n_offsets, inv_freq, layout, batch, heads, steps, head_dim, d_out, rt->stream);
+  rt->launches++;
+  if (e == cudaSuccess) e = cudaStreamSynchronize(rt->stream);  // the table is freed below
+  rt->device_free(inv_freq);
+  if (e != cudaSuccess) return fail(ETC_EXECUTION, std::string("rotary: ") + cudaGetErrorString(e));
+  return ETC_OK;
+}
+
+etc_status etc_swiglu_into(etc_runtime* rt, const float* d_gate, const float* d_up, int64_t n, float* d_out) {
+  ETC_TRY(activate(rt));
+  ETC_CUDA(launch_swiglu(d_gate, d_up, n, d_out, 1, rt->stream));
+  rt->launches++;
+  return ETC_OK;
+}
+
+etc_status etc_add_into(etc_runtime* rt, const float* d_a, const float* d_b, int64_t n, float* d_out) {
+  ETC_TRY(activate(rt));
+  ETC_CUDA(launch_add(d_a, d_b, n, d_out, rt->stream));
+  rt->launches++;
+  return ETC_OK;
+}
+
+etc_status etc_argmax_into(etc_runtime* rt, const float* d_logits, int64_t rows, int64_t vocab, uint32_t* d_tokens) {
+  ETC_TRY(activate(rt));
+  if (vocab <= 0) return fail(ETC_EXECUTION, "sample: logits must be non-empty");
+  if (vocab > 1048576) return fail(ETC_EXECUTION, "sample: vocabulary " + std::to_string(vocab) + " exceeds limit 1048576");
+  ETC_CUDA(launch_argmax(d_logits, rows, vocab, d_tokens, rt->d_status, rt->stream));
+  rt->launches++;
+  return ETC_OK;
+}
+
+etc_status etc_sample_row(etc_runtime* rt, const float* d_logits, int64_t vocab, double temperature, int64_t top_k,
+                          double top_p, uint64_t seed, uint64_t counter, uint32_t* out_token) {
+  ETC_TRY(activate(rt));
+  if (vocab <= 0) return fail(ETC_EXECUTION, "sample: logits must be non-empty");
+  std::vector<float> row((size_t)vocab);
+  cudaError_t e = cudaMemcpyAsync(row.data(), d_logits, (size_t)vocab * sizeof(float), cudaMemcpyDeviceToHost, rt->stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(rt->stream);
+  if (e != cudaSuccess) return fail(ETC_TRANSFER, std::string("readback failed: ") + cudaGetErrorString(e));
+  return sample_logits_host(row.data(), vocab, temperature, top_k, top_p, seed, counter, out_token);
+}
+
+}  // extern "C"

@@ -1,0 +1,20 @@
+// Retained (constant) weights of the C ABI.
+#pragma once
+
+#include "common.h"
+#include "kernels.h"
+
+struct etc_qweight {
+  uint32_t magic = etc::kWeightMagic;
+  etc_runtime* rt = nullptr;
+  etc::TiledWeight tiled;
+};
+
+namespace etc {
+etc_status build_qweight(etc_runtime* rt, int codec, const void* const* parts, const int64_t* part_rows, int n_parts,
+                         int64_t columns, int interleave8, int on_device, etc_qweight** out);
+void destroy_qweight(etc_qweight* w);
+etc_status make_inv_freq(etc_runtime* rt, double theta, int head_dim, double** out_device);
+etc_status sample_logits_host(const float* logits, int64_t length, double temperature, int64_t top_k, double top_p,
+                              uint64_t seed, uint64_t counter, uint32_t* out_token);
+}  // namespace etc

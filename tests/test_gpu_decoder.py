@@ -1,0 +1,187 @@
+"""GPU parity of the compiled decoder against the CPU oracle: greedy token ids (exact) and teacher-forced
+logits on the tiny f32 model, the quantized tensor-core path within the logits tolerance, and the stateful
+transaction rules (padding, rollback, cancellation, device-resident generation)."""
+import numpy as np
+import pytest
+
+import effect_torch_b200 as et
+import oracle as orc
+from tests import helpers
+from tests.gpu_util import runtime
+
+pytestmark = pytest.mark.gpu
+LOGIT_TOL = 2e-3  # north-star tolerance on logits (max |err| / max |ref|)
+
+
+def gpu_decoder(cfg, weights, batch, max_tokens, block_size=16, kv_dtype=et.KV_F32, exact=True, max_advance=16, window=None):
+    dec = et.Executable(runtime(), layers=cfg["layers"], d_model=cfg["d_model"], q_heads=cfg["q_heads"], kv_heads=cfg["kv_heads"],
+                        head_dim=cfg["head_dim"], ffn=cfg["ffn"], vocab=cfg["vocab"], rms_eps=cfg["rms_eps"],
+                        rope_theta=cfg["rope_theta"], batch=batch, max_tokens=max_tokens, block_size=block_size, kv_dtype=kv_dtype,
+                        exact=exact, max_advance=max_advance, window=window)
+    helpers.load_into(dec, weights)
+    dec.finalize()
+    return dec
+
+
+@pytest.fixture(scope="module")
+def tiny():
+    return helpers.make_weights(helpers.TINY, seed=0)
+
+
+def test_tiny_model_greedy_tokens_match_the_oracle_exactly(tiny):
+    """The reference's CPU-runnable configuration: 4 layers, d_model 256, 4 query x 64, 2 KV heads, FFN 688, vocab 4096,
+    f32 weights and KV, 16-token pages; batch 4 prompts of 32 tokens prefetched in chunks of 16, then 64 greedy steps."""
+    cfg = helpers.TINY
+    rng = np.random.default_rng(0)
+    prompts = rng.integers(0, cfg["vocab"], size=(4, 32)).astype(np.uint32)
+    max_tokens = 4 * 96
+    odec = helpers.oracle_decoder(cfg, tiny, batch=4)
+    opool = orc.Pool(cfg["layers"], cfg["kv_heads"], cfg["head_dim"], max_tokens, 16, orc.F32)
+    oseqs = [opool.make_sequence() for _ in range(4)]
+    gdec = gpu_decoder(cfg, tiny, batch=4, max_tokens=max_tokens)
+    gpool = et.NativeKvPool(runtime(), cfg["layers"], cfg["kv_heads"], cfg["head_dim"], max_tokens, 16, et.KV_F32)
+    gseqs = [gpool.makeSequence() for _ in range(4)]
+    worst = 0.0
+    for chunk in (prompts[:, :16], prompts[:, 16:]):
+        ol, osamp = odec.execute(opool, oseqs, chunk)
+        gl = gdec.execute(gpool, gseqs, chunk)
+        worst = max(worst, helpers.rel_err(gl, ol))
+    otok = osamp.copy()
+    gtok = np.asarray([orc.argmax(r) for r in gl], dtype=np.uint32)
+    np.testing.assert_array_equal(gtok, otok)
+    first_divergence = None
+    for step in range(64):
+        ol, onext = odec.execute(opool, oseqs, otok[:, None])
+        gnext = gdec.executeSampled(gpool, gseqs, gtok[:, None])
+        if first_divergence is None and not np.array_equal(onext, gnext):
+            first_divergence = step
+        otok, gtok = onext, gnext
+    assert first_divergence is None, f"greedy tokens diverged at step {first_divergence}"
+    assert worst <= 1e-5
+    assert [s.cursor for s in gseqs] == [s.cursor for s in oseqs] == [96] * 4
+    for gs, os_ in zip(gseqs, oseqs):
+        np.testing.assert_array_equal(gs.blocks[0], os_.blocks)
+
+
+def test_tiny_model_teacher_forced_logits(tiny):
+    # the reference's own answer to argmax instability: compare logits under identical forced tokens
+    cfg = helpers.TINY
+    rng = np.random.default_rng(1)
+    odec = helpers.oracle_decoder(cfg, tiny, batch=2)
+    gdec = gpu_decoder(cfg, tiny, batch=2, max_tokens=128)
+    opool = orc.Pool(cfg["layers"], cfg["kv_heads"], cfg["head_dim"], 128, 16, orc.F32)
+    gpool = et.NativeKvPool(runtime(), cfg["layers"], cfg["kv_heads"], cfg["head_dim"], 128, 16, et.KV_F32)
+    oseqs = [opool.make_sequence() for _ in range(2)]
+    gseqs = [gpool.makeSequence() for _ in range(2)]
+    for advance in (7, 1, 1, 16, 1, 3):
+        toks = rng.integers(0, cfg["vocab"], size=(2, advance)).astype(np.uint32)
+        ol, _ = odec.execute(opool, oseqs, toks)
+        gl = gdec.execute(gpool, gseqs, toks)
+        assert helpers.rel_err(gl, ol) <= 1e-5
+
+
+@pytest.mark.parametrize("codec", [orc.Q4_0, orc.Q8_0])
+@pytest.mark.parametrize("kv_dtype,okv,tol", [(et.KV_F16, orc.F16, LOGIT_TOL), (et.KV_F32, orc.F32, LOGIT_TOL)])
+def test_quantized_model_on_the_tensor_core_path(codec, kv_dtype, okv, tol):
+    """Block-quantized projections on the tiled MMA kernels (and, with an f16 pool, the flash-decoding kernel)
+    against the oracle running the same packed bytes: teacher-forced logits within 2e-3."""
+    cfg = helpers.TINY_Q
+    w = helpers.make_weights(cfg, seed=3, codec=codec)
+    rng = np.random.default_rng(2)
+    B = 3
+    odec = helpers.oracle_decoder(cfg, w, batch=B)
+    gdec = gpu_decoder(cfg, w, batch=B, max_tokens=256, kv_dtype=kv_dtype, exact=False, max_advance=8)
+    opool = orc.Pool(cfg["layers"], cfg["kv_heads"], cfg["head_dim"], 256, 16, okv)
+    gpool = et.NativeKvPool(runtime(), cfg["layers"], cfg["kv_heads"], cfg["head_dim"], 256, 16, kv_dtype)
+    oseqs = [opool.make_sequence() for _ in range(B)]
+    gseqs = [gpool.makeSequence() for _ in range(B)]
+    for advance in (8, 8, 5, 1, 1, 1, 1):
+        toks = rng.integers(0, cfg["vocab"], size=(B, advance)).astype(np.uint32)
+        ol, _ = odec.execute(opool, oseqs, toks)
+        gl = gdec.execute(gpool, gseqs, toks)
+        assert helpers.rel_err(gl, ol) <= tol, f"advance {advance}"
+    assert gdec.diagnostics()["launches_per_step"] > 0
+
+
+def test_device_resident_generation_equals_stepwise_execution():
+    cfg = helpers.TINY_Q
+    w = helpers.make_weights(cfg, seed=4, codec=orc.Q4_0)
+    B, steps = 4, 40
+    rng = np.random.default_rng(5)
+    prompt = rng.integers(0, cfg["vocab"], size=(B, 8)).astype(np.uint32)
+    first = rng.integers(0, cfg["vocab"], size=B).astype(np.uint32)
+    results = []
+    for mode in ("stepwise", "resident"):
+        dec = gpu_decoder(cfg, w, batch=B, max_tokens=512, kv_dtype=et.KV_F16, exact=False, max_advance=8)
+        pool = et.NativeKvPool(runtime(), cfg["layers"], cfg["kv_heads"], cfg["head_dim"], 512, 16, et.KV_F16)
+        seqs = [pool.makeSequence() for _ in range(B)]
+        dec.execute(pool, seqs, prompt)
+        if mode == "stepwise":
+            tok, out = first, []
+            for _ in range(steps):
+                tok = dec.executeSampled(pool, seqs, tok[:, None])
+                out.append(tok)
+            results.append(np.stack(out))
+        else:
+            out, ms = dec.generate_greedy(pool, seqs, first, steps)
+            assert ms > 0
+            results.append(out)
+        assert [s.cursor for s in seqs] == [8 + steps] * B
+    np.testing.assert_array_equal(results[0], results[1])
+
+
+def test_transaction_rollback_padding_and_cancellation(tiny):
+    cfg = helpers.TINY
+    gdec = gpu_decoder(cfg, tiny, batch=4, max_tokens=32, max_advance=16)
+    pool = et.NativeKvPool(runtime(), cfg["layers"], cfg["kv_heads"], cfg["head_dim"], 32, 16, et.KV_F32)
+    a, b = pool.makeSequence(), pool.makeSequence()
+    toks = np.arange(32, dtype=np.uint32).reshape(2, 16)
+    logits = gdec.execute(pool, [a, b], toks)  # 2 active of 4 lanes
+    assert logits.shape == (2, cfg["vocab"]) and (a.cursor, b.cursor) == (16, 16)
+    # single-lane run of the same tokens gives the same logits (padding is inert)
+    pool1 = et.NativeKvPool(runtime(), cfg["layers"], cfg["kv_heads"], cfg["head_dim"], 32, 16, et.KV_F32)
+    s1 = pool1.makeSequence()
+    np.testing.assert_array_equal(gdec.execute(pool1, [s1], toks[:1])[0], logits[0])
+    free_before = pool.freeBlocks
+    with pytest.raises(et.BackendError, match="pool exhausted") as e:
+        gdec.executeSampled(pool, [a, b], np.asarray([[1], [2]], dtype=np.uint32))
+    assert e.value.reason == "execution-failed"
+    assert (a.cursor, b.cursor) == (16, 16) and pool.freeBlocks == free_before
+    with pytest.raises(et.BackendError, match="^operation aborted$") as e:
+        gdec.executeSampled(pool1, [s1], np.asarray([[1]], dtype=np.uint32), cancelled=True)
+    assert e.value.reason == "cancelled" and s1.cursor == 16
+    with pytest.raises(et.BackendError, match=r"accepts 1\.\.=4 sequences"):
+        gdec.execute(pool, [a, b, a, b, a], np.zeros((5, 1), dtype=np.uint32))
+    with pytest.raises(et.BackendError, match="duplicate sequence"):
+        gdec.execute(pool, [a, a], np.zeros((2, 1), dtype=np.uint32))
+    other = et.NativeKvPool(runtime(), cfg["layers"], cfg["kv_heads"], cfg["head_dim"], 64, 16, et.KV_F32)
+    with pytest.raises(et.BackendError, match="does not match the compiled state schema"):
+        gdec.execute(other, [other.makeSequence()], np.zeros((1, 1), dtype=np.uint32))
+    with pytest.raises(et.BackendError, match="is outside 0..4096"):
+        gdec.execute(pool1, [s1], np.asarray([[5000]], dtype=np.uint32))
+    assert s1.cursor == 16  # the failed step rolled back
+    b.release()
+    with pytest.raises(et.BackendError, match="kv sequence 1 is released"):
+        gdec.execute(pool, [a, b], np.zeros((2, 1), dtype=np.uint32))
+
+
+def test_sliding_window_decoder_matches_the_oracle():
+    cfg = dict(helpers.TINY_Q, layers=2)
+    w = helpers.make_weights(cfg, seed=6)
+    odec = orc.Decoder(cfg["layers"], cfg["d_model"], cfg["q_heads"], cfg["kv_heads"], cfg["head_dim"], cfg["ffn"], cfg["vocab"],
+                       eps=cfg["rms_eps"], theta=cfg["rope_theta"], window=20, batch=1)
+    helpers.load_into(odec, w)
+    odec.set_mode(False, 4)
+    gdec = gpu_decoder(cfg, w, batch=1, max_tokens=48, window=20, max_advance=1)
+    opool = orc.Pool(cfg["layers"], cfg["kv_heads"], cfg["head_dim"], 48, 16, orc.F32)
+    gpool = et.NativeKvPool(runtime(), cfg["layers"], cfg["kv_heads"], cfg["head_dim"], 48, 16, et.KV_F32)
+    os_, gs = opool.make_sequence(), gpool.makeSequence()
+    tok = np.asarray([[3]], dtype=np.uint32)
+    for step in range(70):  # cursor runs far past the 48-token pool
+        ol, onext = odec.execute(opool, [os_], tok)
+        gl = gdec.execute(gpool, [gs], tok)
+        assert helpers.rel_err(gl, ol) <= 1e-5, f"step {step}"
+        tok = onext[:, None]
+    assert gs.cursor == os_.cursor == 70
+    np.testing.assert_array_equal(gs.blocks[0], os_.blocks)
+    assert gs.blocks[1] == os_.head
