@@ -297,10 +297,10 @@ class NativeKvSequence:
 
     @property
     def blocks(self):
-        cap = self.pool.max_tokens // self.pool.block_size
-        buf = np.zeros(cap, dtype=np.uint32)
         n, head = C.c_int64(0), C.c_int64(0)
-        _check(self.pool.rt.L.etc_seq_blocks(self.h, _ptr(buf), cap, C.byref(n), C.byref(head)))
+        _check(self.pool.rt.L.etc_seq_blocks(self.h, None, 0, C.byref(n), C.byref(head)))
+        buf = np.zeros(max(n.value, 1), dtype=np.uint32)
+        _check(self.pool.rt.L.etc_seq_blocks(self.h, _ptr(buf), n.value, C.byref(n), C.byref(head)))
         return buf[:n.value].copy(), head.value
 
     @property

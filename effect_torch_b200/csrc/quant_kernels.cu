@@ -122,9 +122,8 @@ __global__ void quantize_q4_0_kernel(const float* __restrict__ x, int64_t total_
     uint8_t* dst = out + blk * 18;
     if (lane < 16) dst[2 + lane] = (uint8_t)(code | (hi << 4));
     if (lane == 0) {
-      const unsigned short bits = __half_as_ushort(__float2half_rn(d));
-      dst[0] = (uint8_t)(bits & 0xff);
-      dst[1] = (uint8_t)(bits >> 8);
+      // block offsets are even, so the little-endian f16 scale is one aligned 16-bit store
+      *reinterpret_cast<unsigned short*>(dst) = __half_as_ushort(__float2half_rn(d));
     }
   }
 }
@@ -145,9 +144,8 @@ __global__ void quantize_q8_0_kernel(const float* __restrict__ x, int64_t total_
     uint8_t* dst = out + blk * 34;
     dst[2 + lane] = (uint8_t)(signed char)(int)q;
     if (lane == 0) {
-      const unsigned short bits = __half_as_ushort(__float2half_rn(d));
-      dst[0] = (uint8_t)(bits & 0xff);
-      dst[1] = (uint8_t)(bits >> 8);
+      // block offsets are even, so the little-endian f16 scale is one aligned 16-bit store
+      *reinterpret_cast<unsigned short*>(dst) = __half_as_ushort(__float2half_rn(d));
     }
   }
 }
