@@ -176,8 +176,8 @@ etc_status run_linear(StepContext& s, const BoundWeight& raw, etc_qweight* tiled
   etc_decoder* d = s.dec;
   cudaStream_t stream = d->rt->stream;
   if (tiled_w) {
-    ETC_CUDA(launch_qlinear_tiled(tiled_w->tiled, x, vectors, nullptr, residual, epilogue, out, d->lin_scratch, d->rt->sm_count,
-                                  stream, &s.launches));
+    ETC_CUDA(launch_qlinear_tiled(tiled_w->tiled, x, vectors, nullptr, residual, epilogue, out, d->lin_scratch,
+                                  d->rt->d_status, d->rt->sm_count, stream, &s.launches));
     return ETC_OK;
   }
   float* target = epilogue == ETC_EPILOGUE_RESIDUAL ? d->proj : out;
@@ -588,13 +588,14 @@ etc_status etc_decoder_finalize(etc_decoder* dec) {
   ETC_TRY(dalloc(dec, &dec->d_tables, (size_t)c.batch * dec->max_blocks));
   if (tiled) {
     size_t need = 0;
-    const int64_t probe = std::min<int64_t>((int64_t)R, 32);
+    // the plan (vector padding, split count) changes at these vector counts; cover every one up to R rows
+    const int64_t probes[] = {1, 9, 17, 32, 64, 128, 256, (int64_t)R};
     for (size_t l = 0; l < L; ++l)
       for (etc_qweight* w : {dec->t_qkv[l], dec->t_o[l], dec->t_gu[l], dec->t_down[l]})
-        for (int64_t v : {(int64_t)1, (int64_t)9, (int64_t)17, probe})
-          need = std::max(need, plan_tiled(w->tiled, std::min(v, probe), rt->sm_count).scratch_bytes);
-    for (int64_t v : {(int64_t)1, (int64_t)9, (int64_t)17, (int64_t)std::min(c.batch, 32)})
-      need = std::max(need, plan_tiled(dec->t_head->tiled, v, rt->sm_count).scratch_bytes);
+        for (int64_t v : probes)
+          need = std::max(need, tiled_scratch_bytes(w->tiled, std::min<int64_t>(v, (int64_t)R), rt->sm_count));
+    for (int64_t v : probes)
+      need = std::max(need, tiled_scratch_bytes(dec->t_head->tiled, std::min<int64_t>(v, c.batch), rt->sm_count));
     dec->lin_scratch_bytes = need;
     if (need) ETC_TRY(dalloc(dec, &dec->lin_scratch, need / sizeof(float)));
     // split-KV partials: the split count never exceeds the plan for the longest possible table

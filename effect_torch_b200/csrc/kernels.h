@@ -21,7 +21,12 @@ cudaError_t launch_qembedding(int codec, const void* indexes, int index_is_i64, 
                               int64_t rows, int64_t columns, float* out, DeviceStatus* status, cudaStream_t stream);
 
 // Tiled (tensor-core) weight layout: see quant_kernels.cu for the byte map.
+enum TiledLayout : int {
+  kLayoutMma16 = 0,   // 16-row tiles for the mma.sync kernel (quant_kernels.cu)
+  kLayoutUmma128 = 1  // 128-row tiles streamed per thread for the tcgen05 kernel (qlinear_umma.cu)
+};
 struct TiledWeight {
+  int layout = kLayoutMma16;
   int codec = 0;
   int64_t rows = 0;         // logical rows (outputs) as seen by the mma tiles (after concatenation/interleave)
   int64_t rows_padded = 0;  // multiple of 16
@@ -45,11 +50,31 @@ struct TiledPlan {
   size_t scratch_bytes = 0;  // splits > 1: [splits][nt*8][rows_padded] f32
 };
 TiledPlan plan_tiled(const TiledWeight& w, int64_t vectors, int sm_count);
-// One pass handles up to 32 vectors; the launcher loops passes. epilogue: etc_epilogue.
-// out_half (optional) additionally receives the f16 copy of the result (same shape as out).
-cudaError_t launch_qlinear_tiled(const TiledWeight& w, const float* x, int64_t vectors, const float* bias,
+// mma.sync path: one pass handles up to 32 vectors; the launcher loops passes. epilogue: etc_epilogue.
+cudaError_t launch_qlinear_mma16(const TiledWeight& w, const float* x, int64_t vectors, const float* bias,
                                  const float* residual, int epilogue, float* out, float* scratch, int sm_count,
                                  cudaStream_t stream, int* launches);
+cudaError_t launch_qlinear_reduce(const float* scratch, int splits, int vpad, int vectors, int rows, int rows_padded,
+                                  const float* bias, const float* residual, int epilogue, float* out, cudaStream_t stream);
+
+// tcgen05 path (qlinear_umma.cu)
+struct UmmaPlan {
+  int nv = 32;               // vectors per pass padded to the MMA N (32, 64, 128 or 256)
+  int tiles = 1, splits = 1, blocks_per_split = 0;
+  size_t xh_bytes = 0;       // f16 activations in [K/8][nv][8] order
+  size_t scratch_bytes = 0;  // split-K partials
+};
+UmmaPlan plan_umma(const TiledWeight& w, int64_t vectors, int sm_count);
+cudaError_t launch_repack_umma(const TiledWeight& w, const RepackParts& parts, cudaStream_t stream);
+cudaError_t launch_qlinear_umma(const TiledWeight& w, const float* x, int64_t vectors, const float* bias, const float* residual,
+                                int epilogue, float* out, __half* xh, float* scratch, DeviceStatus* status, int sm_count,
+                                cudaStream_t stream, int* launches);
+
+// Layout-independent front end. `scratch` must hold tiled_scratch_bytes(w, vectors, sm_count).
+size_t tiled_scratch_bytes(const TiledWeight& w, int64_t vectors, int sm_count);
+cudaError_t launch_qlinear_tiled(const TiledWeight& w, const float* x, int64_t vectors, const float* bias,
+                                 const float* residual, int epilogue, float* out, void* scratch, DeviceStatus* status,
+                                 int sm_count, cudaStream_t stream, int* launches);
 
 // ---- dense / elementwise (elementwise.cu) --------------------------------------------------
 cudaError_t launch_linear_f32(const float* x, int64_t m, int64_t k, const float* w, int64_t n, const float* bias,

@@ -4,7 +4,9 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
+#include <string>
 #include <vector>
 
 #include "common.h"
@@ -145,8 +147,12 @@ etc_status build_qweight(etc_runtime* rt, int codec, const void* const* parts, c
   etc_qweight* w = new etc_qweight();
   w->rt = rt;
   w->tiled.codec = codec;
+  // The tcgen05 kernel (128-row tiles) is the default; ETC_TILED_LAYOUT=mma16 keeps the mma.sync kernel for comparison.
+  const char* layout_env = std::getenv("ETC_TILED_LAYOUT");
+  w->tiled.layout = layout_env && std::string(layout_env) == "mma16" ? kLayoutMma16 : kLayoutUmma128;
+  const int64_t row_tile = w->tiled.layout == kLayoutUmma128 ? 128 : 16;
   w->tiled.rows = rows;
-  w->tiled.rows_padded = (rows + 15) / 16 * 16;
+  w->tiled.rows_padded = (rows + row_tile - 1) / row_tile * row_tile;
   w->tiled.columns = columns;
   w->tiled.interleave8 = interleave8;
   const int64_t kblocks = columns / 32;
@@ -282,7 +288,7 @@ etc_status etc_qweight_shape(const etc_qweight* w, int64_t* rows, int64_t* colum
 
 etc_status etc_qlinear_tiled_scratch_bytes(const etc_qweight* w, int64_t vectors, size_t* scratch_bytes) {
   if (!valid_weight(w)) return fail(ETC_INVALID_HANDLE, "weight handle is invalid or destroyed");
-  *scratch_bytes = plan_tiled(w->tiled, vectors, w->rt->sm_count).scratch_bytes;
+  *scratch_bytes = tiled_scratch_bytes(w->tiled, vectors, w->rt->sm_count);
   return ETC_OK;
 }
 
@@ -296,21 +302,21 @@ etc_status etc_qlinear_tiled_into(etc_runtime* rt, const etc_qweight* w, const f
   if (epilogue == ETC_EPILOGUE_RESIDUAL && !d_residual)
     return fail(ETC_INVALID_ARGUMENT, "quantized_linear: the residual epilogue needs a residual input");
   if (vectors <= 0) return ETC_OK;
-  const size_t need = plan_tiled(w->tiled, vectors, rt->sm_count).scratch_bytes;
-  float* scratch = (float*)d_scratch;
+  const size_t need = tiled_scratch_bytes(w->tiled, vectors, rt->sm_count);
+  void* scratch = d_scratch;
   if (need > 0) {
     if (!scratch) {
       void* ws = nullptr;
       ETC_TRY(rt->workspace(need, &ws));
-      scratch = (float*)ws;
+      scratch = ws;
     } else if (scratch_bytes < need) {
       return fail(ETC_INVALID_ARGUMENT, "quantized_linear: scratch holds " + std::to_string(scratch_bytes) + " bytes, " +
                                             std::to_string(need) + " needed");
     }
   }
   int launches = 0;
-  ETC_CUDA(launch_qlinear_tiled(w->tiled, d_x, vectors, d_bias, d_residual, epilogue, d_out, scratch, rt->sm_count,
-                                rt->stream, &launches));
+  ETC_CUDA(launch_qlinear_tiled(w->tiled, d_x, vectors, d_bias, d_residual, epilogue, d_out, scratch, rt->d_status,
+                                rt->sm_count, rt->stream, &launches));
   rt->launches += (uint64_t)launches;
   return ETC_OK;
 }

@@ -1,0 +1,533 @@
+// Dequant linear on the 5th-generation tensor cores (tcgen05) for Q4_0 / Q8_0 weights.
+//
+//   out[v, r] = sum_k x[v, k] * deq(W[r, k])        (quantized_linear, crates/runtime-cpu/src/quantized.rs:419-499)
+//
+// Mapping onto tcgen05.mma.cta_group::1.kind::f16 (M = 128, N = NV, K = 16 per instruction):
+//   * A operand = 128 weight rows, read from TENSOR MEMORY. Four "dequant" warps own one TMEM lane
+//     (= one weight row) per thread: a thread streams its row's packed blocks from HBM (16-byte coalesced
+//     loads, prefetched in registers), expands nibbles/bytes to f16 in registers, multiplies by the block
+//     scale and writes 16 columns per 32-value block with tcgen05.st. Weights never touch shared memory.
+//   * B operand = the NV input vectors (activations), f16 in shared memory in the canonical K-major
+//     no-swizzle layout: 8-column groups of [NV rows][8 halves] (16 bytes per row), which is exactly how
+//     the producer stores activations in global memory ("xh8": [K/8][NV][8] f16), so a stage of 128
+//     columns is ONE contiguous cp.async.bulk copy completing on an mbarrier.
+//   * D = f32 accumulator [128 x NV] in TMEM, read back once per CTA with tcgen05.ld.
+// A CTA is 6 warps: 4 dequant/epilogue warps, 1 bulk-copy warp, 1 MMA-issue warp (one elected lane each).
+// Stages of 4 blocks (128 columns) cycle through a ring of kStages TMEM A buffers + smem B buffers guarded
+// by full_a / full_b / empty mbarriers; tcgen05.commit releases a stage when its MMAs have retired.
+// Split-K over grid.y writes f32 partials that qlinear_reduce_kernel sums; with one split the epilogue
+// (bias, residual add, SwiGLU over interleaved gate/up rows) runs straight from TMEM.
+//
+// Every mbarrier wait is bounded: on expiry the thread raises the abort flag and the status word, all
+// roles fall through to the teardown, TMEM is freed and the kernel returns.
+//
+// Roofline: HBM-bound for NV <= 32 (bytes = rows*K/32*{18,34} + 2*NV*K + 4*V*rows); tensor-bound for NV = 256.
+#include <cuda_fp16.h>
+
+#include <algorithm>
+
+#include "kernels.h"
+
+namespace etc {
+
+namespace {
+
+constexpr int kUmmaRows = 128;
+constexpr int kStageBlocks = 4;   // 32-value blocks per pipeline stage (128 columns = 8 MMAs of K=16)
+constexpr int kStages = 3;
+constexpr int kAColsPerStage = kStageBlocks * 16;  // 32-bit TMEM columns holding 128 f16 per lane
+constexpr int kDequantThreads = 128;
+constexpr int kThreads = 192;
+constexpr unsigned kSpinLimit = 1u << 24;  // bounded mbarrier waits (a stage takes microseconds)
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait: returns false (and raises the abort flag) when the phase never completes.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  for (unsigned spin = 0; spin < kSpinLimit; ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (spin > 1024) __nanosleep(64);
+  }
+  *abort_flag = 1;
+  return false;
+}
+
+__device__ __forceinline__ void bulk_copy_g2s(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* holder, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(holder)), "r"(ncols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+        "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]) : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,"
+      "%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+        "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
+        "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+        "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// D[tmem] (+)= A[tmem] * B[smem desc]; accumulate == 0 overwrites D.
+__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+
+// Shared-memory matrix descriptor, K-major, no swizzle: 8-row x 16-byte core matrices; LBO = byte distance
+// between the two 8-column halves of a K=16 slice, SBO = byte distance between 8-row groups.
+__device__ __forceinline__ uint64_t make_b_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t desc = 0;
+  desc |= (uint64_t)((smem_addr >> 4) & 0x3fff);
+  desc |= (uint64_t)((lbo_bytes >> 4) & 0x3fff) << 16;
+  desc |= (uint64_t)((sbo_bytes >> 4) & 0x3fff) << 32;
+  desc |= (uint64_t)1 << 46;  // descriptor version for sm_100
+  return desc;                // base offset 0, layout type 0 (no swizzle)
+}
+
+__device__ __forceinline__ uint32_t h2u(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
+__device__ __forceinline__ __half2 u2h(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
+
+// One packed u32 = 8 nibbles, logical column j of the word at bit {0,16,8,24,4,20,12,28}[j] -> four half2
+// in column order (c0,c1)(c2,c3)(c4,c5)(c6,c7), times the block scale.
+__device__ __forceinline__ void expand_q4(uint32_t q, __half2 scale, uint32_t* out4) {
+  const uint32_t magic = 0x64006400u;
+  const uint32_t qs = q >> 8;
+  const __half2 bias_lo = __floats2half2_rn(1032.0f, 1032.0f);
+  const __half2 sixteenth = __floats2half2_rn(0.0625f, 0.0625f);
+  const __half2 bias_hi = __floats2half2_rn(-72.0f, -72.0f);
+  out4[0] = h2u(__hmul2(__hsub2(u2h((q & 0x000F000Fu) | magic), bias_lo), scale));
+  out4[1] = h2u(__hmul2(__hsub2(u2h((qs & 0x000F000Fu) | magic), bias_lo), scale));
+  out4[2] = h2u(__hmul2(__hfma2(u2h((q & 0x00F000F0u) | magic), sixteenth, bias_hi), scale));
+  out4[3] = h2u(__hmul2(__hfma2(u2h((qs & 0x00F000F0u) | magic), sixteenth, bias_hi), scale));
+}
+// Four int8 -> (b0,b1)(b2,b3) times scale.
+__device__ __forceinline__ void expand_q8(uint32_t w, __half2 scale, uint32_t* out2) {
+  const uint32_t x = w ^ 0x80808080u;
+  const __half2 bias = __floats2half2_rn(1152.0f, 1152.0f);
+  out2[0] = h2u(__hmul2(__hsub2(u2h(__byte_perm(x, 0x64646464u, 0x4140)), bias), scale));
+  out2[1] = h2u(__hmul2(__hsub2(u2h(__byte_perm(x, 0x64646464u, 0x4342)), bias), scale));
+}
+
+__device__ __forceinline__ float silu_tanh(float x) { return x * (tanhf(x * 0.5f) * 0.5f + 0.5f); }
+
+struct UmmaArgs {
+  const uint4* quants;    // Q4_0: [tile][kblock][128] uint4 ; Q8_0: [tile][kblock][128][2] uint4
+  const __half* scales;   // [tile][kblock][128]
+  const __half* xh;       // [K/8][NV][8] f16
+  const float* bias;
+  const float* residual;
+  float* out;
+  float* scratch;         // [splits][NV][rows_padded]
+  unsigned long long* status;
+  int vectors, rows, rows_padded, kblocks, blocks_per_split, epilogue;
+};
+
+template <int CODEC, int NV>
+__global__ void __launch_bounds__(kThreads) qlinear_umma_kernel(UmmaArgs a) {
+  constexpr int QW = CODEC == 2 ? 1 : 2;                    // uint4 words per (row, block)
+  constexpr uint32_t kStageBBytes = NV * 128 * 2;           // one stage of activations
+  constexpr uint32_t kTmemCols = NV + kStages * kAColsPerStage <= 256 ? 256 : 512;
+  constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(NV >> 3) << 17) | ((uint32_t)(kUmmaRows >> 4) << 24);  // f16 x f16 -> f32
+  extern __shared__ __align__(128) unsigned char smem[];
+  unsigned char* b_ring = smem;                                            // kStages * kStageBBytes
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBBytes);
+  uint64_t* full_a = bars;                // [kStages] 128 arrivals
+  uint64_t* full_b = bars + kStages;      // [kStages] 1 arrival + tx bytes
+  uint64_t* empty = bars + 2 * kStages;   // [kStages] 1 arrival (tcgen05.commit)
+  uint64_t* done = bars + 3 * kStages;    // accumulator complete
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 3 * kStages + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x, split = blockIdx.y;
+  const int kb0 = split * a.blocks_per_split;
+  const int kb1 = min(a.kblocks, kb0 + a.blocks_per_split);
+  const int nstages = (kb1 - kb0 + kStageBlocks - 1) / kStageBlocks;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_a[s], kDequantThreads);
+      mbar_init(&full_b[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(done, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) tmem_alloc(tmem_holder, kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t d_tmem = tmem_base;             // columns [0, NV)
+  const uint32_t a_tmem0 = tmem_base + NV;       // stage s at columns NV + s*kAColsPerStage
+
+  if (warp < 4) {
+    // ------------------------------------------------------------------ dequant warps
+    const int row = threadIdx.x;  // TMEM lane == row inside the tile
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    const uint4* qrow = a.quants + ((size_t)tile * a.kblocks) * (kUmmaRows * QW) + (size_t)row * QW;
+    const __half* srow = a.scales + ((size_t)tile * a.kblocks) * kUmmaRows + row;
+    constexpr int PF = 2;  // stages of packed weights held in registers ahead of use
+    uint4 qbuf[PF][kStageBlocks][QW];
+    __half sbuf[PF][kStageBlocks];
+    auto load_stage = [&](int stage_index, int slot) {
+#pragma unroll
+      for (int b = 0; b < kStageBlocks; ++b) {
+        const int kb = min(kb0 + stage_index * kStageBlocks + b, kb1 - 1);  // clamped: masked at use
+#pragma unroll
+        for (int w = 0; w < QW; ++w) qbuf[slot][b][w] = __ldg(qrow + (size_t)kb * (kUmmaRows * QW) + w);
+        sbuf[slot][b] = __ldg(srow + (size_t)kb * kUmmaRows);
+      }
+    };
+#pragma unroll
+    for (int p = 0; p < PF; ++p)
+      if (p < nstages) load_stage(p, p);
+    bool ok = true;
+    for (int i0 = 0; i0 < nstages && ok; i0 += PF) {
+#pragma unroll
+      for (int p = 0; p < PF; ++p) {
+        const int i = i0 + p;
+        if (i >= nstages || !ok) break;
+        const int s = i % kStages;
+        const uint32_t round = (uint32_t)(i / kStages);
+        // the MMAs that read this TMEM stage in the previous round must have retired
+        ok = mbar_wait(&empty[s], (round & 1) ^ 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const int valid = min(kStageBlocks, kb1 - (kb0 + i * kStageBlocks));
+#pragma unroll
+        for (int b = 0; b < kStageBlocks; ++b) {
+          uint32_t regs[16];
+          const __half2 sc = __half2half2(b < valid ? sbuf[p][b] : __float2half_rn(0.0f));
+          if (CODEC == 2) {
+            const uint4 q = qbuf[p][b][0];
+            expand_q4(q.x, sc, regs + 0);
+            expand_q4(q.y, sc, regs + 4);
+            expand_q4(q.z, sc, regs + 8);
+            expand_q4(q.w, sc, regs + 12);
+          } else {
+            const uint4 q0 = qbuf[p][b][0], q1 = qbuf[p][b][QW - 1];
+            expand_q8(q0.x, sc, regs + 0); expand_q8(q0.y, sc, regs + 2); expand_q8(q0.z, sc, regs + 4); expand_q8(q0.w, sc, regs + 6);
+            expand_q8(q1.x, sc, regs + 8); expand_q8(q1.y, sc, regs + 10); expand_q8(q1.z, sc, regs + 12); expand_q8(q1.w, sc, regs + 14);
+          }
+          tmem_st16(a_tmem0 + lane_base + (uint32_t)(s * kAColsPerStage + b * 16), regs);
+        }
+        if (i + PF < nstages) load_stage(i + PF, p);  // refill this register slot
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(&full_a[s]);
+      }
+    }
+    // ------------------------------------------------------------------ epilogue
+    if (ok) ok = mbar_wait(done, 0, abort_flag);
+    if (ok) {
+      tc_fence_after();
+      const int r = tile * kUmmaRows + row;
+#pragma unroll 1
+      for (int c0 = 0; c0 < NV; c0 += 32) {
+        uint32_t acc[32];
+        tmem_ld32(d_tmem + lane_base + (uint32_t)c0, acc);
+        tmem_wait_ld();
+        if (gridDim.y > 1) {
+          float* dst = a.scratch + ((size_t)split * NV + c0) * a.rows_padded + r;
+#pragma unroll
+          for (int v = 0; v < 32; ++v) dst[(size_t)v * a.rows_padded] = __uint_as_float(acc[v]);
+        } else if (a.epilogue == ETC_EPILOGUE_SWIGLU) {
+          // rows are interleaved in groups of 8: lanes 0-7 of each 16 hold gate rows, lanes 8-15 their up rows
+          const int oc = (r >> 4) * 8 + (r & 7);
+          const float bias_v = a.bias && r < a.rows ? a.bias[r] : 0.0f;
+#pragma unroll
+          for (int v = 0; v < 32; ++v) {
+            const float mine = __uint_as_float(acc[v]) + bias_v;
+            const float partner = __shfl_xor_sync(0xffffffffu, mine, 8);
+            if ((r & 8) == 0 && r + 8 < a.rows && c0 + v < a.vectors)
+              a.out[(size_t)(c0 + v) * (a.rows / 2) + oc] = silu_tanh(mine) * partner;
+          }
+        } else if (r < a.rows) {
+          const float bias_v = a.bias ? a.bias[r] : 0.0f;
+#pragma unroll
+          for (int v = 0; v < 32; ++v) {
+            if (c0 + v >= a.vectors) break;
+            const size_t o = (size_t)(c0 + v) * a.rows + r;
+            const float val = __uint_as_float(acc[v]) + bias_v;
+            a.out[o] = a.epilogue == ETC_EPILOGUE_RESIDUAL ? a.residual[o] + val : val;
+          }
+        }
+      }
+    }
+    tc_fence_before();
+  } else if (warp == 4) {
+    // ------------------------------------------------------------------ activation loader (one lane)
+    if (lane == 0) {
+      int issued = 0;
+      for (int i = 0; i < nstages; ++i) {
+        const int s = i % kStages;
+        const uint32_t round = (uint32_t)(i / kStages);
+        if (!mbar_wait(&empty[s], (round & 1) ^ 1, abort_flag)) break;
+        const int kb = kb0 + i * kStageBlocks;
+        const int valid = min(kStageBlocks, kb1 - kb);
+        const uint32_t bytes = (uint32_t)valid * 4u * NV * 16u;  // 4 column groups of 8 per block
+        mbar_arrive_expect_tx(&full_b[s], bytes);
+        bulk_copy_g2s(b_ring + (size_t)s * kStageBBytes, a.xh + (size_t)kb * 4 * NV * 8, bytes, &full_b[s]);
+        issued = i + 1;
+      }
+      if (*abort_flag) {
+        // give up path: let this warp's own bulk copies land (bounded) before shared memory is released
+        for (int i = max(0, issued - kStages); i < issued; ++i) {
+          const uint32_t parity = (uint32_t)(i / kStages) & 1;
+          for (unsigned spin = 0; spin < (1u << 20) && !mbar_try_wait(&full_b[i % kStages], parity); ++spin) __nanosleep(64);
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ MMA issuer (one lane)
+    if (lane == 0) {
+      bool ok = true;
+      for (int i = 0; i < nstages && ok; ++i) {
+        const int s = i % kStages;
+        const uint32_t parity = (uint32_t)(i / kStages) & 1;
+        ok = mbar_wait(&full_b[s], parity, abort_flag) && mbar_wait(&full_a[s], parity, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const int valid = min(kStageBlocks, kb1 - (kb0 + i * kStageBlocks));
+        const uint32_t b_base = smem_u32(b_ring + (size_t)s * kStageBBytes);
+        for (int j = 0; j < 2 * valid; ++j) {  // K = 16 per MMA: two column groups of B, 8 TMEM columns of A
+          const uint64_t b_desc = make_b_desc(b_base + (uint32_t)j * 2u * NV * 16u, NV * 16u, 128u);
+          umma_ts(d_tmem, a_tmem0 + (uint32_t)(s * kAColsPerStage + j * 8), b_desc, kIdesc, (i > 0 || j > 0) ? 1u : 0u);
+        }
+        tc_commit(&empty[s]);  // arrives when the MMAs above have finished reading this stage
+      }
+      if (ok) tc_commit(done);
+      tc_fence_before();
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag) atomicCAS(a.status, 0ull, 3ull);  // bounded wait expired
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// f32 [vectors, K] -> xh8 [K/8][NV][8] f16 (rows >= vectors are zero), saturating like the mma.sync path.
+template <int NV>
+__global__ void convert_xh8_kernel(const float* __restrict__ x, int vectors, int K, __half* __restrict__ xh) {
+  const int total = (K / 8) * NV;
+  for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
+    const int kg = idx / NV, n = idx - kg * NV;
+    uint4 packed = make_uint4(0u, 0u, 0u, 0u);
+    if (n < vectors) {
+      const float4 lo = *reinterpret_cast<const float4*>(x + (size_t)n * K + kg * 8);
+      const float4 hi = *reinterpret_cast<const float4*>(x + (size_t)n * K + kg * 8 + 4);
+      auto sat = [](float v) { return fminf(fmaxf(v, -65504.f), 65504.f); };
+      packed.x = h2u(__floats2half2_rn(sat(lo.x), sat(lo.y)));
+      packed.y = h2u(__floats2half2_rn(sat(lo.z), sat(lo.w)));
+      packed.z = h2u(__floats2half2_rn(sat(hi.x), sat(hi.y)));
+      packed.w = h2u(__floats2half2_rn(sat(hi.z), sat(hi.w)));
+    }
+    reinterpret_cast<uint4*>(xh)[idx] = packed;
+  }
+}
+
+// Repack raw GGUF rows into the per-thread streaming layout: for row tile t and block kb the 128 rows'
+// 16 (Q4_0) or 32 (Q8_0) payload bytes are contiguous, so each warp load instruction is 512 contiguous bytes.
+__global__ void repack_umma_kernel(RepackParts parts, int codec, int64_t rows, int64_t rows_padded, int64_t kblocks,
+                                   int interleave8, uint32_t* __restrict__ quants, __half* __restrict__ scales) {
+  const int64_t total = rows_padded * kblocks;
+  const int bb = codec == 2 ? 18 : 34;
+  const int words = codec == 2 ? 4 : 8;
+  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = idx / kblocks, kb = idx - r * kblocks;
+    const uint8_t* src_row = nullptr;
+    if (r < rows) {
+      if (interleave8) {
+        const int64_t grp = r >> 4, within = r & 15;
+        src_row = parts.ptr[within >= 8 ? 1 : 0] + (grp * 8 + (within & 7)) * kblocks * bb;
+      } else {
+        int64_t rr = r;
+        for (int p = 0; p < parts.n_parts; ++p) {
+          if (rr < parts.rows[p]) { src_row = parts.ptr[p] + rr * kblocks * bb; break; }
+          rr -= parts.rows[p];
+        }
+      }
+    }
+    const int64_t tile = r / kUmmaRows, row = r % kUmmaRows;
+    uint32_t* dst = quants + ((tile * kblocks + kb) * kUmmaRows + row) * words;
+    __half scale = __float2half_rn(0.0f);
+    if (!src_row) {
+      for (int w = 0; w < words; ++w) dst[w] = codec == 2 ? 0x88888888u : 0u;
+    } else {
+      const uint8_t* blk = src_row + kb * bb;
+      scale = __ushort_as_half((unsigned short)(blk[0] | (blk[1] << 8)));
+      if (codec == 2) {
+        const int pos[8] = {0, 16, 8, 24, 4, 20, 12, 28};
+        for (int w = 0; w < 4; ++w) {
+          uint32_t word = 0;
+          for (int j = 0; j < 8; ++j) {
+            const int i = 8 * w + j;
+            const uint32_t code = i < 16 ? (blk[2 + i] & 0x0fu) : (uint32_t)(blk[2 + i - 16] >> 4);
+            word |= code << pos[j];
+          }
+          dst[w] = word;
+        }
+      } else {
+        for (int w = 0; w < 8; ++w) {
+          uint32_t word = 0;
+          for (int j = 0; j < 4; ++j) word |= (uint32_t)blk[2 + 4 * w + j] << (8 * j);
+          dst[w] = word;
+        }
+      }
+    }
+    scales[(tile * kblocks + kb) * kUmmaRows + row] = scale;
+  }
+}
+
+template <int CODEC, int NV>
+cudaError_t launch_umma_pass(const UmmaArgs& args, int tiles, int splits, cudaStream_t stream) {
+  constexpr size_t smem = (size_t)kStages * NV * 128 * 2 + (3 * kStages + 1) * sizeof(uint64_t) + 16;
+  auto kernel = qlinear_umma_kernel<CODEC, NV>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  kernel<<<dim3((unsigned)tiles, (unsigned)splits), kThreads, smem, stream>>>(args);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_repack_umma(const TiledWeight& w, const RepackParts& parts, cudaStream_t stream) {
+  const int64_t kblocks = w.columns / 32;
+  const int64_t total = w.rows_padded * kblocks;
+  if (total == 0) return cudaSuccess;
+  const unsigned grid = (unsigned)std::min<int64_t>((total + 255) / 256, 148 * 32);
+  repack_umma_kernel<<<grid, 256, 0, stream>>>(parts, w.codec, w.rows, w.rows_padded, kblocks, w.interleave8, (uint32_t*)w.quants, w.scales);
+  return cudaGetLastError();
+}
+
+int umma_vector_pad(int64_t vectors) { return vectors <= 32 ? 32 : (vectors <= 64 ? 64 : (vectors <= 128 ? 128 : 256)); }
+
+UmmaPlan plan_umma(const TiledWeight& w, int64_t vectors, int sm_count) {
+  UmmaPlan p;
+  const int64_t chunk = std::min<int64_t>(vectors, 256);
+  p.nv = umma_vector_pad(chunk);
+  p.tiles = (int)(w.rows_padded / kUmmaRows);
+  const int kblocks = (int)(w.columns / 32);
+  const int stages = (kblocks + kStageBlocks - 1) / kStageBlocks;
+  const int ctas_per_sm = p.nv <= 32 ? 2 : 1;
+  const int target = std::max(1, sm_count) * ctas_per_sm;
+  int splits = std::max(1, target / std::max(1, p.tiles));
+  splits = std::min(splits, std::max(1, stages / 2));  // at least two stages per split
+  const int stages_per_split = (stages + splits - 1) / splits;
+  p.blocks_per_split = stages_per_split * kStageBlocks;
+  p.splits = (kblocks + p.blocks_per_split - 1) / p.blocks_per_split;
+  p.xh_bytes = (size_t)(w.columns / 8) * p.nv * 16;
+  p.scratch_bytes = p.splits > 1 ? (size_t)p.splits * p.nv * w.rows_padded * sizeof(float) : 0;
+  return p;
+}
+
+// qlinear_reduce_kernel lives in quant_kernels.cu
+cudaError_t launch_qlinear_reduce(const float* scratch, int splits, int vpad, int vectors, int rows, int rows_padded,
+                                  const float* bias, const float* residual, int epilogue, float* out, cudaStream_t stream);
+
+cudaError_t launch_qlinear_umma(const TiledWeight& w, const float* x, int64_t vectors, const float* bias, const float* residual,
+                                int epilogue, float* out, __half* xh, float* scratch, DeviceStatus* status, int sm_count,
+                                cudaStream_t stream, int* launches) {
+  const int out_cols = (int)(epilogue == ETC_EPILOGUE_SWIGLU ? w.rows / 2 : w.rows);
+  for (int64_t v0 = 0; v0 < vectors; v0 += 256) {
+    const int64_t chunk = std::min<int64_t>(256, vectors - v0);
+    const UmmaPlan plan = plan_umma(w, chunk, sm_count);
+    const int K = (int)w.columns;
+    const int total = (K / 8) * plan.nv;
+    const unsigned cgrid = (unsigned)std::min((total + 255) / 256, 148 * 4);
+    const float* xin = x + v0 * w.columns;
+    switch (plan.nv) {
+      case 32: convert_xh8_kernel<32><<<cgrid, 256, 0, stream>>>(xin, (int)chunk, K, xh); break;
+      case 64: convert_xh8_kernel<64><<<cgrid, 256, 0, stream>>>(xin, (int)chunk, K, xh); break;
+      case 128: convert_xh8_kernel<128><<<cgrid, 256, 0, stream>>>(xin, (int)chunk, K, xh); break;
+      default: convert_xh8_kernel<256><<<cgrid, 256, 0, stream>>>(xin, (int)chunk, K, xh); break;
+    }
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    if (launches) ++*launches;
+    UmmaArgs args;
+    args.quants = reinterpret_cast<const uint4*>(w.quants);
+    args.scales = w.scales;
+    args.xh = xh;
+    args.bias = bias;
+    args.residual = residual ? residual + v0 * out_cols : nullptr;
+    args.out = out + v0 * out_cols;
+    args.scratch = scratch;
+    args.status = &status->code;
+    args.vectors = (int)chunk;
+    args.rows = (int)w.rows;
+    args.rows_padded = (int)w.rows_padded;
+    args.kblocks = K / 32;
+    args.blocks_per_split = plan.blocks_per_split;
+    args.epilogue = epilogue;
+    const bool q4 = w.codec == 2;
+    switch (plan.nv) {
+      case 32: e = q4 ? launch_umma_pass<2, 32>(args, plan.tiles, plan.splits, stream) : launch_umma_pass<8, 32>(args, plan.tiles, plan.splits, stream); break;
+      case 64: e = q4 ? launch_umma_pass<2, 64>(args, plan.tiles, plan.splits, stream) : launch_umma_pass<8, 64>(args, plan.tiles, plan.splits, stream); break;
+      case 128: e = q4 ? launch_umma_pass<2, 128>(args, plan.tiles, plan.splits, stream) : launch_umma_pass<8, 128>(args, plan.tiles, plan.splits, stream); break;
+      default: e = q4 ? launch_umma_pass<2, 256>(args, plan.tiles, plan.splits, stream) : launch_umma_pass<8, 256>(args, plan.tiles, plan.splits, stream); break;
+    }
+    if (e != cudaSuccess) return e;
+    if (launches) ++*launches;
+    if (plan.splits > 1) {
+      e = launch_qlinear_reduce(scratch, plan.splits, plan.nv, (int)chunk, (int)w.rows, (int)w.rows_padded, bias, args.residual,
+                                epilogue, args.out, stream);
+      if (e != cudaSuccess) return e;
+      if (launches) ++*launches;
+    }
+  }
+  return cudaSuccess;
+}
+
+}  // namespace etc

@@ -337,6 +337,7 @@ __global__ void repack_q8_0_kernel(RepackParts parts, int64_t rows, int64_t rows
 }
 
 cudaError_t launch_repack(const TiledWeight& w, const RepackParts& parts, cudaStream_t stream) {
+  if (w.layout == kLayoutUmma128) return launch_repack_umma(w, parts, stream);
   const int64_t kblocks = w.columns / 32;
   const int64_t total = w.rows_padded * kblocks;
   if (total == 0) return cudaSuccess;
@@ -654,7 +655,48 @@ static cudaError_t launch_tiled_pass(const TiledWeight& w, const TiledPlan& plan
   return cudaGetLastError();
 }
 
+cudaError_t launch_qlinear_reduce(const float* scratch, int splits, int vpad, int vectors, int rows, int rows_padded,
+                                  const float* bias, const float* residual, int epilogue, float* out, cudaStream_t stream) {
+  const int out_cols = epilogue == ETC_EPILOGUE_SWIGLU ? rows / 2 : rows;
+  const int64_t total = (int64_t)vectors * out_cols;
+  if (total == 0) return cudaSuccess;
+  const unsigned grid = (unsigned)std::min<int64_t>((total + 255) / 256, 148 * 8);
+  qlinear_reduce_kernel<<<grid, 256, 0, stream>>>(scratch, splits, vpad, vectors, rows, rows_padded, bias, residual, epilogue, out);
+  return cudaGetLastError();
+}
+
+// Scratch layout of the tcgen05 path: [xh8 activations, rounded to 256 B][split-K partials].
+static size_t umma_xh_region(const UmmaPlan& p) { return (p.xh_bytes + 255) & ~(size_t)255; }
+
+size_t tiled_scratch_bytes(const TiledWeight& w, int64_t vectors, int sm_count) {
+  if (w.layout == kLayoutUmma128) {
+    size_t need = 0;
+    for (int64_t v0 = 0; v0 < vectors; v0 += 256) {
+      const UmmaPlan p = plan_umma(w, std::min<int64_t>(256, vectors - v0), sm_count);
+      need = std::max(need, umma_xh_region(p) + p.scratch_bytes);
+    }
+    return need;
+  }
+  return plan_tiled(w, vectors, sm_count).scratch_bytes;
+}
+
 cudaError_t launch_qlinear_tiled(const TiledWeight& w, const float* x, int64_t vectors, const float* bias,
+                                 const float* residual, int epilogue, float* out, void* scratch, DeviceStatus* status,
+                                 int sm_count, cudaStream_t stream, int* launches) {
+  if (w.layout == kLayoutUmma128) {
+    // the xh8 region is sized for the widest pass of this call
+    size_t xh_region = 0;
+    for (int64_t v0 = 0; v0 < vectors; v0 += 256)
+      xh_region = std::max(xh_region, umma_xh_region(plan_umma(w, std::min<int64_t>(256, vectors - v0), sm_count)));
+    return launch_qlinear_umma(w, x, vectors, bias, residual, epilogue, out, reinterpret_cast<__half*>(scratch),
+                               reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + xh_region), status, sm_count, stream,
+                               launches);
+  }
+  return launch_qlinear_mma16(w, x, vectors, bias, residual, epilogue, out, reinterpret_cast<float*>(scratch), sm_count, stream,
+                              launches);
+}
+
+cudaError_t launch_qlinear_mma16(const TiledWeight& w, const float* x, int64_t vectors, const float* bias,
                                  const float* residual, int epilogue, float* out, float* scratch, int sm_count,
                                  cudaStream_t stream, int* launches) {
   const int out_cols = (int)(epilogue == ETC_EPILOGUE_SWIGLU ? w.rows / 2 : w.rows);
