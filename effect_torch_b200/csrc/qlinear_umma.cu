@@ -33,11 +33,24 @@ namespace etc {
 namespace {
 
 constexpr int kUmmaRows = 128;
-constexpr int kStageBlocks = 4;   // 32-value blocks per pipeline stage (128 columns = 8 MMAs of K=16)
-constexpr int kStages = 3;
-constexpr int kAColsPerStage = kStageBlocks * 16;  // 32-bit TMEM columns holding 128 f16 per lane
-constexpr int kDequantThreads = 128;
-constexpr int kThreads = 192;
+constexpr int kDequantThreads = 128;  // one TMEM lane (weight row) per thread of a dequant group
+
+// Pipeline shape per vector padding. For decode (NV = 32) the kernel is bound by how fast warps can expand
+// packed weights, so two groups of four dequant warps alternate over short stages (2 blocks) in a 6-deep
+// ring and two CTAs share an SM (256 TMEM columns each); for wide passes the MMAs dominate and one group
+// with 4-block stages suffices.
+template <int NV>
+struct UmmaCfg {
+  static constexpr int kGroups = NV <= 32 ? 2 : 1;
+  static constexpr int kStageBlocks = NV <= 32 ? 2 : 4;   // 32-value blocks per stage (K = 16 per MMA: 2 MMAs per block)
+  static constexpr int kStages = NV <= 32 ? 6 : 3;
+  static constexpr int kAColsPerStage = kStageBlocks * 16;  // 32-bit TMEM columns holding the stage's f16 per lane
+  static constexpr int kThreads = (4 * kGroups + 2) * 32;  // dequant warps + bulk-copy warp + MMA warp
+  static constexpr uint32_t kStageBBytes = NV * kStageBlocks * 32 * 2;
+  static constexpr uint32_t kTmemCols = NV + kStages * kAColsPerStage <= 256 ? 256 : 512;
+  static constexpr size_t kSmemBytes = (size_t)kStages * kStageBBytes + (3 * kStages + 1) * sizeof(uint64_t) + 16;
+};
+constexpr int stage_blocks_for(int nv) { return nv <= 32 ? 2 : 4; }
 constexpr unsigned kSpinLimit = 1u << 24;  // bounded mbarrier waits (a stage takes microseconds)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -166,10 +179,13 @@ struct UmmaArgs {
 };
 
 template <int CODEC, int NV>
-__global__ void __launch_bounds__(kThreads) qlinear_umma_kernel(UmmaArgs a) {
+__global__ void __launch_bounds__(UmmaCfg<NV>::kThreads) qlinear_umma_kernel(UmmaArgs a) {
+  using Cfg = UmmaCfg<NV>;
+  constexpr int kGroups = Cfg::kGroups, kStageBlocks = Cfg::kStageBlocks, kStages = Cfg::kStages;
+  constexpr int kAColsPerStage = Cfg::kAColsPerStage;
   constexpr int QW = CODEC == 2 ? 1 : 2;                    // uint4 words per (row, block)
-  constexpr uint32_t kStageBBytes = NV * 128 * 2;           // one stage of activations
-  constexpr uint32_t kTmemCols = NV + kStages * kAColsPerStage <= 256 ? 256 : 512;
+  constexpr uint32_t kStageBBytes = Cfg::kStageBBytes;      // one stage of activations
+  constexpr uint32_t kTmemCols = Cfg::kTmemCols;
   constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(NV >> 3) << 17) | ((uint32_t)(kUmmaRows >> 4) << 24);  // f16 x f16 -> f32
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* b_ring = smem;                                            // kStages * kStageBBytes
@@ -205,13 +221,15 @@ __global__ void __launch_bounds__(kThreads) qlinear_umma_kernel(UmmaArgs a) {
   const uint32_t d_tmem = tmem_base;             // columns [0, NV)
   const uint32_t a_tmem0 = tmem_base + NV;       // stage s at columns NV + s*kAColsPerStage
 
-  if (warp < 4) {
+  if (warp < 4 * kGroups) {
     // ------------------------------------------------------------------ dequant warps
-    const int row = threadIdx.x;  // TMEM lane == row inside the tile
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    // group g = warp / 4 expands stages g, g + kGroups, ...; inside a group warp w owns TMEM lanes 32*(w%4)...
+    const int group = warp >> 2;
+    const int row = (warp & 3) * 32 + lane;  // TMEM lane == row inside the tile
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const uint4* qrow = a.quants + ((size_t)tile * a.kblocks) * (kUmmaRows * QW) + (size_t)row * QW;
     const __half* srow = a.scales + ((size_t)tile * a.kblocks) * kUmmaRows + row;
-    constexpr int PF = 2;  // stages of packed weights held in registers ahead of use
+    constexpr int PF = NV <= 32 ? 4 : 2;  // of this group's stages, held packed in registers ahead of use
     uint4 qbuf[PF][kStageBlocks][QW];
     __half sbuf[PF][kStageBlocks];
     auto load_stage = [&](int stage_index, int slot) {
@@ -223,15 +241,17 @@ __global__ void __launch_bounds__(kThreads) qlinear_umma_kernel(UmmaArgs a) {
         sbuf[slot][b] = __ldg(srow + (size_t)kb * kUmmaRows);
       }
     };
+    const int my_stages = nstages > group ? (nstages - group + kGroups - 1) / kGroups : 0;
 #pragma unroll
     for (int p = 0; p < PF; ++p)
-      if (p < nstages) load_stage(p, p);
+      if (p < my_stages) load_stage(group + p * kGroups, p);
     bool ok = true;
-    for (int i0 = 0; i0 < nstages && ok; i0 += PF) {
+    for (int j0 = 0; j0 < my_stages && ok; j0 += PF) {
 #pragma unroll
       for (int p = 0; p < PF; ++p) {
-        const int i = i0 + p;
-        if (i >= nstages || !ok) break;
+        const int j = j0 + p;
+        if (j >= my_stages || !ok) break;
+        const int i = group + j * kGroups;  // global stage index
         const int s = i % kStages;
         const uint32_t round = (uint32_t)(i / kStages);
         // the MMAs that read this TMEM stage in the previous round must have retired
@@ -256,13 +276,14 @@ __global__ void __launch_bounds__(kThreads) qlinear_umma_kernel(UmmaArgs a) {
           }
           tmem_st16(a_tmem0 + lane_base + (uint32_t)(s * kAColsPerStage + b * 16), regs);
         }
-        if (i + PF < nstages) load_stage(i + PF, p);  // refill this register slot
+        if (j + PF < my_stages) load_stage(group + (j + PF) * kGroups, p);  // refill this register slot
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(&full_a[s]);
       }
     }
-    // ------------------------------------------------------------------ epilogue
+    // ------------------------------------------------------------------ epilogue (first group)
+    if (group != 0) ok = false;
     if (ok) ok = mbar_wait(done, 0, abort_flag);
     if (ok) {
       tc_fence_after();
@@ -300,7 +321,7 @@ __global__ void __launch_bounds__(kThreads) qlinear_umma_kernel(UmmaArgs a) {
       }
     }
     tc_fence_before();
-  } else if (warp == 4) {
+  } else if (warp == 4 * kGroups) {
     // ------------------------------------------------------------------ activation loader (one lane)
     if (lane == 0) {
       int issued = 0;
@@ -428,7 +449,7 @@ __global__ void repack_umma_kernel(RepackParts parts, int codec, int64_t rows, i
 
 template <int CODEC, int NV>
 cudaError_t launch_umma_pass(const UmmaArgs& args, int tiles, int splits, cudaStream_t stream) {
-  constexpr size_t smem = (size_t)kStages * NV * 128 * 2 + (3 * kStages + 1) * sizeof(uint64_t) + 16;
+  constexpr size_t smem = UmmaCfg<NV>::kSmemBytes;
   auto kernel = qlinear_umma_kernel<CODEC, NV>;
   static bool configured = false;
   if (!configured) {
@@ -436,7 +457,7 @@ cudaError_t launch_umma_pass(const UmmaArgs& args, int tiles, int splits, cudaSt
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  kernel<<<dim3((unsigned)tiles, (unsigned)splits), kThreads, smem, stream>>>(args);
+  kernel<<<dim3((unsigned)tiles, (unsigned)splits), UmmaCfg<NV>::kThreads, smem, stream>>>(args);
   return cudaGetLastError();
 }
 
@@ -459,6 +480,7 @@ UmmaPlan plan_umma(const TiledWeight& w, int64_t vectors, int sm_count) {
   p.nv = umma_vector_pad(chunk);
   p.tiles = (int)(w.rows_padded / kUmmaRows);
   const int kblocks = (int)(w.columns / 32);
+  const int kStageBlocks = stage_blocks_for(p.nv);
   const int stages = (kblocks + kStageBlocks - 1) / kStageBlocks;
   const int ctas_per_sm = p.nv <= 32 ? 2 : 1;
   const int target = std::max(1, sm_count) * ctas_per_sm;
