@@ -50,6 +50,9 @@ struct etc_decoder {
   float *hidden = nullptr, *normed = nullptr, *qkv = nullptr, *qh = nullptr, *kh = nullptr, *vh = nullptr, *qr = nullptr,
         *kr = nullptr, *att = nullptr, *attl = nullptr, *proj = nullptr, *g = nullptr, *u = nullptr, *act = nullptr,
         *last = nullptr, *logits = nullptr;
+  // f16 activation hand-off between kernels of the one-token fast path ([K/8][32][8] order, rows >= batch stay zero)
+  __half *xh_norm = nullptr, *xh_att = nullptr, *xh_act = nullptr;
+  bool xh_path = false;
   float* lin_scratch = nullptr;
   size_t lin_scratch_bytes = 0;
   float* attn_scratch = nullptr;
@@ -172,12 +175,12 @@ struct StepContext {
 
 // out = x W^T (+ epilogue) for one projection, choosing the tensor-core tiling when it exists.
 etc_status run_linear(StepContext& s, const BoundWeight& raw, etc_qweight* tiled_w, const float* x, int64_t vectors, float* out,
-                      int epilogue, const float* residual) {
+                      int epilogue, const float* residual, const __half* xh_ready = nullptr, __half* out_xh = nullptr) {
   etc_decoder* d = s.dec;
   cudaStream_t stream = d->rt->stream;
   if (tiled_w) {
     ETC_CUDA(launch_qlinear_tiled(tiled_w->tiled, x, vectors, nullptr, residual, epilogue, out, d->lin_scratch,
-                                  d->rt->d_status, d->rt->sm_count, stream, &s.launches));
+                                  d->rt->d_status, d->rt->sm_count, stream, &s.launches, xh_ready, out_xh));
     return ETC_OK;
   }
   float* target = epilogue == ETC_EPILOGUE_RESIDUAL ? d->proj : out;
@@ -218,12 +221,15 @@ etc_status enqueue_step(StepContext& s) {
   for (int l = 0; l < c.layers; ++l) {
     const size_t li = (size_t)l;
     const PoolView view = s.pool->view(l);
-    ETC_CUDA(launch_rmsnorm(d->hidden, (const float*)d->attn_norm[li].d_raw, c.rms_eps, rows, c.d_model, d->normed, stream));
+    // one-token steps of a tiled model hand activations from kernel to kernel as f16 in the tensor-core operand order
+    const bool xh = d->xh_path && T == 1;
+    if (xh) ETC_CUDA(launch_rmsnorm_xh8(d->hidden, (const float*)d->attn_norm[li].d_raw, c.rms_eps, rows, c.d_model, d->xh_norm, stream));
+    else ETC_CUDA(launch_rmsnorm(d->hidden, (const float*)d->attn_norm[li].d_raw, c.rms_eps, rows, c.d_model, d->normed, stream));
     ++s.launches;
     const float *qp, *kp, *vp;
     int64_t stride_q, stride_kv;
     if (d->tiled) {
-      ETC_TRY(run_linear(s, d->wq[li], d->t_qkv[li], d->normed, rows, d->qkv, ETC_EPILOGUE_NONE, nullptr));
+      ETC_TRY(run_linear(s, d->wq[li], d->t_qkv[li], d->normed, rows, d->qkv, ETC_EPILOGUE_NONE, nullptr, xh ? d->xh_norm : nullptr));
       qp = d->qkv; kp = d->qkv + qw; vp = d->qkv + qw + kvw;
       stride_q = stride_kv = qkvw;
     } else {
@@ -242,7 +248,7 @@ etc_status enqueue_step(StepContext& s) {
       ++s.launches;
       const AttnPlan plan = plan_attention(B, Hq, Hkv, D, std::max(1, s.max_pages), d->rt->sm_count);
       ETC_CUDA(launch_attention_mma(view, d->qr, d->d_lanes, d->d_tables, B, Hq, scale, c.window, d->attl, plan,
-                                    d->attn_scratch, stream, &s.launches));
+                                    d->attn_scratch, stream, &s.launches, xh ? d->xh_att : nullptr));
     } else {
       ETC_CUDA(launch_heads_first(qp, d->qh, B, T, Hq, D, stride_q, stream));
       ETC_CUDA(launch_heads_first(kp, d->kh, B, T, Hkv, D, stride_kv, stream));
@@ -255,20 +261,27 @@ etc_status enqueue_step(StepContext& s) {
       ETC_CUDA(launch_heads_last(d->att, d->attl, B, T, Hq, D, stream));
       s.launches += 8;
     }
-    ETC_TRY(run_linear(s, d->wo[li], d->tiled ? d->t_o[li] : nullptr, d->attl, rows, d->hidden, ETC_EPILOGUE_RESIDUAL, d->hidden));
-    ETC_CUDA(launch_rmsnorm(d->hidden, (const float*)d->ffn_norm[li].d_raw, c.rms_eps, rows, c.d_model, d->normed, stream));
+    const bool xh_o = xh && fast_attention;
+    ETC_TRY(run_linear(s, d->wo[li], d->tiled ? d->t_o[li] : nullptr, d->attl, rows, d->hidden, ETC_EPILOGUE_RESIDUAL, d->hidden,
+                       xh_o ? d->xh_att : nullptr));
+    if (xh) ETC_CUDA(launch_rmsnorm_xh8(d->hidden, (const float*)d->ffn_norm[li].d_raw, c.rms_eps, rows, c.d_model, d->xh_norm, stream));
+    else ETC_CUDA(launch_rmsnorm(d->hidden, (const float*)d->ffn_norm[li].d_raw, c.rms_eps, rows, c.d_model, d->normed, stream));
     ++s.launches;
     if (d->tiled) {
-      ETC_TRY(run_linear(s, d->gate[li], d->t_gu[li], d->normed, rows, d->act, ETC_EPILOGUE_SWIGLU, nullptr));
+      ETC_TRY(run_linear(s, d->gate[li], d->t_gu[li], d->normed, rows, xh ? nullptr : d->act, ETC_EPILOGUE_SWIGLU, nullptr,
+                         xh ? d->xh_norm : nullptr, xh ? d->xh_act : nullptr));
     } else {
       ETC_TRY(run_linear(s, d->gate[li], nullptr, d->normed, rows, d->g, ETC_EPILOGUE_NONE, nullptr));
       ETC_TRY(run_linear(s, d->up[li], nullptr, d->normed, rows, d->u, ETC_EPILOGUE_NONE, nullptr));
       ETC_CUDA(launch_swiglu(d->g, d->u, rows * c.ffn, d->act, c.exact, stream));
       ++s.launches;
     }
-    ETC_TRY(run_linear(s, d->down[li], d->tiled ? d->t_down[li] : nullptr, d->act, rows, d->hidden, ETC_EPILOGUE_RESIDUAL, d->hidden));
+    ETC_TRY(run_linear(s, d->down[li], d->tiled ? d->t_down[li] : nullptr, d->act, rows, d->hidden, ETC_EPILOGUE_RESIDUAL, d->hidden,
+                       xh ? d->xh_act : nullptr));
   }
-  ETC_CUDA(launch_rmsnorm(d->hidden, (const float*)d->out_norm.d_raw, c.rms_eps, rows, c.d_model, d->normed, stream));
+  const bool xh_head = d->xh_path && T == 1;
+  if (xh_head) ETC_CUDA(launch_rmsnorm_xh8(d->hidden, (const float*)d->out_norm.d_raw, c.rms_eps, rows, c.d_model, d->xh_norm, stream));
+  else ETC_CUDA(launch_rmsnorm(d->hidden, (const float*)d->out_norm.d_raw, c.rms_eps, rows, c.d_model, d->normed, stream));
   ++s.launches;
   // LastTokenRow then the head: only the selected row of each lane reaches the head projection
   // (each head output is an independent dot product, so the result equals projecting all rows first).
@@ -278,7 +291,8 @@ etc_status enqueue_step(StepContext& s) {
     ++s.launches;
     head_in = d->last;
   }
-  ETC_TRY(run_linear(s, d->head, d->tiled ? d->t_head : nullptr, head_in, B, d->logits, ETC_EPILOGUE_NONE, nullptr));
+  ETC_TRY(run_linear(s, d->head, d->tiled ? d->t_head : nullptr, head_in, B, d->logits, ETC_EPILOGUE_NONE, nullptr,
+                     xh_head ? d->xh_norm : nullptr));
   ETC_CUDA(launch_argmax(d->logits, B, c.vocab, d->d_tokens, d->rt->d_status, stream));
   ++s.launches;
   return ETC_OK;
@@ -596,6 +610,17 @@ etc_status etc_decoder_finalize(etc_decoder* dec) {
           need = std::max(need, tiled_scratch_bytes(w->tiled, std::min<int64_t>(v, (int64_t)R), rt->sm_count));
     for (int64_t v : probes)
       need = std::max(need, tiled_scratch_bytes(dec->t_head->tiled, std::min<int64_t>(v, c.batch), rt->sm_count));
+    dec->xh_path = c.batch <= 32 && c.d_model % 8 == 0 && c.ffn % 8 == 0 && (c.q_heads * c.head_dim) % 8 == 0 &&
+                   c.d_model <= 8192 && dec->t_head->tiled.layout == kLayoutUmma128;
+    if (dec->xh_path) {
+      ETC_TRY(dalloc(dec, &dec->xh_norm, (size_t)c.d_model * 32));
+      ETC_TRY(dalloc(dec, &dec->xh_att, qw * 32));
+      ETC_TRY(dalloc(dec, &dec->xh_act, (size_t)c.ffn * 32));
+      ETC_CUDA(cudaMemsetAsync(dec->xh_norm, 0, (size_t)c.d_model * 32 * sizeof(__half), rt->stream));
+      ETC_CUDA(cudaMemsetAsync(dec->xh_att, 0, qw * 32 * sizeof(__half), rt->stream));
+      ETC_CUDA(cudaMemsetAsync(dec->xh_act, 0, (size_t)c.ffn * 32 * sizeof(__half), rt->stream));
+      ETC_CUDA(cudaStreamSynchronize(rt->stream));
+    }
     dec->lin_scratch_bytes = need;
     if (need) ETC_TRY(dalloc(dec, &dec->lin_scratch, need / sizeof(float)));
     // split-KV partials: the split count never exceeds the plan for the longest possible table
@@ -631,7 +656,8 @@ etc_status etc_decoder_destroy(etc_decoder* dec) {
   destroy_qweight(dec->t_head);
   for (void* p : {(void*)dec->d_inv_freq, (void*)dec->hidden, (void*)dec->normed, (void*)dec->qkv, (void*)dec->qh, (void*)dec->kh,
                   (void*)dec->vh, (void*)dec->qr, (void*)dec->kr, (void*)dec->att, (void*)dec->attl, (void*)dec->proj, (void*)dec->g,
-                  (void*)dec->u, (void*)dec->act, (void*)dec->last, (void*)dec->logits, (void*)dec->lin_scratch,
+                  (void*)dec->u, (void*)dec->act, (void*)dec->last, (void*)dec->logits, (void*)dec->lin_scratch, (void*)dec->xh_norm,
+                  (void*)dec->xh_att, (void*)dec->xh_act,
                   (void*)dec->attn_scratch, (void*)dec->exact_scratch, (void*)dec->d_ids, (void*)dec->d_cursors, (void*)dec->d_tokens,
                   (void*)dec->d_history, (void*)dec->d_step_counter, (void*)dec->d_lanes, (void*)dec->d_tables})
     if (p) rt->device_free(p);

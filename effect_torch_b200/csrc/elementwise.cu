@@ -88,10 +88,77 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const float* __restrict__ 
   }
 }
 
+// Single-pass variant for n <= 8192, n % 4 == 0: the row stays in registers between the reduction and the
+// scaling (same f64 arithmetic). XH = true stores the result as f16 in [n/8][32][8] order (row < 32), the
+// B-operand layout of the tcgen05 linear, instead of f32 row-major.
+template <bool XH>
+__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ weight,
+                                                           double eps, int n, float* __restrict__ out, __half* __restrict__ out_xh) {
+  __shared__ double partial[8];
+  __shared__ double scale_s;
+  const int row = blockIdx.x;
+  const float4* src = reinterpret_cast<const float4*>(x + (size_t)row * n);
+  const int chunks = n / 4;
+  float4 v[8];
+  double sum = 0.0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int c = threadIdx.x + 256 * j;
+    v[j] = c < chunks ? src[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    sum += (double)v[j].x * (double)v[j].x + (double)v[j].y * (double)v[j].y + (double)v[j].z * (double)v[j].z +
+           (double)v[j].w * (double)v[j].w;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+  if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = sum;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double total = 0.0;
+    for (int i = 0; i < 8; ++i) total += partial[i];
+    scale_s = 1.0 / sqrt(total / (double)n + eps);
+  }
+  __syncthreads();
+  const double scale = scale_s;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int c = threadIdx.x + 256 * j;
+    if (c >= chunks) continue;
+    float4 w = weight ? reinterpret_cast<const float4*>(weight)[c] : make_float4(1.f, 1.f, 1.f, 1.f);
+    const float r0 = (float)__dmul_rn(__dmul_rn((double)v[j].x, scale), (double)w.x);
+    const float r1 = (float)__dmul_rn(__dmul_rn((double)v[j].y, scale), (double)w.y);
+    const float r2 = (float)__dmul_rn(__dmul_rn((double)v[j].z, scale), (double)w.z);
+    const float r3 = (float)__dmul_rn(__dmul_rn((double)v[j].w, scale), (double)w.w);
+    if (XH) {
+      auto sat = [](float f) { return fminf(fmaxf(f, -65504.f), 65504.f); };
+      __half2 h01 = __floats2half2_rn(sat(r0), sat(r1)), h23 = __floats2half2_rn(sat(r2), sat(r3));
+      const int k = 4 * c;
+      uint2 packed = make_uint2(*reinterpret_cast<uint32_t*>(&h01), *reinterpret_cast<uint32_t*>(&h23));
+      *reinterpret_cast<uint2*>(out_xh + ((size_t)(k >> 3) * 32 + row) * 8 + (k & 7)) = packed;
+    } else {
+      reinterpret_cast<float4*>(out + (size_t)row * n)[c] = make_float4(r0, r1, r2, r3);
+    }
+  }
+}
+
+static bool rmsnorm_fast_ok(const float* x, const float* weight, int64_t n) {
+  return n % 4 == 0 && n <= 8192 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)weight % 16) == 0;
+}
+
 cudaError_t launch_rmsnorm(const float* x, const float* weight, double eps, int64_t rows, int64_t n, float* out,
                            cudaStream_t stream) {
   if (rows == 0) return cudaSuccess;
-  rmsnorm_kernel<<<(unsigned)rows, 256, 0, stream>>>(x, weight, eps, n, out);
+  if (rmsnorm_fast_ok(x, weight, n) && ((uintptr_t)out % 16) == 0)
+    rmsnorm_rows_kernel<false><<<(unsigned)rows, 256, 0, stream>>>(x, weight, eps, (int)n, out, nullptr);
+  else
+    rmsnorm_kernel<<<(unsigned)rows, 256, 0, stream>>>(x, weight, eps, n, out);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_rmsnorm_xh8(const float* x, const float* weight, double eps, int64_t rows, int64_t n, __half* out_xh,
+                               cudaStream_t stream) {
+  if (rows == 0) return cudaSuccess;
+  if (rows > 32 || n % 8 != 0 || !rmsnorm_fast_ok(x, weight, n)) return cudaErrorInvalidValue;
+  rmsnorm_rows_kernel<true><<<(unsigned)rows, 256, 0, stream>>>(x, weight, eps, (int)n, nullptr, out_xh);
   return cudaGetLastError();
 }
 

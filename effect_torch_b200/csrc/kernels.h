@@ -54,8 +54,10 @@ TiledPlan plan_tiled(const TiledWeight& w, int64_t vectors, int sm_count);
 cudaError_t launch_qlinear_mma16(const TiledWeight& w, const float* x, int64_t vectors, const float* bias,
                                  const float* residual, int epilogue, float* out, float* scratch, int sm_count,
                                  cudaStream_t stream, int* launches);
+// out_xh (optional, vectors <= 32): the result also stored as f16 in [cols/8][32][8] order for the next linear.
 cudaError_t launch_qlinear_reduce(const float* scratch, int splits, int vpad, int vectors, int rows, int rows_padded,
-                                  const float* bias, const float* residual, int epilogue, float* out, cudaStream_t stream);
+                                  const float* bias, const float* residual, int epilogue, float* out, __half* out_xh,
+                                  cudaStream_t stream);
 
 // tcgen05 path (qlinear_umma.cu)
 struct UmmaPlan {
@@ -66,15 +68,21 @@ struct UmmaPlan {
 };
 UmmaPlan plan_umma(const TiledWeight& w, int64_t vectors, int sm_count);
 cudaError_t launch_repack_umma(const TiledWeight& w, const RepackParts& parts, cudaStream_t stream);
-cudaError_t launch_qlinear_umma(const TiledWeight& w, const float* x, int64_t vectors, const float* bias, const float* residual,
-                                int epilogue, float* out, __half* xh, float* scratch, DeviceStatus* status, int sm_count,
-                                cudaStream_t stream, int* launches);
+// x: f32 [vectors, K], converted to xh8 into `xh` first — unless xh_ready (already [K/8][32][8] f16, vectors <= 32) is given.
+cudaError_t launch_qlinear_umma(const TiledWeight& w, const float* x, const __half* xh_ready, int64_t vectors, const float* bias,
+                                const float* residual, int epilogue, float* out, __half* out_xh, __half* xh, float* scratch,
+                                DeviceStatus* status, int sm_count, cudaStream_t stream, int* launches);
 
 // Layout-independent front end. `scratch` must hold tiled_scratch_bytes(w, vectors, sm_count).
 size_t tiled_scratch_bytes(const TiledWeight& w, int64_t vectors, int sm_count);
+// xh_ready / out_xh: optional f16 activation hand-off between linears (tcgen05 layout only, vectors <= 32).
 cudaError_t launch_qlinear_tiled(const TiledWeight& w, const float* x, int64_t vectors, const float* bias,
                                  const float* residual, int epilogue, float* out, void* scratch, DeviceStatus* status,
-                                 int sm_count, cudaStream_t stream, int* launches);
+                                 int sm_count, cudaStream_t stream, int* launches, const __half* xh_ready = nullptr,
+                                 __half* out_xh = nullptr);
+// RMSNorm whose output is stored as xh8 f16 [n/8][32][8] (rows <= 32); out_f32 optional.
+cudaError_t launch_rmsnorm_xh8(const float* x, const float* weight, double eps, int64_t rows, int64_t n, __half* out_xh,
+                               cudaStream_t stream);
 
 // ---- dense / elementwise (elementwise.cu) --------------------------------------------------
 cudaError_t launch_linear_f32(const float* x, int64_t m, int64_t k, const float* w, int64_t n, const float* bias,
@@ -136,7 +144,8 @@ size_t plan_attention_max_scratch(int batch, int q_heads, int kv_heads, int head
 bool attention_mma_supported(const PoolView& pool, int q_heads, int tokens);
 cudaError_t launch_attention_mma(const PoolView& pool, const float* q, const LaneInfo* lanes, const int* tables,
                                  int batch, int q_heads, double scale, long long op_window, float* out,
-                                 const AttnPlan& plan, float* scratch, cudaStream_t stream, int* launches);
+                                 const AttnPlan& plan, float* scratch, cudaStream_t stream, int* launches,
+                                 __half* out_xh = nullptr);
 // Fused RoPE(q), RoPE(k) and KV append for one-token steps: qkv [B, (Hq+2*Hkv)*D] f32 (the fused
 // projection output) -> q_out [B,Hq,D] f32 rotated, K/V rows written to the pool.
 cudaError_t launch_rope_append(const PoolView& pool, const float* qkv, const LaneInfo* lanes, const int* tables,

@@ -41,16 +41,16 @@ constexpr int kDequantThreads = 128;  // one TMEM lane (weight row) per thread o
 // with 4-block stages suffices.
 template <int NV>
 struct UmmaCfg {
-  static constexpr int kGroups = NV <= 32 ? 2 : 1;
-  static constexpr int kStageBlocks = NV <= 32 ? 2 : 4;   // 32-value blocks per stage (K = 16 per MMA: 2 MMAs per block)
-  static constexpr int kStages = NV <= 32 ? 6 : 3;
+  static constexpr int kGroups = 1;
+  static constexpr int kStageBlocks = 4;   // 32-value blocks per stage (K = 16 per MMA: 2 MMAs per block)
+  static constexpr int kStages = 3;
   static constexpr int kAColsPerStage = kStageBlocks * 16;  // 32-bit TMEM columns holding the stage's f16 per lane
   static constexpr int kThreads = (4 * kGroups + 2) * 32;  // dequant warps + bulk-copy warp + MMA warp
   static constexpr uint32_t kStageBBytes = NV * kStageBlocks * 32 * 2;
   static constexpr uint32_t kTmemCols = NV + kStages * kAColsPerStage <= 256 ? 256 : 512;
   static constexpr size_t kSmemBytes = (size_t)kStages * kStageBBytes + (3 * kStages + 1) * sizeof(uint64_t) + 16;
 };
-constexpr int stage_blocks_for(int nv) { return nv <= 32 ? 2 : 4; }
+constexpr int stage_blocks_for(int) { return 4; }
 constexpr unsigned kSpinLimit = 1u << 24;  // bounded mbarrier waits (a stage takes microseconds)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -175,6 +175,8 @@ struct UmmaArgs {
   float* out;
   float* scratch;         // [splits][NV][rows_padded]
   unsigned long long* status;
+  __half* out_xh;         // optional: result additionally stored as xh8 f16 [cols/8][out_xh_nv][8] for the next linear
+  int out_xh_nv;
   int vectors, rows, rows_padded, kblocks, blocks_per_split, epilogue;
 };
 
@@ -229,7 +231,7 @@ __global__ void __launch_bounds__(UmmaCfg<NV>::kThreads) qlinear_umma_kernel(Umm
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const uint4* qrow = a.quants + ((size_t)tile * a.kblocks) * (kUmmaRows * QW) + (size_t)row * QW;
     const __half* srow = a.scales + ((size_t)tile * a.kblocks) * kUmmaRows + row;
-    constexpr int PF = NV <= 32 ? 4 : 2;  // of this group's stages, held packed in registers ahead of use
+    constexpr int PF = 2;  // of this group's stages, held packed in registers ahead of use
     uint4 qbuf[PF][kStageBlocks][QW];
     __half sbuf[PF][kStageBlocks];
     auto load_stage = [&](int stage_index, int slot) {
@@ -246,6 +248,9 @@ __global__ void __launch_bounds__(UmmaCfg<NV>::kThreads) qlinear_umma_kernel(Umm
     for (int p = 0; p < PF; ++p)
       if (p < my_stages) load_stage(group + p * kGroups, p);
     bool ok = true;
+    // Software pipeline: stage j is expanded in registers while the TMEM stores of stage j-1 are still in
+    // flight; only then are those stores awaited and published, so the store latency hides behind ALU work.
+    int pending_slot = -1;
     for (int j0 = 0; j0 < my_stages && ok; j0 += PF) {
 #pragma unroll
       for (int p = 0; p < PF; ++p) {
@@ -254,33 +259,43 @@ __global__ void __launch_bounds__(UmmaCfg<NV>::kThreads) qlinear_umma_kernel(Umm
         const int i = group + j * kGroups;  // global stage index
         const int s = i % kStages;
         const uint32_t round = (uint32_t)(i / kStages);
+        const int valid = min(kStageBlocks, kb1 - (kb0 + i * kStageBlocks));
+        uint32_t regs[kStageBlocks][16];
+#pragma unroll
+        for (int b = 0; b < kStageBlocks; ++b) {
+          const __half2 sc = __half2half2(b < valid ? sbuf[p][b] : __float2half_rn(0.0f));
+          if (CODEC == 2) {
+            const uint4 q = qbuf[p][b][0];
+            expand_q4(q.x, sc, regs[b] + 0);
+            expand_q4(q.y, sc, regs[b] + 4);
+            expand_q4(q.z, sc, regs[b] + 8);
+            expand_q4(q.w, sc, regs[b] + 12);
+          } else {
+            const uint4 q0 = qbuf[p][b][0], q1 = qbuf[p][b][QW - 1];
+            expand_q8(q0.x, sc, regs[b] + 0); expand_q8(q0.y, sc, regs[b] + 2); expand_q8(q0.z, sc, regs[b] + 4); expand_q8(q0.w, sc, regs[b] + 6);
+            expand_q8(q1.x, sc, regs[b] + 8); expand_q8(q1.y, sc, regs[b] + 10); expand_q8(q1.z, sc, regs[b] + 12); expand_q8(q1.w, sc, regs[b] + 14);
+          }
+        }
+        if (j + PF < my_stages) load_stage(group + (j + PF) * kGroups, p);  // refill this register slot
+        if (pending_slot >= 0) {  // publish the previous stage of this group
+          tmem_wait_st();
+          tc_fence_before();
+          mbar_arrive(&full_a[pending_slot]);
+        }
         // the MMAs that read this TMEM stage in the previous round must have retired
         ok = mbar_wait(&empty[s], (round & 1) ^ 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
-        const int valid = min(kStageBlocks, kb1 - (kb0 + i * kStageBlocks));
 #pragma unroll
-        for (int b = 0; b < kStageBlocks; ++b) {
-          uint32_t regs[16];
-          const __half2 sc = __half2half2(b < valid ? sbuf[p][b] : __float2half_rn(0.0f));
-          if (CODEC == 2) {
-            const uint4 q = qbuf[p][b][0];
-            expand_q4(q.x, sc, regs + 0);
-            expand_q4(q.y, sc, regs + 4);
-            expand_q4(q.z, sc, regs + 8);
-            expand_q4(q.w, sc, regs + 12);
-          } else {
-            const uint4 q0 = qbuf[p][b][0], q1 = qbuf[p][b][QW - 1];
-            expand_q8(q0.x, sc, regs + 0); expand_q8(q0.y, sc, regs + 2); expand_q8(q0.z, sc, regs + 4); expand_q8(q0.w, sc, regs + 6);
-            expand_q8(q1.x, sc, regs + 8); expand_q8(q1.y, sc, regs + 10); expand_q8(q1.z, sc, regs + 12); expand_q8(q1.w, sc, regs + 14);
-          }
-          tmem_st16(a_tmem0 + lane_base + (uint32_t)(s * kAColsPerStage + b * 16), regs);
-        }
-        if (j + PF < my_stages) load_stage(group + (j + PF) * kGroups, p);  // refill this register slot
-        tmem_wait_st();
-        tc_fence_before();
-        mbar_arrive(&full_a[s]);
+        for (int b = 0; b < kStageBlocks; ++b)
+          tmem_st16(a_tmem0 + lane_base + (uint32_t)(s * kAColsPerStage + b * 16), regs[b]);
+        pending_slot = s;
       }
+    }
+    if (ok && pending_slot >= 0) {
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&full_a[pending_slot]);
     }
     // ------------------------------------------------------------------ epilogue (first group)
     if (group != 0) ok = false;
@@ -305,8 +320,13 @@ __global__ void __launch_bounds__(UmmaCfg<NV>::kThreads) qlinear_umma_kernel(Umm
           for (int v = 0; v < 32; ++v) {
             const float mine = __uint_as_float(acc[v]) + bias_v;
             const float partner = __shfl_xor_sync(0xffffffffu, mine, 8);
-            if ((r & 8) == 0 && r + 8 < a.rows && c0 + v < a.vectors)
-              a.out[(size_t)(c0 + v) * (a.rows / 2) + oc] = silu_tanh(mine) * partner;
+            if ((r & 8) == 0 && r + 8 < a.rows && c0 + v < a.vectors) {
+              const float act = silu_tanh(mine) * partner;
+              if (a.out) a.out[(size_t)(c0 + v) * (a.rows / 2) + oc] = act;
+              if (a.out_xh)
+                a.out_xh[((size_t)(oc >> 3) * a.out_xh_nv + (c0 + v)) * 8 + (oc & 7)] =
+                    __float2half_rn(fminf(fmaxf(act, -65504.f), 65504.f));
+            }
           }
         } else if (r < a.rows) {
           const float bias_v = a.bias ? a.bias[r] : 0.0f;
@@ -495,12 +515,9 @@ UmmaPlan plan_umma(const TiledWeight& w, int64_t vectors, int sm_count) {
 }
 
 // qlinear_reduce_kernel lives in quant_kernels.cu
-cudaError_t launch_qlinear_reduce(const float* scratch, int splits, int vpad, int vectors, int rows, int rows_padded,
-                                  const float* bias, const float* residual, int epilogue, float* out, cudaStream_t stream);
-
-cudaError_t launch_qlinear_umma(const TiledWeight& w, const float* x, int64_t vectors, const float* bias, const float* residual,
-                                int epilogue, float* out, __half* xh, float* scratch, DeviceStatus* status, int sm_count,
-                                cudaStream_t stream, int* launches) {
+cudaError_t launch_qlinear_umma(const TiledWeight& w, const float* x, const __half* xh_ready, int64_t vectors, const float* bias,
+                                const float* residual, int epilogue, float* out, __half* out_xh, __half* xh, float* scratch,
+                                DeviceStatus* status, int sm_count, cudaStream_t stream, int* launches) {
   const int out_cols = (int)(epilogue == ETC_EPILOGUE_SWIGLU ? w.rows / 2 : w.rows);
   for (int64_t v0 = 0; v0 < vectors; v0 += 256) {
     const int64_t chunk = std::min<int64_t>(256, vectors - v0);
@@ -508,8 +525,9 @@ cudaError_t launch_qlinear_umma(const TiledWeight& w, const float* x, int64_t ve
     const int K = (int)w.columns;
     const int total = (K / 8) * plan.nv;
     const unsigned cgrid = (unsigned)std::min((total + 255) / 256, 148 * 4);
-    const float* xin = x + v0 * w.columns;
-    switch (plan.nv) {
+    const float* xin = x ? x + v0 * w.columns : nullptr;
+    const bool ready = xh_ready != nullptr && vectors <= 32;  // producer already stored xh8 with 32 padded rows
+    if (!ready) switch (plan.nv) {
       case 32: convert_xh8_kernel<32><<<cgrid, 256, 0, stream>>>(xin, (int)chunk, K, xh); break;
       case 64: convert_xh8_kernel<64><<<cgrid, 256, 0, stream>>>(xin, (int)chunk, K, xh); break;
       case 128: convert_xh8_kernel<128><<<cgrid, 256, 0, stream>>>(xin, (int)chunk, K, xh); break;
@@ -517,11 +535,13 @@ cudaError_t launch_qlinear_umma(const TiledWeight& w, const float* x, int64_t ve
     }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    if (launches) ++*launches;
+    if (launches && !ready) ++*launches;
     UmmaArgs args;
     args.quants = reinterpret_cast<const uint4*>(w.quants);
     args.scales = w.scales;
-    args.xh = xh;
+    args.xh = ready ? xh_ready : xh;
+    args.out_xh = vectors <= 32 ? out_xh : nullptr;
+    args.out_xh_nv = 32;
     args.bias = bias;
     args.residual = residual ? residual + v0 * out_cols : nullptr;
     args.out = out + v0 * out_cols;
@@ -544,7 +564,7 @@ cudaError_t launch_qlinear_umma(const TiledWeight& w, const float* x, int64_t ve
     if (launches) ++*launches;
     if (plan.splits > 1) {
       e = launch_qlinear_reduce(scratch, plan.splits, plan.nv, (int)chunk, (int)w.rows, (int)w.rows_padded, bias, args.residual,
-                                epilogue, args.out, stream);
+                                epilogue, args.out, args.out_xh, stream);
       if (e != cudaSuccess) return e;
       if (launches) ++*launches;
     }
