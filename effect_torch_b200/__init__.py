@@ -221,6 +221,16 @@ class QWeight:
         _check(self.rt.L.etc_qlinear_tiled_into(self.rt.h, self.h, _ptr(x), vectors, _ptr(bias), _ptr(residual), epilogue,
                                                 _ptr(out), _ptr(scratch), scratch_bytes))
 
+    def linear_static_into(self, x, vectors, out, bias=None, residual=None, epilogue=EPILOGUE_NONE):
+        """The same linear with its scratch in the library's fixed device array: the call allocates nothing."""
+        _check(self.rt.L.etc_qlinear_tiled_static_into(self.rt.h, self.h, _ptr(x), vectors, _ptr(bias), _ptr(residual),
+                                                       epilogue, _ptr(out)))
+
+    def static_scratch_max_bytes(self) -> int:
+        out = C.c_size_t(0)
+        _check(self.rt.L.etc_qlinear_tiled_static_max_bytes(C.byref(out)))
+        return out.value
+
 
 class NativeKvPool:
     """native-addon.ts:193-207."""

@@ -54,6 +54,8 @@ SIGNATURES = {
     "etc_qweight_shape": (None, [P, P, P, P, P]),
     "etc_qlinear_tiled_scratch_bytes": (None, [P, I64, P]),
     "etc_qlinear_tiled_into": (None, [P, P, P, I64, P, P, I, P, P, SZ]),
+    "etc_qlinear_tiled_static_max_bytes": (None, [P]),
+    "etc_qlinear_tiled_static_into": (None, [P, P, P, I64, P, P, I, P]),
     "etc_qembedding_into": (None, [P, I, P, I, I64, P, I64, I64, P]),
     "etc_linear_f32_into": (None, [P, P, I64, I64, P, I64, P, P]),
     "etc_rmsnorm_into": (None, [P, P, P, D, I64, I64, P]),

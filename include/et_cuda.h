@@ -166,6 +166,18 @@ ETC_API etc_status etc_qlinear_tiled_into(etc_runtime* rt, const etc_qweight* w,
                                           const float* d_bias, const float* d_residual, etc_epilogue epilogue,
                                           float* d_out, void* d_scratch, size_t scratch_bytes);
 
+/* The same linear with its scratch in a fixed 16 MiB device array inside the library: the call allocates nothing,
+ * neither device nor pinned memory, for callers that must not allocate while they run. No counterpart in the
+ * reference, whose backends allocate per operation. Results equal etc_qlinear_tiled_into's. A call that needs more
+ * than etc_qlinear_tiled_static_max_bytes of scratch is rejected with ETC_INVALID_ARGUMENT (the message gives both
+ * sizes). The first call on each device also looks up the array's device address, so make that first call before
+ * any stream capture begins. All calls on a device share the array: calls that overlap in time race, serialise them.
+ * Nothing in the array needs to be zero. */
+ETC_API etc_status etc_qlinear_tiled_static_max_bytes(size_t* max_bytes);
+ETC_API etc_status etc_qlinear_tiled_static_into(etc_runtime* rt, const etc_qweight* w, const float* d_x, int64_t vectors,
+                                                 const float* d_bias, const float* d_residual, etc_epilogue epilogue,
+                                                 float* d_out);
+
 /* embedding_into (quantized.rs:546-616): decode rows selected by u32/i64 indexes. An index that is
  * negative or >= rows is reported at the next synchronising call as ETC_EXECUTION
  * "quantized_embedding: index {i} is outside 0..{rows}". codec F32 gathers dense rows. */

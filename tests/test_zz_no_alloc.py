@@ -1,0 +1,66 @@
+"""The allocation-free tiled linear (scratch in the library's fixed device array) against the existing entry point.
+
+Collected last (file name) so that it also runs after every other GPU test has used the runtime's workspace."""
+import numpy as np
+import pytest
+import torch
+
+import effect_torch_b200 as et
+import oracle as orc
+from tests.golden import reference_vectors as gv
+from tests.gpu_util import dev, empty, host, runtime
+
+pytestmark = pytest.mark.gpu
+
+
+def _weight(codec, rows, columns, seed):
+    rng = np.random.default_rng(seed)
+    w = rng.normal(0, 0.02, size=(rows, columns)).astype(np.float32)
+    return orc.quantize(codec, w)
+
+
+@pytest.mark.parametrize("codec", [gv.Q4_0, gv.Q8_0])
+@pytest.mark.parametrize("rows,columns,vectors", [(512, 4096, 32), (384, 1024, 7), (1024, 2048, 300)])
+def test_static_scratch_linear_equals_the_existing_entry_point_twice_in_a_row(codec, rows, columns, vectors):
+    rt = runtime()
+    packed = _weight(codec, rows, columns, rows + vectors)
+    qw = et.QWeight(rt, codec, [dev(packed)], [rows], columns)
+    assert qw.scratch_bytes(vectors) <= qw.static_scratch_max_bytes()
+    rng = np.random.default_rng(vectors)
+    for call in range(2):  # two calls in a row share the array: the second must not see the first one's leftovers
+        x = rng.normal(size=(vectors, columns)).astype(np.float32)
+        bias = rng.normal(size=rows).astype(np.float32)
+        expected = empty((vectors, rows))
+        qw.linear_into(dev(x), vectors, expected, bias=dev(bias))
+        got = empty((vectors, rows))
+        qw.linear_static_into(dev(x), vectors, got, bias=dev(bias))
+        np.testing.assert_array_equal(host(got), host(expected), err_msg=f"call {call}")
+
+
+def test_static_scratch_linear_with_epilogues():
+    rt = runtime()
+    d, ffn, vectors = 512, 384, 32
+    pg, pu = _weight(gv.Q4_0, ffn, d, 1), _weight(gv.Q4_0, ffn, d, 2)
+    qgu = et.QWeight(rt, gv.Q4_0, [dev(pg), dev(pu)], [ffn, ffn], d, interleave8=True)
+    x = np.random.default_rng(3).normal(size=(vectors, d)).astype(np.float32)
+    expected, got = empty((vectors, ffn)), empty((vectors, ffn))
+    qgu.linear_into(dev(x), vectors, expected, epilogue=et.EPILOGUE_SWIGLU)
+    qgu.linear_static_into(dev(x), vectors, got, epilogue=et.EPILOGUE_SWIGLU)
+    np.testing.assert_array_equal(host(got), host(expected))
+    with pytest.raises(et.BackendError, match="residual"):
+        qgu.linear_static_into(dev(x), vectors, got, epilogue=et.EPILOGUE_RESIDUAL)
+
+
+def test_static_scratch_linear_rejects_calls_beyond_its_maximum():
+    rt = runtime()
+    rows, columns = 8192, 4096
+    raw = torch.zeros((rows, columns // 32 * 18), dtype=torch.uint8, device="cuda")
+    torch.cuda.synchronize()
+    qw = et.QWeight(rt, gv.Q4_0, [raw], [rows], columns)
+    limit = qw.static_scratch_max_bytes()
+    assert limit == 16 << 20
+    too_many = next((v for v in (256, 512, 1024, 4096) if qw.scratch_bytes(v) > limit), None)
+    assert too_many is not None, "no probe size exceeds the static scratch"
+    x, out = empty((too_many, columns)), empty((too_many, rows))
+    with pytest.raises(et.BackendError, match="static scratch holds"):
+        qw.linear_static_into(x, too_many, out)
