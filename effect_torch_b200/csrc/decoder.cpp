@@ -611,7 +611,7 @@ etc_status etc_decoder_finalize(etc_decoder* dec) {
     for (int64_t v : probes)
       need = std::max(need, tiled_scratch_bytes(dec->t_head->tiled, std::min<int64_t>(v, c.batch), rt->sm_count));
     dec->xh_path = c.batch <= 32 && c.d_model % 8 == 0 && c.ffn % 8 == 0 && (c.q_heads * c.head_dim) % 8 == 0 &&
-                   c.d_model <= 8192 && dec->t_head->tiled.layout == kLayoutUmma128;
+                   c.d_model <= 8192 && dec->t_head->tiled.layout != kLayoutMma16;
     if (dec->xh_path) {
       ETC_TRY(dalloc(dec, &dec->xh_norm, (size_t)c.d_model * 32));
       ETC_TRY(dalloc(dec, &dec->xh_att, qw * 32));

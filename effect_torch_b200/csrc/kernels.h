@@ -23,7 +23,8 @@ cudaError_t launch_qembedding(int codec, const void* indexes, int index_is_i64, 
 // Tiled (tensor-core) weight layout: see quant_kernels.cu for the byte map.
 enum TiledLayout : int {
   kLayoutMma16 = 0,   // 16-row tiles for the mma.sync kernel (quant_kernels.cu)
-  kLayoutUmma128 = 1  // 128-row tiles streamed per thread for the tcgen05 kernel (qlinear_umma.cu)
+  kLayoutUmma128 = 1, // 128-row tiles streamed per thread for the tcgen05 kernel (qlinear_umma.cu)
+  kLayoutStream256 = 2 // 256-row tiles, payload and scales of a block in one chunk, for the stream-K tcgen05 kernel (qlinear_stream.cu)
 };
 struct TiledWeight {
   int layout = kLayoutMma16;
@@ -35,6 +36,7 @@ struct TiledWeight {
   uint8_t* quants = nullptr;
   __half* scales = nullptr;
   size_t quant_bytes = 0, scale_bytes = 0;
+  int* counters = nullptr;  // kLayoutStream256: [rows_padded/256][4] arrival tickets, zero between launches
 };
 struct RepackParts {
   const uint8_t* ptr[4];
@@ -72,6 +74,21 @@ cudaError_t launch_repack_umma(const TiledWeight& w, const RepackParts& parts, c
 cudaError_t launch_qlinear_umma(const TiledWeight& w, const float* x, const __half* xh_ready, int64_t vectors, const float* bias,
                                 const float* residual, int epilogue, float* out, __half* out_xh, __half* xh, float* scratch,
                                 DeviceStatus* status, int sm_count, cudaStream_t stream, int* launches);
+
+// stream-K tcgen05 path (qlinear_stream.cu): up to kStreamMaxVectors vectors per pass
+constexpr int kStreamMaxVectors = 128;
+struct StreamPlan {
+  int nvp = 32;  // vectors per pass padded to 32
+  int tiles = 1, spt = 1, total_units = 1, units_per_cta = 1, grid = 1, slot_mode = 0, own_sum = 1;
+  size_t xh_bytes = 0;       // f16 activations in [K/8][nvp][8] order
+  size_t partial_bytes = 0;  // partial sums of ranges that cover part of a tile
+};
+StreamPlan plan_stream(const TiledWeight& w, int64_t vectors, int sm_count);
+size_t stream_weight_bytes(int codec, int64_t rows_padded, int64_t columns);
+cudaError_t launch_repack_stream(const TiledWeight& w, const RepackParts& parts, cudaStream_t stream);
+cudaError_t launch_qlinear_stream(const TiledWeight& w, const float* x, const __half* xh_ready, int64_t vectors, const float* bias,
+                                  const float* residual, int epilogue, float* out, __half* out_xh, __half* xh, float* partials,
+                                  DeviceStatus* status, int sm_count, cudaStream_t stream, int* launches);
 
 // Layout-independent front end. `scratch` must hold tiled_scratch_bytes(w, vectors, sm_count).
 size_t tiled_scratch_bytes(const TiledWeight& w, int64_t vectors, int sm_count);

@@ -147,10 +147,12 @@ etc_status build_qweight(etc_runtime* rt, int codec, const void* const* parts, c
   etc_qweight* w = new etc_qweight();
   w->rt = rt;
   w->tiled.codec = codec;
-  // The tcgen05 kernel (128-row tiles) is the default; ETC_TILED_LAYOUT=mma16 keeps the mma.sync kernel for comparison.
+  // The tcgen05 kernel with 128-row tiles is the default; ETC_TILED_LAYOUT=stream256 selects the stream-K tcgen05 kernel
+  // (weights on the MMA's N side), ETC_TILED_LAYOUT=mma16 the mma.sync kernel, both kept for comparison.
   const char* layout_env = std::getenv("ETC_TILED_LAYOUT");
-  w->tiled.layout = layout_env && std::string(layout_env) == "mma16" ? kLayoutMma16 : kLayoutUmma128;
-  const int64_t row_tile = w->tiled.layout == kLayoutUmma128 ? 128 : 16;
+  const std::string layout_name = layout_env ? layout_env : "";
+  w->tiled.layout = layout_name == "mma16" ? kLayoutMma16 : (layout_name == "stream256" ? kLayoutStream256 : kLayoutUmma128);
+  const int64_t row_tile = w->tiled.layout == kLayoutStream256 ? 256 : (w->tiled.layout == kLayoutUmma128 ? 128 : 16);
   w->tiled.rows = rows;
   w->tiled.rows_padded = (rows + row_tile - 1) / row_tile * row_tile;
   w->tiled.columns = columns;
@@ -158,8 +160,19 @@ etc_status build_qweight(etc_runtime* rt, int codec, const void* const* parts, c
   const int64_t kblocks = columns / 32;
   w->tiled.quant_bytes = (size_t)w->tiled.rows_padded * kblocks * (codec == ETC_CODEC_Q4_0 ? 16 : 32);
   w->tiled.scale_bytes = (size_t)w->tiled.rows_padded * kblocks * 2;
+  size_t counter_bytes = 0;
+  if (w->tiled.layout == kLayoutStream256) {  // payload and scales share one array of chunks
+    w->tiled.quant_bytes = stream_weight_bytes(codec, w->tiled.rows_padded, columns);
+    w->tiled.scale_bytes = 0;
+    counter_bytes = (size_t)(w->tiled.rows_padded / 256) * 4 * sizeof(int);
+  }
   etc_status st = rt->device_alloc(w->tiled.quant_bytes, (void**)&w->tiled.quants);
-  if (st == ETC_OK) st = rt->device_alloc(w->tiled.scale_bytes, (void**)&w->tiled.scales);
+  if (st == ETC_OK && w->tiled.scale_bytes) st = rt->device_alloc(w->tiled.scale_bytes, (void**)&w->tiled.scales);
+  if (st == ETC_OK && counter_bytes) {
+    st = rt->device_alloc(counter_bytes, (void**)&w->tiled.counters);
+    if (st == ETC_OK && cudaMemsetAsync(w->tiled.counters, 0, counter_bytes, rt->stream) != cudaSuccess)
+      st = fail(ETC_EXECUTION, "qweight: clearing the arrival tickets failed");
+  }
   RepackParts rp;
   std::memset(&rp, 0, sizeof(rp));
   rp.n_parts = n_parts;
@@ -190,6 +203,7 @@ etc_status build_qweight(etc_runtime* rt, int codec, const void* const* parts, c
   if (st != ETC_OK) {
     rt->device_free(w->tiled.quants);
     rt->device_free(w->tiled.scales);
+    rt->device_free(w->tiled.counters);
     delete w;
     return fail(st, message);
   }
@@ -201,6 +215,7 @@ void destroy_qweight(etc_qweight* w) {
   if (!w) return;
   w->rt->device_free(w->tiled.quants);
   w->rt->device_free(w->tiled.scales);
+  w->rt->device_free(w->tiled.counters);
   w->magic = 0;
   delete w;
 }

@@ -338,6 +338,7 @@ __global__ void repack_q8_0_kernel(RepackParts parts, int64_t rows, int64_t rows
 
 cudaError_t launch_repack(const TiledWeight& w, const RepackParts& parts, cudaStream_t stream) {
   if (w.layout == kLayoutUmma128) return launch_repack_umma(w, parts, stream);
+  if (w.layout == kLayoutStream256) return launch_repack_stream(w, parts, stream);
   const int64_t kblocks = w.columns / 32;
   const int64_t total = w.rows_padded * kblocks;
   if (total == 0) return cudaSuccess;
@@ -675,7 +676,17 @@ cudaError_t launch_qlinear_reduce(const float* scratch, int splits, int vpad, in
 // Scratch layout of the tcgen05 path: [xh8 activations, rounded to 256 B][split-K partials].
 static size_t umma_xh_region(const UmmaPlan& p) { return (p.xh_bytes + 255) & ~(size_t)255; }
 
+static size_t stream_xh_region(const StreamPlan& p) { return (p.xh_bytes + 255) & ~(size_t)255; }
+
 size_t tiled_scratch_bytes(const TiledWeight& w, int64_t vectors, int sm_count) {
+  if (w.layout == kLayoutStream256) {
+    size_t need = 0;
+    for (int64_t v0 = 0; v0 < vectors; v0 += kStreamMaxVectors) {
+      const StreamPlan p = plan_stream(w, std::min<int64_t>(kStreamMaxVectors, vectors - v0), sm_count);
+      need = std::max(need, stream_xh_region(p) + p.partial_bytes);
+    }
+    return need;
+  }
   if (w.layout == kLayoutUmma128) {
     size_t need = 0;
     for (int64_t v0 = 0; v0 < vectors; v0 += 256) {
@@ -690,6 +701,14 @@ size_t tiled_scratch_bytes(const TiledWeight& w, int64_t vectors, int sm_count) 
 cudaError_t launch_qlinear_tiled(const TiledWeight& w, const float* x, int64_t vectors, const float* bias,
                                  const float* residual, int epilogue, float* out, void* scratch, DeviceStatus* status,
                                  int sm_count, cudaStream_t stream, int* launches, const __half* xh_ready, __half* out_xh) {
+  if (w.layout == kLayoutStream256) {
+    size_t xh_region = 0;
+    for (int64_t v0 = 0; v0 < vectors; v0 += kStreamMaxVectors)
+      xh_region = std::max(xh_region, stream_xh_region(plan_stream(w, std::min<int64_t>(kStreamMaxVectors, vectors - v0), sm_count)));
+    return launch_qlinear_stream(w, x, xh_ready, vectors, bias, residual, epilogue, out, out_xh, reinterpret_cast<__half*>(scratch),
+                                 reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + xh_region), status, sm_count, stream,
+                                 launches);
+  }
   if (w.layout == kLayoutUmma128) {
     // the xh8 region is sized for the widest pass of this call
     size_t xh_region = 0;

@@ -17,7 +17,7 @@ SCALE_FIELDS = {gv.Q4_0: [0], gv.Q8_0: [0], gv.Q2_K: [80, 82], gv.Q3_K: [108], g
 REL_TOL = 2e-3  # north-star tolerance on f16/f32 linear outputs, as max |err| / max |ref|
 
 
-@pytest.fixture(params=["umma128", "mma16"])
+@pytest.fixture(params=["stream256", "umma128", "mma16"])
 def tiled_layout(request, monkeypatch):
     """Both tensor-core tilings: the tcgen05 kernel (default) and the mma.sync kernel; read at weight creation."""
     monkeypatch.setenv("ETC_TILED_LAYOUT", request.param)

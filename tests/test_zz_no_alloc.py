@@ -30,10 +30,10 @@ def test_static_scratch_linear_equals_the_existing_entry_point_twice_in_a_row(co
     for call in range(2):  # two calls in a row share the array: the second must not see the first one's leftovers
         x = rng.normal(size=(vectors, columns)).astype(np.float32)
         bias = rng.normal(size=rows).astype(np.float32)
-        expected = empty((vectors, rows))
-        qw.linear_into(dev(x), vectors, expected, bias=dev(bias))
-        got = empty((vectors, rows))
-        qw.linear_static_into(dev(x), vectors, got, bias=dev(bias))
+        dx, dbias = dev(x), dev(bias)  # held until the results are read: the runtime's stream is not torch's
+        expected, got = empty((vectors, rows)), empty((vectors, rows))
+        qw.linear_into(dx, vectors, expected, bias=dbias)
+        qw.linear_static_into(dx, vectors, got, bias=dbias)
         np.testing.assert_array_equal(host(got), host(expected), err_msg=f"call {call}")
 
 
@@ -43,12 +43,13 @@ def test_static_scratch_linear_with_epilogues():
     pg, pu = _weight(gv.Q4_0, ffn, d, 1), _weight(gv.Q4_0, ffn, d, 2)
     qgu = et.QWeight(rt, gv.Q4_0, [dev(pg), dev(pu)], [ffn, ffn], d, interleave8=True)
     x = np.random.default_rng(3).normal(size=(vectors, d)).astype(np.float32)
+    dx = dev(x)
     expected, got = empty((vectors, ffn)), empty((vectors, ffn))
-    qgu.linear_into(dev(x), vectors, expected, epilogue=et.EPILOGUE_SWIGLU)
-    qgu.linear_static_into(dev(x), vectors, got, epilogue=et.EPILOGUE_SWIGLU)
+    qgu.linear_into(dx, vectors, expected, epilogue=et.EPILOGUE_SWIGLU)
+    qgu.linear_static_into(dx, vectors, got, epilogue=et.EPILOGUE_SWIGLU)
     np.testing.assert_array_equal(host(got), host(expected))
     with pytest.raises(et.BackendError, match="residual"):
-        qgu.linear_static_into(dev(x), vectors, got, epilogue=et.EPILOGUE_RESIDUAL)
+        qgu.linear_static_into(dx, vectors, got, epilogue=et.EPILOGUE_RESIDUAL)
 
 
 def test_static_scratch_linear_rejects_calls_beyond_its_maximum():
