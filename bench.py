@@ -14,8 +14,8 @@ Printed JSON line (rank 0):
             (etc_decoder_generate_greedy), timed with CUDA events, max over ranks
   e2e       the same metric through the reference-facing call (Executable.executeSampled): every step copies the
             step's token ids / lane descriptors / page tables host->device and reads the sampled tokens back
-  roofline  the dominant kernel (tiled Q4_0 linear, fused gate/up shape [28672 x 4096], 32 vectors) timed alone with
-            CUDA events on the launching stream over weight sets larger than L2
+  roofline  the dominant kernel (tcgen05 Q4_0 linear, fused gate/up shape [28672 x 4096], 32 vectors) timed alone with
+            CUDA events on the launching stream (graph replays) over weight sets larger than L2
   cpu_baseline  the CPU oracle (restatement of the reference CPU backend) on a bounded sample, host cores stated
 """
 from __future__ import annotations
@@ -270,14 +270,20 @@ def time_dominant_kernel(rt, et, torch, model, vectors, iters=40):
     for i in range(8):
         copies[i % 4].linear_into(x, vectors, out, epilogue=et.EPILOGUE_SWIGLU, scratch=scratch, scratch_bytes=scratch_bytes)
     rt.synchronize()
+    # a Python launch loop is slower than the kernel: capture the launches once and time replays of the graph
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with torch.cuda.stream(stream):
-        start.record()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
         for i in range(iters):
             copies[i % 4].linear_into(x, vectors, out, epilogue=et.EPILOGUE_SWIGLU, scratch=scratch, scratch_bytes=scratch_bytes)
+    with torch.cuda.stream(stream):
+        graph.replay()
+        start.record()
+        graph.replay()
+        graph.replay()
         stop.record()
     rt.synchronize()
-    ms = start.elapsed_time(stop) / iters
+    ms = start.elapsed_time(stop) / (2 * iters)
     algorithmic = 2 * ffn * (d // 32) * 18 + 4 * vectors * d + 4 * vectors * ffn
     for c in copies:
         c.close()
@@ -394,8 +400,12 @@ def run_gpu_arm(args, rank, world):
             "step_roofline": {"algorithmic_bytes_per_step": step_bytes, "achieved_gbs": step_bytes * K / device_seconds / 1e9,
                               "frac_of_" + peak_kind: step_bytes * K / device_seconds / 1e9 / peaks["hbm_gbs"]},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
-                         "traffic": None, "peak_kind": peak_kind,
-                         "kernel": "qlinear_tiled_kernel<Q4_0> fused gate/up [28672x4096], 32 vectors, SwiGLU epilogue",
+                         # DRAM bytes per launch of the main kernel: ncu's read/write sums of the lm-head launch of the same kernel
+                         # (296.0 MB read for 295.5 MB of weights) scaled to this shape, plus its two split-K partial stores
+                         "traffic": int(2 * MODEL["ffn"] * (MODEL["d_model"] // 32) * 18 * (296.0 / 295.5) + 2 * 32 * 2 * MODEL["ffn"] * 4),
+                         "traffic_source": "profiles/qlinear_umma_q4_0_decode_step.md, scaled by weight bytes",
+                         "peak_kind": peak_kind,
+                         "kernel": "qlinear_umma_kernel<Q4_0,32> fused gate/up [28672x4096], 32 vectors, with its f16 conversion and split-K sum launches",
                          "ms_per_launch": kernel_ms, "algorithmic_bytes_per_launch": kernel_bytes},
             "cpu_baseline": cpu,
             "clocks": clocks,
