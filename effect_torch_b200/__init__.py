@@ -232,6 +232,13 @@ class QWeight:
         return out.value
 
 
+def tensor_parallel_id() -> bytes:
+    """128 bytes made by rank 0 and handed to every rank's `Executable.set_tensor_parallel`."""
+    buf = (C.c_uint8 * 128)()
+    _check(_lib.load().etc_tp_unique_id(buf))
+    return bytes(buf)
+
+
 class NativeKvPool:
     """native-addon.ts:193-207."""
 
@@ -367,6 +374,12 @@ class Executable:
 
     def finalize(self):
         _check(self.rt.L.etc_decoder_finalize(self.h))
+
+    def set_tensor_parallel(self, rank: int, world: int, unique_id: bytes | None):
+        """Joins this rank's decoder (built with local geometry and weight shards) to the tensor-parallel group.
+        Every rank calls this with the id rank 0 made with `tensor_parallel_id()`; it returns when all have joined."""
+        buf = (C.c_uint8 * 128).from_buffer_copy(unique_id) if unique_id is not None else None
+        _check(self.rt.L.etc_decoder_set_tensor_parallel(self.h, rank, world, buf))
 
     @staticmethod
     def _seq_array(seqs):

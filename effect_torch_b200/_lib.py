@@ -86,6 +86,8 @@ SIGNATURES = {
     "etc_decoder_set_weight": (None, [P, I, I, I, P, I64, I64]),
     "etc_decoder_set_weight_device": (None, [P, I, I, I, P, I64, I64]),
     "etc_decoder_set_max_advance": (None, [P, I]),
+    "etc_tp_unique_id": (None, [P]),
+    "etc_decoder_set_tensor_parallel": (None, [P, I, I, P]),
     "etc_decoder_finalize": (None, [P]),
     "etc_decoder_execute": (None, [P, P, P, I, P, I, P, P]),
     "etc_decoder_execute_sampled": (None, [P, P, P, I, P, I, P, P]),

@@ -17,6 +17,7 @@
 #include "common.h"
 #include "kernels.h"
 #include "pool.h"
+#include "tensor_parallel.h"
 #include "weights.h"
 
 using namespace etc;
@@ -83,6 +84,10 @@ struct etc_decoder {
   // what the captured graph baked in: it is re-captured when any of these changes
   int graph_active = 0, graph_pages = 0, graph_ctx = 0;
   const etc_pool* graph_pool = nullptr;
+
+  // tensor parallel: this decoder holds one rank's shard of every projection (rows of q/k/v/gate/up, columns of o/down)
+  TpComm* tp = nullptr;
+  int tp_rank = 0, tp_world = 1;
 };
 
 namespace {
@@ -198,6 +203,23 @@ etc_status run_linear(StepContext& s, const BoundWeight& raw, etc_qweight* tiled
   return ETC_OK;
 }
 
+// hidden += x W^T for the o and down projections. Under tensor parallelism every rank holds a column range of W and so
+// a partial sum: rank 0 adds the residual, the others overwrite, and the all-reduce leaves the same hidden state on
+// every rank (crates/runtime-cpu has no counterpart: the reference is single-device).
+etc_status project_into_hidden(StepContext& s, const BoundWeight& raw, etc_qweight* tiled_w, const float* x, int64_t rows,
+                               const __half* xh_ready) {
+  etc_decoder* d = s.dec;
+  const bool sharded = d->tp_world > 1;
+  const int epilogue = sharded && d->tp_rank != 0 ? ETC_EPILOGUE_NONE : ETC_EPILOGUE_RESIDUAL;
+  ETC_TRY(run_linear(s, raw, tiled_w, x, rows, d->hidden, epilogue, epilogue == ETC_EPILOGUE_RESIDUAL ? d->hidden : nullptr, xh_ready));
+  if (sharded) {
+    std::string error;
+    if (!tp_allreduce_sum(d->tp, d->hidden, (size_t)rows * d->cfg.d_model, d->rt->stream, &error)) return fail(ETC_EXECUTION, error);
+    ++s.launches;
+  }
+  return ETC_OK;
+}
+
 // Enqueues one invocation (all layers + head + greedy argmax) on the runtime's stream.
 etc_status enqueue_step(StepContext& s) {
   etc_decoder* d = s.dec;
@@ -262,8 +284,7 @@ etc_status enqueue_step(StepContext& s) {
       s.launches += 8;
     }
     const bool xh_o = xh && fast_attention;
-    ETC_TRY(run_linear(s, d->wo[li], d->tiled ? d->t_o[li] : nullptr, d->attl, rows, d->hidden, ETC_EPILOGUE_RESIDUAL, d->hidden,
-                       xh_o ? d->xh_att : nullptr));
+    ETC_TRY(project_into_hidden(s, d->wo[li], d->tiled ? d->t_o[li] : nullptr, d->attl, rows, xh_o ? d->xh_att : nullptr));
     if (xh) ETC_CUDA(launch_rmsnorm_xh8(d->hidden, (const float*)d->ffn_norm[li].d_raw, c.rms_eps, rows, c.d_model, d->xh_norm, stream));
     else ETC_CUDA(launch_rmsnorm(d->hidden, (const float*)d->ffn_norm[li].d_raw, c.rms_eps, rows, c.d_model, d->normed, stream));
     ++s.launches;
@@ -276,8 +297,7 @@ etc_status enqueue_step(StepContext& s) {
       ETC_CUDA(launch_swiglu(d->g, d->u, rows * c.ffn, d->act, c.exact, stream));
       ++s.launches;
     }
-    ETC_TRY(run_linear(s, d->down[li], d->tiled ? d->t_down[li] : nullptr, d->act, rows, d->hidden, ETC_EPILOGUE_RESIDUAL, d->hidden,
-                       xh ? d->xh_act : nullptr));
+    ETC_TRY(project_into_hidden(s, d->down[li], d->tiled ? d->t_down[li] : nullptr, d->act, rows, xh ? d->xh_act : nullptr));
   }
   const bool xh_head = d->xh_path && T == 1;
   if (xh_head) ETC_CUDA(launch_rmsnorm_xh8(d->hidden, (const float*)d->out_norm.d_raw, c.rms_eps, rows, c.d_model, d->xh_norm, stream));
@@ -523,6 +543,32 @@ etc_status etc_decoder_set_max_advance(etc_decoder* dec, int max_advance) {
   return ETC_OK;
 }
 
+etc_status etc_tp_unique_id(uint8_t* out_id) {
+  if (!out_id) return fail(ETC_INVALID_ARGUMENT, "tensor parallel: the id buffer is null");
+  std::string error;
+  if (!tp_unique_id(out_id, &error)) return fail(ETC_UNAVAILABLE, "tensor parallel: " + error);
+  return ETC_OK;
+}
+
+etc_status etc_decoder_set_tensor_parallel(etc_decoder* dec, int rank, int world, const uint8_t* id) {
+  if (!valid_decoder(dec)) return fail(ETC_INVALID_HANDLE, "decoder handle is invalid or destroyed");
+  if (world < 1 || rank < 0 || rank >= world) return fail(ETC_INVALID_ARGUMENT, "tensor parallel: rank " + std::to_string(rank) + " is outside 0.." + std::to_string(world));
+  if (dec->tp) return fail(ETC_COMPILATION, "tensor parallel: the decoder already has a communicator");
+  if (world == 1) return ETC_OK;
+  if (!id) return fail(ETC_INVALID_ARGUMENT, "tensor parallel: the id buffer is null");
+  ETC_TRY(activate(dec->rt));
+  std::string error;
+  dec->tp = tp_comm_create(rank, world, id, &error);
+  if (!dec->tp) return fail(ETC_UNAVAILABLE, "tensor parallel: " + error);
+  dec->tp_rank = rank;
+  dec->tp_world = world;
+  if (dec->step_graph) {  // captured without the all-reduces
+    cudaGraphExecDestroy(dec->step_graph);
+    dec->step_graph = nullptr;
+  }
+  return ETC_OK;
+}
+
 etc_status etc_decoder_finalize(etc_decoder* dec) {
   if (!valid_decoder(dec)) return fail(ETC_INVALID_HANDLE, "decoder handle is invalid or destroyed");
   etc_runtime* rt = dec->rt;
@@ -647,6 +693,7 @@ etc_status etc_decoder_destroy(etc_decoder* dec) {
   ETC_TRY(activate(rt));
   cudaStreamSynchronize(rt->stream);
   if (dec->step_graph) cudaGraphExecDestroy(dec->step_graph);
+  tp_comm_destroy(dec->tp);
   auto free_bound = [&](BoundWeight& w) { if (w.d_raw) rt->device_free(w.d_raw); w.d_raw = nullptr; };
   free_bound(dec->tok_embd); free_bound(dec->out_norm); free_bound(dec->head);
   for (auto* list : {&dec->attn_norm, &dec->ffn_norm, &dec->wq, &dec->wk, &dec->wv, &dec->wo, &dec->gate, &dec->up, &dec->down})

@@ -277,7 +277,7 @@ __global__ void __launch_bounds__(StreamRoles<LW>::kThreads, 1) qlinear_stream_k
     const int row = threadIdx.x & (kTileRows - 1);
     for (int i = warp / kGroupWarps; i < n; i += kDequantWarps / kGroupWarps) {
       const int sw = i % kWStages, st = i % kStages;
-      if (!mbar_wait(&full_w[sw], (uint32_t)(i / kWStages) & 1, abort_flag)) break;
+      if (!mbar_wait_warp(&full_w[sw], (uint32_t)(i / kWStages) & 1, abort_flag)) break;
       const unsigned char* ws = w_ring + (size_t)sw * Cfg::kRingStageBytes;
       uint4 q[kStageBlocks][QW];
       __half sc[kStageBlocks];
@@ -306,7 +306,7 @@ __global__ void __launch_bounds__(StreamRoles<LW>::kThreads, 1) qlinear_stream_k
         }
       }
       // the MMAs that read this stage in the previous round must have retired
-      if (!mbar_wait(&empty[st], ((uint32_t)(i / kStages) & 1) ^ 1, abort_flag)) break;
+      if (!mbar_wait_warp(&empty[st], ((uint32_t)(i / kStages) & 1) ^ 1, abort_flag)) break;
       unsigned char* dst = b_ring + (size_t)st * kStageBBytes + (size_t)row * 16;
 #pragma unroll
       for (int b = 0; b < kStageBlocks; ++b)
@@ -326,7 +326,7 @@ __global__ void __launch_bounds__(StreamRoles<LW>::kThreads, 1) qlinear_stream_k
       const uint32_t lane_base = (uint32_t)(lw * 32) << 16;
       for (int i = 0; i < n; ++i) {
         const int sw = i % kWStages, st = i % kStages;
-        if (!mbar_wait(&full_w[sw], (uint32_t)(i / kWStages) & 1, abort_flag)) break;
+        if (!mbar_wait_warp(&full_w[sw], (uint32_t)(i / kWStages) & 1, abort_flag)) break;
         const uint4* src = reinterpret_cast<const uint4*>(w_ring + (size_t)sw * Cfg::kRingStageBytes + Cfg::kStageWBytes) + v;
         uint32_t x[2][16];
 #pragma unroll
@@ -337,7 +337,7 @@ __global__ void __launch_bounds__(StreamRoles<LW>::kThreads, 1) qlinear_stream_k
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty_w[sw]);
-        if (!mbar_wait(&empty[st], ((uint32_t)(i / kStages) & 1) ^ 1, abort_flag)) break;
+        if (!mbar_wait_warp(&empty[st], ((uint32_t)(i / kStages) & 1) ^ 1, abort_flag)) break;
         tc_fence_after();
         tmem_st16(a_tmem0 + lane_base + (uint32_t)(st * 32), x[0]);
         tmem_st16(a_tmem0 + lane_base + (uint32_t)(st * 32 + 16), x[1]);
@@ -358,7 +358,7 @@ __global__ void __launch_bounds__(StreamRoles<LW>::kThreads, 1) qlinear_stream_k
         const int u = u0 + i, tile = u / a.spt, ks0 = u - tile * a.spt;
         const int len = min(a.spt - ks0, n - i);
         i += len;
-        if (!mbar_wait(d_full, (uint32_t)seg & 1, abort_flag)) break;
+        if (!mbar_wait_warp(d_full, (uint32_t)seg & 1, abort_flag)) break;
         tc_fence_after();
         if (len == a.spt) {
 #pragma unroll 1

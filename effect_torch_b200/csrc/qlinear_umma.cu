@@ -171,7 +171,7 @@ __global__ void __launch_bounds__(UmmaCfg<NV>::kThreads) qlinear_umma_kernel(Umm
           mbar_arrive(&full_a[pending_slot]);
         }
         // the MMAs that read this TMEM stage in the previous round must have retired
-        ok = mbar_wait(&empty[s], (round & 1) ^ 1, abort_flag);
+        ok = mbar_wait_warp(&empty[s], (round & 1) ^ 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
@@ -188,6 +188,7 @@ __global__ void __launch_bounds__(UmmaCfg<NV>::kThreads) qlinear_umma_kernel(Umm
     // ------------------------------------------------------------------ epilogue (first group)
     if (group != 0) ok = false;
     if (ok) ok = mbar_wait(done, 0, abort_flag);
+    ok = __all_sync(0xffffffffu, ok);  // warp-uniform: the epilogue below shuffles across the warp
     if (ok) {
       tc_fence_after();
       const int r = tile * kUmmaRows + row;

@@ -57,6 +57,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return false;
 }
 
+// The same for a whole warp: every lane gets the same answer, so the warp can keep using __syncwarp afterwards even
+// when the wait gave up on some lanes only.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag)) != 0;
+}
+
 // Bounded wait for roles with slack (they run stages ahead, or wait for a whole range): poll, then sleep. A sleeping
 // warp costs the warps that share its scheduler nothing, unlike a spinning or a parked one.
 __device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, volatile int* abort_flag, unsigned sleep_ns) {

@@ -1,0 +1,89 @@
+"""Host-side sharding for tensor parallelism: which part of every weight a rank holds, and the local geometry its
+decoder is built with. Column-parallel projections (wq, wk, wv, gate, up) split the ROWS of the reference's [N, K]
+weights; row-parallel ones (wo, down) split K, i.e. a range of 32-value blocks of every packed row (quantized rows are
+sequences of blocks: crates/runtime-cpu/src/quantized.rs:263-292). Embedding, norms and head are replicated.
+
+Works on numpy arrays and on torch tensors alike (only slicing, reshape and contiguity are used).
+"""
+from __future__ import annotations
+
+BLOCK_BYTES = {0: None, 2: 18, 8: 34}  # codec -> bytes per 32-value block (0 = dense f32)
+ROW_SPLIT = ("wq", "wk", "wv", "gate", "up")
+COLUMN_SPLIT = ("wo", "down")
+
+
+def check_geometry(cfg: dict, world: int) -> None:
+    """Raises ValueError when the model cannot be cut into `world` shards."""
+    if world < 1:
+        raise ValueError("world size must be positive")
+    for key in ("q_heads", "kv_heads", "ffn"):
+        if cfg[key] % world:
+            raise ValueError(f"{key} = {cfg[key]} is not divisible by the {world} ranks")
+    if (cfg["ffn"] // world) % 64 or (cfg["q_heads"] // world * cfg["head_dim"]) % 64:
+        raise ValueError("a rank's share of ffn and of q_heads * head_dim must be a multiple of 64 columns")
+
+
+def local_config(cfg: dict, world: int) -> dict:
+    """The geometry one rank's decoder and KV pool are created with."""
+    check_geometry(cfg, world)
+    out = dict(cfg)
+    out["q_heads"] = cfg["q_heads"] // world
+    out["kv_heads"] = cfg["kv_heads"] // world
+    out["ffn"] = cfg["ffn"] // world
+    return out
+
+
+def _contiguous(x):
+    return x.contiguous() if hasattr(x, "contiguous") else __import__("numpy").ascontiguousarray(x)
+
+
+def shard_rows(weight, rank: int, world: int):
+    """Rows [rank * N / world, (rank + 1) * N / world) of a dense or packed [N, ...] matrix."""
+    n = weight.shape[0]
+    if n % world:
+        raise ValueError(f"{n} rows are not divisible by {world}")
+    per = n // world
+    return _contiguous(weight[rank * per:(rank + 1) * per])
+
+
+def shard_columns(weight, codec: int, rank: int, world: int):
+    """Columns [rank * K / world, (rank + 1) * K / world) of every row: f32 elements, or whole 32-value blocks."""
+    unit = 1 if codec == 0 else BLOCK_BYTES[codec]
+    width = weight.shape[1]
+    if width % unit:
+        raise ValueError("row width is not a whole number of blocks")
+    units = width // unit
+    granule = 32 if codec == 0 else 1  # a dense shard keeps 32-column alignment like a packed one
+    if units % (world * granule):
+        raise ValueError(f"{units} column units are not divisible by {world} ranks")
+    per = units // world * unit
+    return _contiguous(weight[:, rank * per:(rank + 1) * per])
+
+
+def shard_weights(weights: dict, cfg: dict, rank: int, world: int) -> dict:
+    """One rank's share of a weight dictionary laid out like tests/helpers.make_weights: projections are either dense
+    [N, K] arrays or (packed, rows, columns) tuples."""
+    check_geometry(cfg, world)
+    codec = weights["codec"]
+
+    def rows(value):
+        if isinstance(value, tuple):
+            packed, n, k = value
+            return (shard_rows(packed, rank, world), n // world, k)
+        return shard_rows(value, rank, world)
+
+    def columns(value):
+        if isinstance(value, tuple):
+            packed, n, k = value
+            return (shard_columns(packed, codec, rank, world), n, k // world)
+        return shard_columns(value, 0, rank, world)
+
+    out = {"tok_embd": weights["tok_embd"], "out_norm": weights["out_norm"], "head": weights["head"], "codec": codec, "layers": []}
+    for layer in weights["layers"]:
+        local = dict(layer)
+        for name in ROW_SPLIT:
+            local[name] = rows(layer[name])
+        for name in COLUMN_SPLIT:
+            local[name] = columns(layer[name])
+        out["layers"].append(local)
+    return out

@@ -293,6 +293,17 @@ typedef enum etc_weight_slot {
   ETC_W_FFN_NORM = 6, ETC_W_GATE = 7, ETC_W_UP = 8, ETC_W_DOWN = 9, ETC_W_OUT_NORM = 10, ETC_W_HEAD = 11
 } etc_weight_slot;
 
+/* Tensor parallelism (one process per GPU; no counterpart in the single-device reference). Each rank creates its
+ * decoder with LOCAL geometry (q_heads/world, kv_heads/world, ffn/world; d_model and vocab whole) and binds its shard
+ * of every projection: a contiguous row range of wq/wk/wv/gate/up, a contiguous range of 32-value blocks of every row
+ * of wo/down; embedding, norms and head are replicated, and so is the host-side page allocation, so every rank's KV
+ * pool (built with the local kv_heads) holds the same page tables. Rank 0 makes the 128-byte id, the host sends it to
+ * every rank by its own means, and all ranks call etc_decoder_set_tensor_parallel together (it blocks until the last
+ * one joins). After o and down the partial sums are all-reduced (f32, NCCL, on the runtime's stream, inside the
+ * captured step graph as well); rank 0 alone adds the residual. world == 1 is accepted and changes nothing. */
+ETC_API etc_status etc_tp_unique_id(uint8_t* out_id_128_bytes);
+ETC_API etc_status etc_decoder_set_tensor_parallel(etc_decoder* dec, int rank, int world, const uint8_t* id_128_bytes);
+
 ETC_API etc_status etc_decoder_create(etc_runtime* rt, const etc_decoder_config* config, etc_decoder** out);
 ETC_API etc_status etc_decoder_destroy(etc_decoder* dec);
 /* Bind one weight (host pointer; uploaded and retained — constantWeights). codec F32 = dense f32

@@ -1,0 +1,121 @@
+"""Tensor-parallel host logic on CPU: the shard arithmetic against the oracle, and a world_size-2 gloo run of one
+projection block (shard, partial linear, residual on rank 0 only, all-reduce) against the unsharded oracle."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+import oracle as orc
+from effect_torch_b200 import tensor_parallel as tp
+from tests import helpers
+from tests.golden import reference_vectors as gv
+
+
+def test_local_geometry_and_divisibility_errors():
+    cfg = helpers.TINY_Q
+    local = tp.local_config(cfg, 2)
+    assert (local["q_heads"], local["kv_heads"], local["ffn"], local["d_model"], local["vocab"]) == (2, 1, 384, 256, 2048)
+    with pytest.raises(ValueError, match="kv_heads"):
+        tp.local_config(cfg, 4)
+    with pytest.raises(ValueError, match="multiple of 64"):
+        tp.local_config(dict(cfg, ffn=704, kv_heads=2), 2)  # 352 columns per rank
+
+
+@pytest.mark.parametrize("codec", [gv.Q4_0, gv.Q8_0])
+def test_row_and_column_shards_recombine_to_the_full_linear(codec):
+    rng = np.random.default_rng(5)
+    n, k, world = 96, 256, 2
+    w = rng.normal(0, 0.05, size=(n, k)).astype(np.float32)
+    packed = orc.quantize(codec, w)
+    x = rng.normal(size=(3, k)).astype(np.float32)
+    full = orc.qlinear(codec, x, packed, n, k)
+    # column-parallel projection: ranks hold row ranges, outputs concatenate
+    parts = [orc.qlinear(codec, x, tp.shard_rows(packed, r, world), n // world, k) for r in range(world)]
+    np.testing.assert_array_equal(np.concatenate(parts, axis=1), full)
+    # row-parallel projection: ranks hold block ranges of every row and the matching slice of x, outputs add
+    kk = k // world
+    partial = [orc.qlinear(codec, np.ascontiguousarray(x[:, r * kk:(r + 1) * kk]), tp.shard_columns(packed, codec, r, world), n, kk)
+               for r in range(world)]
+    assert helpers.rel_err(partial[0] + partial[1], full) <= 1e-6
+    # the shard's bytes are the blocks of that column range, bit for bit
+    np.testing.assert_array_equal(orc.dequantize(codec, tp.shard_columns(packed, codec, 1, world), n, kk),
+                                  orc.dequantize(codec, packed, n, k)[:, kk:])
+
+
+def test_shard_weights_covers_every_projection():
+    cfg = helpers.TINY_Q
+    weights = helpers.make_weights(cfg, seed=2, codec=gv.Q4_0)
+    shards = [tp.shard_weights(weights, cfg, r, 2) for r in range(2)]
+    for name in tp.ROW_SPLIT:
+        packed, n, k = weights["layers"][0][name]
+        got = np.concatenate([s["layers"][0][name][0] for s in shards], axis=0)
+        np.testing.assert_array_equal(got, packed)
+        assert shards[0]["layers"][0][name][1:] == (n // 2, k)
+    for name in tp.COLUMN_SPLIT:
+        packed, n, k = weights["layers"][0][name]
+        got = np.concatenate([s["layers"][0][name][0] for s in shards], axis=1)
+        np.testing.assert_array_equal(got, packed)
+        assert shards[1]["layers"][0][name][1:] == (n, k // 2)
+    assert shards[0]["head"] is weights["head"] and shards[1]["tok_embd"] is weights["tok_embd"]
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank, world, port, results):
+    import torch
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        # rank 0's 128-byte id reaches every rank through the host transport (what the CUDA path does with the NCCL id)
+        ident = torch.zeros(128, dtype=torch.uint8)
+        if rank == 0:
+            ident = torch.arange(128, dtype=torch.uint8)
+        dist.broadcast(ident, src=0)
+        assert ident.tolist() == list(range(128))
+        cfg = helpers.TINY_Q
+        codec = gv.Q4_0
+        weights = helpers.make_weights(cfg, seed=7, codec=codec)  # same seed on every rank: replicated host state
+        local = tp.shard_weights(weights, cfg, rank, world)
+        rng = np.random.default_rng(11)
+        hidden = rng.normal(size=(4, cfg["d_model"])).astype(np.float32)
+        att = rng.normal(size=(4, cfg["q_heads"] * cfg["head_dim"])).astype(np.float32)
+        packed, n, k = weights["layers"][0]["wo"]
+        expected = hidden + orc.qlinear(codec, att, packed, n, k)
+        lp, ln, lk = local["layers"][0]["wo"]
+        partial = orc.qlinear(codec, np.ascontiguousarray(att[:, rank * lk:(rank + 1) * lk]), lp, ln, lk)
+        mine = torch.from_numpy((hidden + partial) if rank == 0 else partial)  # the residual enters once
+        dist.all_reduce(mine)
+        results[rank] = helpers.rel_err(mine.numpy(), expected)
+        # gate/up are row shards: the ranks' activations concatenate to the full SwiGLU input of down
+        g, gn, gk = local["layers"][0]["gate"]
+        u, _, _ = local["layers"][0]["up"]
+        x = rng.normal(size=(4, cfg["d_model"])).astype(np.float32)
+        act_local = orc.silu_mul(orc.qlinear(codec, x, g, gn, gk), orc.qlinear(codec, x, u, gn, gk))
+        dp, dn, dk = local["layers"][0]["down"]
+        down_partial = torch.from_numpy(orc.qlinear(codec, act_local, dp, dn, dk))
+        dist.all_reduce(down_partial)
+        fg, fgn, fgk = weights["layers"][0]["gate"]
+        fu, _, _ = weights["layers"][0]["up"]
+        fd, fdn, fdk = weights["layers"][0]["down"]
+        full = orc.qlinear(codec, orc.silu_mul(orc.qlinear(codec, x, fg, fgn, fgk), orc.qlinear(codec, x, fu, fgn, fgk)), fd, fdn, fdk)
+        results[world + rank] = helpers.rel_err(down_partial.numpy(), full)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_projection_block_over_gloo_matches_the_unsharded_oracle():
+    import torch.multiprocessing as mp
+
+    world, port = 2, _free_port()
+    manager = mp.get_context("spawn").Manager()
+    results = manager.dict()
+    mp.spawn(_rank_main, args=(world, port, results), nprocs=world, join=True)
+    assert sorted(results.keys()) == [0, 1, 2, 3]
+    assert all(err <= 1e-6 for err in results.values()), dict(results)
