@@ -202,9 +202,15 @@ def run_reference_arm(args, rank):
 
 
 # ------------------------------------------------------------------------------------------------ GPU arm
-def build_decoder(rt, et, torch, model, batch, max_tokens, seed):
+def build_decoder(rt, et, torch, model, batch, max_tokens, seed, shared_seed=None):
+    """Random-init weights of the model's shape. `shared_seed`: tensors that tensor-parallel ranks replicate (embedding,
+    head) are drawn from it so that every rank holds the same values; the projections are this rank's own shard."""
     gen = torch.Generator(device="cuda")
     gen.manual_seed(seed)
+    shared = gen
+    if shared_seed is not None:
+        shared = torch.Generator(device="cuda")
+        shared.manual_seed(shared_seed)
     dec = et.Executable(rt, layers=model["layers"], d_model=model["d_model"], q_heads=model["q_heads"], kv_heads=model["kv_heads"],
                         head_dim=model["head_dim"], ffn=model["ffn"], vocab=model["vocab"], rms_eps=model["rms_eps"],
                         rope_theta=model["rope_theta"], batch=batch, max_tokens=max_tokens, block_size=BLOCK, kv_dtype=et.KV_F16,
@@ -212,13 +218,13 @@ def build_decoder(rt, et, torch, model, batch, max_tokens, seed):
     d, qw, kvw, ffn, V = (model["d_model"], model["q_heads"] * model["head_dim"], model["kv_heads"] * model["head_dim"], model["ffn"],
                           model["vocab"])
 
-    def normal(rows, cols):
-        w = torch.randn((rows, cols), generator=gen, device="cuda", dtype=torch.float32)
+    def normal(rows, cols, g=None):
+        w = torch.randn((rows, cols), generator=g or gen, device="cuda", dtype=torch.float32)
         w.mul_(0.02)
         return w
 
-    def quantized(rows, cols):
-        w = normal(rows, cols)
+    def quantized(rows, cols, g=None):
+        w = normal(rows, cols, g)
         packed = torch.empty((rows, cols // 32 * 18), dtype=torch.uint8, device="cuda")
         torch.cuda.synchronize()
         rt.quantize_into(Q4_0, w, rows, cols, packed)
@@ -229,7 +235,7 @@ def build_decoder(rt, et, torch, model, batch, max_tokens, seed):
         torch.cuda.synchronize()
         dec.set_weight(slot, layer, tensor, codec=codec, rows=rows, columns=cols)
 
-    bind(et.W_TOK_EMBD, 0, normal(V, d))
+    bind(et.W_TOK_EMBD, 0, normal(V, d, shared))
     ones = torch.ones(d, device="cuda", dtype=torch.float32)
     for l in range(model["layers"]):
         bind(et.W_ATTN_NORM, l, ones)
@@ -238,7 +244,7 @@ def build_decoder(rt, et, torch, model, batch, max_tokens, seed):
                              (et.W_UP, (ffn, d)), (et.W_DOWN, (d, ffn))):
             bind(slot, l, quantized(r, c), Q4_0, r, c)
     bind(et.W_OUT_NORM, 0, ones)
-    bind(et.W_HEAD, 0, quantized(V, d), Q4_0, V, d)
+    bind(et.W_HEAD, 0, quantized(V, d, shared), Q4_0, V, d)
     dec.finalize()
     torch.cuda.empty_cache()
     return dec
@@ -303,13 +309,25 @@ def run_gpu_arm(args, rank, world):
     model = dict(MODEL)
     if args.layers:
         model["layers"] = args.layers
+    # N > 1: independent replicas by default; --parallelism tp cuts one model over the ranks (an all-reduce after the o
+    # and down projections)
+    tp = world > 1 and args.parallelism == "tp"
+    if tp:
+        from effect_torch_b200 import tensor_parallel
+        model = tensor_parallel.local_config(model, world)  # this rank's share of heads and ffn
     K, W = args.steps, args.warmup
     # every sequence: prompt + warm-up + timed steps, twice (end-to-end leg, then device-resident leg)
     per_seq = ((PROMPT + W + K + BLOCK) // BLOCK + 1) * BLOCK
     max_tokens = 2 * BATCH * per_seq
-    dec = build_decoder(rt, et, torch, model, BATCH, max_tokens, seed=3 + rank)
+    dec = build_decoder(rt, et, torch, model, BATCH, max_tokens, seed=3 + rank, shared_seed=3 if tp else None)
+    if tp:
+        ident = torch.zeros(128, dtype=torch.uint8, device="cuda")
+        if rank == 0:
+            ident = torch.frombuffer(bytearray(et.tensor_parallel_id()), dtype=torch.uint8).cuda()
+        dist.broadcast(ident, src=0)
+        dec.set_tensor_parallel(rank, world, bytes(ident.cpu().tolist()))
     pool = et.NativeKvPool(rt, model["layers"], model["kv_heads"], model["head_dim"], max_tokens, BLOCK, et.KV_F16)
-    rng = np.random.default_rng(3 + rank)
+    rng = np.random.default_rng(3 if tp else 3 + rank)  # tensor-parallel ranks decode the same sequences
     prompts = rng.integers(0, model["vocab"], size=(BATCH, PROMPT)).astype(np.uint32)
 
     def prefill():
@@ -361,6 +379,13 @@ def run_gpu_arm(args, rank, world):
     times = torch.tensor([device_ms / 1000.0, e2e_seconds], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    if tp:  # every rank must have generated the same tokens
+        mine = torch.from_numpy(out.astype(np.int64)).cuda()
+        lo, hi = mine.clone(), mine.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        if not torch.equal(lo, hi):
+            raise RuntimeError("tensor-parallel ranks generated different tokens")
     device_seconds, e2e_seconds = [float(v) for v in times.cpu()]
     graph_launches = dec.diagnostics()["launches_per_step"]
     mean_ctx = PROMPT + W + (K + 1) / 2.0
@@ -374,8 +399,9 @@ def run_gpu_arm(args, rank, world):
         else:
             kernel_ms, kernel_bytes = time_dominant_kernel(rt, et, torch, model, BATCH)
         achieved = kernel_bytes / (kernel_ms * 1e-3) / 1e9
-        value = world * BATCH * K / device_seconds
-        e2e_value = world * BATCH * K / e2e_seconds
+        jobs = 1 if tp else world  # replicas each decode their own batch; tensor-parallel ranks share one
+        value = jobs * BATCH * K / device_seconds
+        e2e_value = jobs * BATCH * K / e2e_seconds
         max_blocks = max_tokens // BLOCK + 3
         h2d = BATCH * 4 + BATCH * 16 + BATCH * 8 + BATCH * max_blocks * 4
         d2h = BATCH * 4 + 32
@@ -388,11 +414,14 @@ def run_gpu_arm(args, rank, world):
             cpu = {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample, "cpu_seconds": seconds}
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": 1000.0 * device_seconds / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": 1000.0 * device_seconds / K, "higher_is_better": True, "scaling": "strong" if tp else "weak", "vs_baseline": None,
             "dtype": "f16 MMA operands, f32 accumulate (Q4_0 weights, f16 KV)", "data": "synthetic",
             "config": {"workload": f"llama3-8b-shape Q4_0 paged decode: {model['layers']} layers, batch {BATCH}, prompt {PROMPT}, "
                                    f"{K} greedy steps, f16 KV 16-token pages",
-                       "global_batch": BATCH * world, "parallelism": "single GPU" if world == 1 else f"{world} independent replicas",
+                       "global_batch": BATCH * jobs,
+                       "parallelism": "single GPU" if world == 1 else (f"tp{world}: rows of q/k/v/gate/up and columns of o/down cut over the ranks, "
+                                                                       f"NCCL all-reduce of [batch, d_model] f32 after o and down, head replicated"
+                                                                       if tp else f"{world} independent replicas"),
                        "l2": "per-step working set (weights 4.2 GB + KV) exceeds the 126 MB L2; no flush needed"},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": 1000.0 * e2e_seconds / K, "launches_per_step": launches_per_step},
@@ -425,6 +454,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="debug: fewer layers than the 8B shape (the result is then not a bench value)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--parallelism", default="replicas", choices=["replicas", "tp"],
+                    help="N > 1: N independent replicas, each decoding its own batch (weak scaling; the 8B shape fits one GPU), or "
+                         "one tensor-parallel model over the ranks (strong scaling)")
     ap.add_argument("--prefill", default="model", choices=["model", "direct"],
                     help="model: the prompt runs through the decode path (the benchmark); direct: K/V rows are written "
                          "straight into the pages (profiling shortcut, not a bench value)")
