@@ -86,6 +86,14 @@ SIGNATURES = {
     "etc_decoder_set_weight": (None, [P, I, I, I, P, I64, I64]),
     "etc_decoder_set_weight_device": (None, [P, I, I, I, P, I64, I64]),
     "etc_decoder_set_max_advance": (None, [P, I]),
+    "etc_gguf_open": (None, [C.c_char_p, P, P]),
+    "etc_gguf_close": (None, [P]),
+    "etc_gguf_summary": (None, [P, P, P, P]),
+    "etc_gguf_metadata": (None, [P, I64, P, P, P, P, P, P, P]),
+    "etc_gguf_tensor": (None, [P, I64, P, P, P, P, P, P, P]),
+    "etc_gguf_find_tensor": (None, [P, C.c_char_p, P]),
+    "etc_gguf_read_tensor_into": (None, [P, I64, P, C.c_uint64, P]),
+    "etc_gguf_load_tensor_device": (None, [P, P, I64, P, C.c_uint64, P]),
     "etc_tp_unique_id": (None, [P]),
     "etc_decoder_set_tensor_parallel": (None, [P, I, I, P]),
     "etc_decoder_finalize": (None, [P]),

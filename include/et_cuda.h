@@ -293,6 +293,38 @@ typedef enum etc_weight_slot {
   ETC_W_FFN_NORM = 6, ETC_W_GATE = 7, ETC_W_UP = 8, ETC_W_DOWN = 9, ETC_W_OUT_NORM = 10, ETC_W_HEAD = 11
 } etc_weight_slot;
 
+/* ---- GGUF v3 files (crates/runtime/src/gguf.rs; napi loadGguf / inspectGguf, native-addon.ts:316-325) ----
+ * etc_gguf_open parses header, metadata table and tensor catalog (parse_gguf, gguf.rs:682-946) with the reference's
+ * resource limits, overflow checks and message texts, reading no payload. Differences: GGML type codes 2 (Q4_0) and
+ * 8 (Q8_0) are accepted as well, their least-major dimension must be divisible by 32 instead of 256.
+ * Errors: malformed file -> ETC_INVALID_ARGUMENT "gguf: ..."; I/O -> ETC_TRANSFER "gguf: I/O failed: ...";
+ * cancellation flag set -> ETC_CANCELLED "gguf: operation aborted". Strings returned live as long as the handle. */
+typedef struct etc_gguf etc_gguf;
+ETC_API etc_status etc_gguf_open(const char* path, const volatile int* cancelled, etc_gguf** out);
+ETC_API etc_status etc_gguf_close(etc_gguf* file);
+ETC_API etc_status etc_gguf_summary(const etc_gguf* file, const char** architecture, int64_t* metadata_count,
+                                    int64_t* tensor_count);
+/* One metadata entry in file order. value_type is the GGUF type code (9 = array, then element_type and count are set
+ * and the scalar outputs hold the first element). Integers and bool come in integer_bits (two's complement for the
+ * signed types), f32/f64 in real, strings in string. */
+ETC_API etc_status etc_gguf_metadata(const etc_gguf* file, int64_t index, const char** key, int* value_type,
+                                     int* element_type, int64_t* count, uint64_t* integer_bits, double* real,
+                                     const char** string);
+/* One catalog entry (GgufTensorDescriptor, gguf.rs:309-337): logical shape row-major (GGUF dimensions reversed);
+ * physical shape = logical for F32, [rows, encoded_row_bytes] for block codecs; absolute, validated byte range. */
+ETC_API etc_status etc_gguf_tensor(const etc_gguf* file, int64_t index, const char** name, etc_codec* codec, int* rank,
+                                   int64_t* logical_shape4, int64_t* physical_shape4, uint64_t* data_offset,
+                                   uint64_t* byte_len);
+ETC_API etc_status etc_gguf_find_tensor(const etc_gguf* file, const char* name, int64_t* index);
+/* read_gguf_tensor_into (gguf.rs:948-990): dst_bytes must equal the tensor's byte length exactly; positioned reads in
+ * 8 MiB chunks with the cancellation flag polled between them. */
+ETC_API etc_status etc_gguf_read_tensor_into(const etc_gguf* file, int64_t index, void* h_dst, uint64_t dst_bytes,
+                                             const volatile int* cancelled);
+/* The same payload streamed into device memory through two pinned staging buffers (file read of one chunk overlaps
+ * the copy of the previous one); returns after the runtime's stream has the whole tensor. */
+ETC_API etc_status etc_gguf_load_tensor_device(etc_runtime* rt, const etc_gguf* file, int64_t index, void* d_dst,
+                                               uint64_t dst_bytes, const volatile int* cancelled);
+
 /* Tensor parallelism (one process per GPU; no counterpart in the single-device reference). Each rank creates its
  * decoder with LOCAL geometry (q_heads/world, kv_heads/world, ffn/world; d_model and vocab whole) and binds its shard
  * of every projection: a contiguous row range of wq/wk/wv/gate/up, a contiguous range of 32-value blocks of every row
