@@ -381,6 +381,17 @@ class Executable:
         buf = (C.c_uint8 * 128).from_buffer_copy(unique_id) if unique_id is not None else None
         _check(self.rt.L.etc_decoder_set_tensor_parallel(self.h, rank, world, buf))
 
+    def peer_exchange_handle(self) -> bytes:
+        """64-byte CUDA IPC handle of this rank's all-reduce exchange region (after finalize and set_tensor_parallel)."""
+        buf = (C.c_uint8 * 64)()
+        _check(self.rt.L.etc_decoder_tp_peer_export(self.h, buf))
+        return bytes(buf)
+
+    def use_peer_allreduce(self, handles: list):
+        """Switches the all-reduces to the one-shot kernel over peer memory; `handles[r]` is rank r's exchange handle."""
+        table = (C.c_uint8 * (64 * len(handles))).from_buffer_copy(b"".join(handles))
+        _check(self.rt.L.etc_decoder_tp_peer_import(self.h, table))
+
     @staticmethod
     def _seq_array(seqs):
         return (C.c_void_p * max(len(seqs), 1))(*[s.h for s in seqs])

@@ -96,6 +96,8 @@ SIGNATURES = {
     "etc_gguf_load_tensor_device": (None, [P, P, I64, P, C.c_uint64, P]),
     "etc_tp_unique_id": (None, [P]),
     "etc_decoder_set_tensor_parallel": (None, [P, I, I, P]),
+    "etc_decoder_tp_peer_export": (None, [P, P]),
+    "etc_decoder_tp_peer_import": (None, [P, P]),
     "etc_decoder_finalize": (None, [P]),
     "etc_decoder_execute": (None, [P, P, P, I, P, I, P, P]),
     "etc_decoder_execute_sampled": (None, [P, P, P, I, P, I, P, P]),

@@ -88,6 +88,13 @@ struct etc_decoder {
   // tensor parallel: this decoder holds one rank's shard of every projection (rows of q/k/v/gate/up, columns of o/down)
   TpComm* tp = nullptr;
   int tp_rank = 0, tp_world = 1;
+  // optional all-reduce over peer memory instead of NCCL: one exported region per rank
+  // [flags 256 B][epoch + done counters 256 B][partial 0][partial 1], opened by every peer through CUDA IPC
+  unsigned char* tp_region = nullptr;
+  size_t tp_partial_bytes = 0;
+  void* tp_peer_base[kMaxTpRanks] = {};
+  PeerView tp_view{};
+  bool tp_peer = false;
 };
 
 namespace {
@@ -207,9 +214,18 @@ etc_status run_linear(StepContext& s, const BoundWeight& raw, etc_qweight* tiled
 // a partial sum: rank 0 adds the residual, the others overwrite, and the all-reduce leaves the same hidden state on
 // every rank (crates/runtime-cpu has no counterpart: the reference is single-device).
 etc_status project_into_hidden(StepContext& s, const BoundWeight& raw, etc_qweight* tiled_w, const float* x, int64_t rows,
-                               const __half* xh_ready) {
+                               const __half* xh_ready, int buffer) {
   etc_decoder* d = s.dec;
   const bool sharded = d->tp_world > 1;
+  if (sharded && d->tp_peer) {
+    // every rank leaves its partial sum in its exported buffer; the all-reduce kernel adds all of them onto hidden
+    float* partial = reinterpret_cast<float*>(d->tp_region + 512 + (size_t)buffer * d->tp_partial_bytes);
+    ETC_TRY(run_linear(s, raw, tiled_w, x, rows, partial, ETC_EPILOGUE_NONE, nullptr, xh_ready));
+    ETC_CUDA(launch_tp_allreduce(d->tp_view, buffer, d->hidden, (size_t)rows * d->cfg.d_model, reinterpret_cast<uint32_t*>(d->tp_region + 256),
+                                 reinterpret_cast<uint32_t*>(d->tp_region + 260), d->rt->d_status, d->rt->stream));
+    ++s.launches;
+    return ETC_OK;
+  }
   const int epilogue = sharded && d->tp_rank != 0 ? ETC_EPILOGUE_NONE : ETC_EPILOGUE_RESIDUAL;
   ETC_TRY(run_linear(s, raw, tiled_w, x, rows, d->hidden, epilogue, epilogue == ETC_EPILOGUE_RESIDUAL ? d->hidden : nullptr, xh_ready));
   if (sharded) {
@@ -284,7 +300,7 @@ etc_status enqueue_step(StepContext& s) {
       s.launches += 8;
     }
     const bool xh_o = xh && fast_attention;
-    ETC_TRY(project_into_hidden(s, d->wo[li], d->tiled ? d->t_o[li] : nullptr, d->attl, rows, xh_o ? d->xh_att : nullptr));
+    ETC_TRY(project_into_hidden(s, d->wo[li], d->tiled ? d->t_o[li] : nullptr, d->attl, rows, xh_o ? d->xh_att : nullptr, 0));
     if (xh) ETC_CUDA(launch_rmsnorm_xh8(d->hidden, (const float*)d->ffn_norm[li].d_raw, c.rms_eps, rows, c.d_model, d->xh_norm, stream));
     else ETC_CUDA(launch_rmsnorm(d->hidden, (const float*)d->ffn_norm[li].d_raw, c.rms_eps, rows, c.d_model, d->normed, stream));
     ++s.launches;
@@ -297,7 +313,7 @@ etc_status enqueue_step(StepContext& s) {
       ETC_CUDA(launch_swiglu(d->g, d->u, rows * c.ffn, d->act, c.exact, stream));
       ++s.launches;
     }
-    ETC_TRY(project_into_hidden(s, d->down[li], d->tiled ? d->t_down[li] : nullptr, d->act, rows, xh ? d->xh_act : nullptr));
+    ETC_TRY(project_into_hidden(s, d->down[li], d->tiled ? d->t_down[li] : nullptr, d->act, rows, xh ? d->xh_act : nullptr, 1));
   }
   const bool xh_head = d->xh_path && T == 1;
   if (xh_head) ETC_CUDA(launch_rmsnorm_xh8(d->hidden, (const float*)d->out_norm.d_raw, c.rms_eps, rows, c.d_model, d->xh_norm, stream));
@@ -569,6 +585,62 @@ etc_status etc_decoder_set_tensor_parallel(etc_decoder* dec, int rank, int world
   return ETC_OK;
 }
 
+etc_status etc_decoder_tp_peer_export(etc_decoder* dec, uint8_t* out_handle) {
+  if (!valid_decoder(dec)) return fail(ETC_INVALID_HANDLE, "decoder handle is invalid or destroyed");
+  if (!out_handle) return fail(ETC_INVALID_ARGUMENT, "tensor parallel: the handle buffer is null");
+  if (!dec->finalized) return fail(ETC_COMPILATION, "tensor parallel: finalize the decoder before exporting its exchange region");
+  if (dec->tp_world < 2 || dec->tp_world > kMaxTpRanks)
+    return fail(ETC_UNSUPPORTED, "tensor parallel: the peer-memory all-reduce serves 2 to " + std::to_string(kMaxTpRanks) + " ranks");
+  etc_runtime* rt = dec->rt;
+  ETC_TRY(activate(rt));
+  if (!dec->tp_region) {
+    const size_t floats = (size_t)dec->cfg.batch * dec->max_advance * dec->cfg.d_model;
+    dec->tp_partial_bytes = (floats * sizeof(float) + 255) & ~(size_t)255;
+    const size_t bytes = 512 + 2 * dec->tp_partial_bytes;
+    ETC_TRY(rt->device_alloc(bytes, (void**)&dec->tp_region));
+    ETC_CUDA(cudaMemsetAsync(dec->tp_region, 0, bytes, rt->stream));
+    ETC_CUDA(cudaStreamSynchronize(rt->stream));  // peers may write flags as soon as they hold the handle
+  }
+  cudaIpcMemHandle_t handle;
+  ETC_CUDA(cudaIpcGetMemHandle(&handle, dec->tp_region));
+  static_assert(sizeof(handle) == 64, "CUDA IPC handles are 64 bytes");
+  std::memcpy(out_handle, &handle, sizeof(handle));
+  return ETC_OK;
+}
+
+etc_status etc_decoder_tp_peer_import(etc_decoder* dec, const uint8_t* handles) {
+  if (!valid_decoder(dec)) return fail(ETC_INVALID_HANDLE, "decoder handle is invalid or destroyed");
+  if (!handles) return fail(ETC_INVALID_ARGUMENT, "tensor parallel: the handle table is null");
+  if (!dec->tp_region) return fail(ETC_COMPILATION, "tensor parallel: export this rank's region before importing the peers'");
+  if (dec->tp_peer) return fail(ETC_COMPILATION, "tensor parallel: the peers are already mapped");
+  etc_runtime* rt = dec->rt;
+  ETC_TRY(activate(rt));
+  PeerView view{};
+  view.rank = dec->tp_rank;
+  view.world = dec->tp_world;
+  for (int r = 0; r < dec->tp_world; ++r) {
+    unsigned char* base = dec->tp_region;
+    if (r != dec->tp_rank) {
+      cudaIpcMemHandle_t handle;
+      std::memcpy(&handle, handles + (size_t)r * 64, sizeof(handle));
+      void* mapped = nullptr;
+      ETC_CUDA(cudaIpcOpenMemHandle(&mapped, handle, cudaIpcMemLazyEnablePeerAccess));
+      dec->tp_peer_base[r] = mapped;
+      base = static_cast<unsigned char*>(mapped);
+    }
+    view.flags[r] = reinterpret_cast<uint32_t*>(base);
+    view.partial[r][0] = reinterpret_cast<const float*>(base + 512);
+    view.partial[r][1] = reinterpret_cast<const float*>(base + 512 + dec->tp_partial_bytes);
+  }
+  dec->tp_view = view;
+  dec->tp_peer = true;
+  if (dec->step_graph) {  // captured with the NCCL all-reduces
+    cudaGraphExecDestroy(dec->step_graph);
+    dec->step_graph = nullptr;
+  }
+  return ETC_OK;
+}
+
 etc_status etc_decoder_finalize(etc_decoder* dec) {
   if (!valid_decoder(dec)) return fail(ETC_INVALID_HANDLE, "decoder handle is invalid or destroyed");
   etc_runtime* rt = dec->rt;
@@ -694,6 +766,9 @@ etc_status etc_decoder_destroy(etc_decoder* dec) {
   cudaStreamSynchronize(rt->stream);
   if (dec->step_graph) cudaGraphExecDestroy(dec->step_graph);
   tp_comm_destroy(dec->tp);
+  for (int r = 0; r < kMaxTpRanks; ++r)
+    if (dec->tp_peer_base[r]) cudaIpcCloseMemHandle(dec->tp_peer_base[r]);
+  if (dec->tp_region) rt->device_free(dec->tp_region);
   auto free_bound = [&](BoundWeight& w) { if (w.d_raw) rt->device_free(w.d_raw); w.d_raw = nullptr; };
   free_bound(dec->tok_embd); free_bound(dec->out_norm); free_bound(dec->head);
   for (auto* list : {&dec->attn_norm, &dec->ffn_norm, &dec->wq, &dec->wk, &dec->wv, &dec->wo, &dec->gate, &dec->up, &dec->down})

@@ -245,11 +245,33 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
   float best = -INFINITY;
   long long arg = 0x7fffffffffffffffll;
   long long bad = 0x7fffffffffffffffll;
-  for (int64_t i = threadIdx.x; i < vocab; i += blockDim.x) {
-    const float v = row[i];
+  auto take = [&](float v, int64_t i) {
     if (!isfinite(v)) bad = min(bad, (long long)i);
     if (v > best) { best = v; arg = i; }
+  };
+  int64_t head = 0;
+  if ((vocab & 3) == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    // 16-byte loads, four in flight per thread; a thread's indices still ascend, so strict > keeps the lowest index
+    const float4* row4 = reinterpret_cast<const float4*>(row);
+    const int64_t n4 = vocab >> 2;
+    int64_t i = threadIdx.x;
+    for (; i + 3 * (int64_t)blockDim.x < n4; i += 4 * (int64_t)blockDim.x) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = row4[i + u * (int64_t)blockDim.x];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int64_t base = (i + u * (int64_t)blockDim.x) << 2;
+        take(v[u].x, base); take(v[u].y, base + 1); take(v[u].z, base + 2); take(v[u].w, base + 3);
+      }
+    }
+    for (; i < n4; i += blockDim.x) {
+      const float4 v = row4[i];
+      take(v.x, i << 2); take(v.y, (i << 2) + 1); take(v.z, (i << 2) + 2); take(v.w, (i << 2) + 3);
+    }
+    head = vocab;
   }
+  for (int64_t i = head + threadIdx.x; i < vocab; i += blockDim.x) take(row[i], i);
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) {
     const float ov = __shfl_xor_sync(0xffffffffu, best, off);

@@ -101,6 +101,17 @@ cudaError_t launch_qlinear_tiled(const TiledWeight& w, const float* x, int64_t v
 cudaError_t launch_rmsnorm_xh8(const float* x, const float* weight, double eps, int64_t rows, int64_t n, __half* out_xh,
                                cudaStream_t stream);
 
+// ---- tensor-parallel all-reduce over peer memory (tp_kernels.cu) -----------------------------
+constexpr int kMaxTpRanks = 8;
+struct PeerView {
+  const float* partial[kMaxTpRanks][2];  // every rank's two partial-sum buffers (own: local memory, others: peer mappings)
+  uint32_t* flags[kMaxTpRanks];          // every rank's flag array [kMaxTpRanks]; entry r is written by rank r
+  int rank, world;
+};
+// hidden[0, count) += sum over ranks of partial[rank][buffer][0, count); count is a multiple of 4.
+cudaError_t launch_tp_allreduce(const PeerView& view, int buffer, float* hidden, size_t count, uint32_t* epoch_counter,
+                                uint32_t* done_counter, DeviceStatus* status, cudaStream_t stream);
+
 // ---- dense / elementwise (elementwise.cu) --------------------------------------------------
 cudaError_t launch_linear_f32(const float* x, int64_t m, int64_t k, const float* w, int64_t n, const float* bias,
                               float* out, cudaStream_t stream);

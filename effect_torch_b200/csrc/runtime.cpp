@@ -135,6 +135,8 @@ etc_status etc_runtime::check_status() {
     return fail(ETC_EXECUTION, "quantized_embedding: index " + std::to_string(seen.value) + " is outside 0.." + std::to_string(seen.bound));
   if (seen.code == kStatusNonFiniteLogit)
     return fail(ETC_EXECUTION, "sample: logit " + std::to_string(seen.value) + " is not finite");
+  if (seen.code == 3) return fail(ETC_EXECUTION, "quantized_linear: a pipeline wait inside the kernel ran out; the launch gave up");
+  if (seen.code == 4) return fail(ETC_EXECUTION, "tensor parallel: a peer never arrived at the all-reduce; the launch gave up");
   return fail(ETC_EXECUTION, "device reported status " + std::to_string(seen.code));
 }
 

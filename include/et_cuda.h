@@ -335,6 +335,13 @@ ETC_API etc_status etc_gguf_load_tensor_device(etc_runtime* rt, const etc_gguf* 
  * captured step graph as well); rank 0 alone adds the residual. world == 1 is accepted and changes nothing. */
 ETC_API etc_status etc_tp_unique_id(uint8_t* out_id_128_bytes);
 ETC_API etc_status etc_decoder_set_tensor_parallel(etc_decoder* dec, int rank, int world, const uint8_t* id_128_bytes);
+/* Optional, after etc_decoder_set_tensor_parallel and etc_decoder_finalize: replace the NCCL all-reduce by a one-shot
+ * kernel over peer memory (CUDA IPC, plain peer loads over NVLink, 2..8 ranks on one node). Every rank exports a
+ * 64-byte handle of its exchange region, the host gathers the handles of all ranks into a table [world][64] (own slot
+ * ignored) and every rank imports it. The kernel's wait for its peers is bounded: a rank that never arrives turns
+ * into ETC_EXECUTION at the next synchronising call, not into a hang. */
+ETC_API etc_status etc_decoder_tp_peer_export(etc_decoder* dec, uint8_t* out_handle_64_bytes);
+ETC_API etc_status etc_decoder_tp_peer_import(etc_decoder* dec, const uint8_t* handles_world_x_64_bytes);
 
 ETC_API etc_status etc_decoder_create(etc_runtime* rt, const etc_decoder_config* config, etc_decoder** out);
 ETC_API etc_status etc_decoder_destroy(etc_decoder* dec);

@@ -44,53 +44,66 @@ def main():
     dist.broadcast(ident, src=0)
     dec.set_tensor_parallel(rank, world, bytes(ident.tolist()))
     pool = et.NativeKvPool(rt, lcfg["layers"], lcfg["kv_heads"], lcfg["head_dim"], max_tokens, 16, et.KV_F16)
-    seqs = [pool.makeSequence() for _ in range(B)]
-
     failures = []
-    if rank == 0:
-        odec = helpers.oracle_decoder(cfg, weights, batch=B)
-        opool = orc.Pool(cfg["layers"], cfg["kv_heads"], cfg["head_dim"], max_tokens, 16, orc.F16)
-        oseqs = [opool.make_sequence() for _ in range(B)]
-    rng = np.random.default_rng(2)
-    for advance in (8, 5, 1, 1, 1):
-        toks = rng.integers(0, cfg["vocab"], size=(B, advance)).astype(np.uint32)
-        gl = dec.execute(pool, seqs, toks)
-        if rank == 0:
-            ol, _ = odec.execute(opool, oseqs, toks)
-            err = helpers.rel_err(gl, ol)
-            if err > LOGIT_TOL:
-                failures.append(f"advance {advance}: logits rel err {err:.3e}")
-        mine = torch.from_numpy(gl.copy())
+    odec = helpers.oracle_decoder(cfg, weights, batch=B) if rank == 0 else None
+
+    def same_on_all_ranks(array):
+        mine = torch.from_numpy(np.ascontiguousarray(array).copy())
         everyone = [torch.empty_like(mine) for _ in range(world)]
         dist.all_gather(everyone, mine)
-        if any(not torch.equal(everyone[0], e) for e in everyone[1:]):
-            failures.append(f"advance {advance}: ranks hold different logits")
+        return all(torch.equal(everyone[0], e) for e in everyone[1:])
 
-    # step by step, then the same continuation device-resident on a second set of sequences
-    first = rng.integers(0, cfg["vocab"], size=B).astype(np.uint32)
-    prompt = rng.integers(0, cfg["vocab"], size=(B, 8)).astype(np.uint32)
-    outs = []
-    for mode in ("stepwise", "resident"):
-        s2 = [pool.makeSequence() for _ in range(B)]
-        dec.execute(pool, s2, prompt)
-        if mode == "stepwise":
-            tok, out = first, []
-            for _ in range(12):
-                tok = dec.executeSampled(pool, s2, tok[:, None])
-                out.append(tok)
-            outs.append(np.stack(out))
-        else:
-            out, _ = dec.generate_greedy(pool, s2, first, 12)
-            outs.append(out)
-        for s in s2:
+    def run_checks(tag):
+        seqs = [pool.makeSequence() for _ in range(B)]
+        if rank == 0:
+            opool = orc.Pool(cfg["layers"], cfg["kv_heads"], cfg["head_dim"], max_tokens, 16, orc.F16)
+            oseqs = [opool.make_sequence() for _ in range(B)]
+        rng = np.random.default_rng(2)
+        for advance in (8, 5, 1, 1, 1):
+            toks = rng.integers(0, cfg["vocab"], size=(B, advance)).astype(np.uint32)
+            gl = dec.execute(pool, seqs, toks)
+            if rank == 0:
+                ol, _ = odec.execute(opool, oseqs, toks)
+                err = helpers.rel_err(gl, ol)
+                if err > LOGIT_TOL:
+                    failures.append(f"{tag}: advance {advance}: logits rel err {err:.3e}")
+            if not same_on_all_ranks(gl):
+                failures.append(f"{tag}: advance {advance}: ranks hold different logits")
+        for s in seqs:
             s.release()
-    if not np.array_equal(outs[0], outs[1]):
-        failures.append("device-resident generation differs from step-by-step execution")
-    mine = torch.from_numpy(outs[1].astype(np.int64))
-    everyone = [torch.empty_like(mine) for _ in range(world)]
-    dist.all_gather(everyone, mine)
-    if any(not torch.equal(everyone[0], e) for e in everyone[1:]):
-        failures.append("ranks generated different tokens")
+        # step by step, then the same continuation device-resident on a second set of sequences
+        first = rng.integers(0, cfg["vocab"], size=B).astype(np.uint32)
+        prompt = rng.integers(0, cfg["vocab"], size=(B, 8)).astype(np.uint32)
+        outs = []
+        for mode in ("stepwise", "resident"):
+            s2 = [pool.makeSequence() for _ in range(B)]
+            dec.execute(pool, s2, prompt)
+            if mode == "stepwise":
+                tok, out = first, []
+                for _ in range(12):
+                    tok = dec.executeSampled(pool, s2, tok[:, None])
+                    out.append(tok)
+                outs.append(np.stack(out))
+            else:
+                out, _ = dec.generate_greedy(pool, s2, first, 12)
+                outs.append(out)
+            for s in s2:
+                s.release()
+        if not np.array_equal(outs[0], outs[1]):
+            failures.append(f"{tag}: device-resident generation differs from step-by-step execution")
+        if not same_on_all_ranks(outs[1].astype(np.int64)):
+            failures.append(f"{tag}: ranks generated different tokens")
+        return outs[1]
+
+    tokens_nccl = run_checks("nccl all-reduce")
+    # the same again with the one-shot all-reduce over peer memory
+    mine = torch.frombuffer(bytearray(dec.peer_exchange_handle()), dtype=torch.uint8).clone()
+    table = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(table, mine)
+    dec.use_peer_allreduce([bytes(t.tolist()) for t in table])
+    tokens_peer = run_checks("peer-memory all-reduce")
+    if world == 2 and not np.array_equal(tokens_nccl, tokens_peer):  # two ranks: both paths add in the same order
+        failures.append("the two all-reduce paths generated different tokens")
 
     flag = torch.tensor([len(failures)])
     dist.all_reduce(flag)
