@@ -296,6 +296,130 @@ def time_dominant_kernel(rt, et, torch, model, vectors, iters=40):
     return ms, algorithmic
 
 
+def run_attention_microbench(args):
+    """Paged-attention decode alone (the survey's microbench shape): 64 sequences, 32 query / 8 KV heads of 128, f16 pool of
+    65 536 pages x 16 tokens, contexts ~U[128, 4096] (rounded to 64), one query token per sequence. Prints one JSON line."""
+    import torch
+    import effect_torch_b200 as et
+
+    torch.cuda.set_device(0)
+    rt = et.Runtime(0)
+    B, Hq, Hkv, D, pages = 64, 32, 8, 128, 65536
+    rng = np.random.default_rng(1)
+    ctx = np.sort((rng.integers(128, 4097, size=B) // 64) * 64)[::-1].copy()
+    pool = et.NativeKvPool(rt, 1, Hkv, D, pages * BLOCK, BLOCK, et.KV_F16)
+    seqs = [pool.makeSequence() for _ in range(B)]
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(1)
+    chunk = 64
+    kv = torch.randn((B, Hkv, chunk, D), generator=gen, device="cuda", dtype=torch.float32)
+    torch.cuda.synchronize()
+    filler = np.arange(chunk, dtype=np.uint32)
+    for start in range(0, int(ctx.max()), chunk):  # sequences are sorted by length: the first `active` still grow
+        active = int((ctx > start).sum())
+        rt.kv_append_into(pool, 0, seqs[:active], B, active, chunk, kv, kv, chunk)
+        for s in seqs[:active]:
+            s.commit(filler)
+    q = torch.randn((B, Hq, D), generator=gen, device="cuda", dtype=torch.float32)
+    k1 = torch.randn((B, Hkv, D), generator=gen, device="cuda", dtype=torch.float32)
+    out = torch.empty((B, Hq, D), device="cuda", dtype=torch.float32)
+    torch.cuda.synchronize()
+    scale = 1.0 / np.sqrt(D)
+    stream = torch.cuda.ExternalStream(rt.stream)
+    start_ev, stop_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(0)
+    for _ in range(max(args.warmup, 3)):
+        rt.kv_attention_decode_into(pool, 0, seqs, B, B, q, k1, k1, Hq, scale, out=out)
+    rt.synchronize()
+    sampler.start()
+    iters = max(args.steps, 20)
+    with torch.cuda.stream(stream):
+        start_ev.record()
+        for _ in range(iters):
+            rt.kv_attention_decode_into(pool, 0, seqs, B, B, q, k1, k1, Hq, scale, out=out)
+        stop_ev.record()
+    rt.synchronize()
+    clocks = sampler.stop()
+    ms = start_ev.elapsed_time(stop_ev) / iters
+    total_ctx = int(ctx.sum()) + B
+    algorithmic = total_ctx * 2 * Hkv * D * 2 + B * Hq * D * 8 + 4 * int(np.ceil((ctx + 1) / BLOCK).sum())
+    peaks, peak_kind = measured_peaks()
+    achieved = algorithmic / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "paged attention decode, HBM GB/s vs peak", "value": achieved, "unit": "GB/s", "n_gpus": 1, "steps": iters,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "dtype": "f16 KV, f16 MMA operands, f32 softmax/accumulate",
+        "data": "synthetic", "config": {"workload": f"paged attention microbench: {B} sequences, {Hq} query / {Hkv} KV heads x {D}, contexts "
+                                                    f"{int(ctx.min())}..{int(ctx.max())} (sum {total_ctx}), {pages} pages x {BLOCK} tokens, "
+                                                    "each step appends one token per sequence (host lane/table upload included) and attends",
+                                        "l2": f"KV read per step {algorithmic / 1e6:.0f} MB exceeds the 126 MB L2"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                     "traffic": None, "peak_kind": peak_kind, "kernel": "attention_mma_kernel<128,f16> + merge + kv append",
+                     "algorithmic_bytes_per_launch": algorithmic},
+        "clocks": clocks}), flush=True)
+
+
+def run_linear_microbench(args):
+    """The quantized-matmul microbench shapes: Q4_0 and Q8_0, [4096x4096], [14336x4096], [4096x14336], 1 / 8 / 64 / 512 input
+    vectors, each timed through graph replays over enough weight copies to exceed L2. One JSON line with a table."""
+    import torch
+    import effect_torch_b200 as et
+
+    torch.cuda.set_device(0)
+    rt = et.Runtime(0)
+    peaks, peak_kind = measured_peaks()
+    rows_out = []
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(2)
+    stream = torch.cuda.ExternalStream(rt.stream)
+    for codec, bb, name in ((Q4_0, 18, "Q4_0"), (8, 34, "Q8_0")):
+        for n, k in ((4096, 4096), (14336, 4096), (4096, 14336)):
+            packed_bytes = n * (k // 32) * bb
+            copies = max(2, int(np.ceil(300e6 / packed_bytes)))
+            weights = []
+            for _ in range(copies):
+                w = torch.randn((n, k), generator=gen, device="cuda", dtype=torch.float32) * 0.02
+                p = torch.empty((n, k // 32 * bb), dtype=torch.uint8, device="cuda")
+                torch.cuda.synchronize()
+                rt.quantize_into(codec, w, n, k, p)
+                rt.synchronize()
+                weights.append(et.QWeight(rt, codec, [p], [n], k))
+                del w, p
+            for m in (1, 8, 64, 512):
+                x = torch.randn((m, k), generator=gen, device="cuda", dtype=torch.float32)
+                out = torch.empty((m, n), device="cuda", dtype=torch.float32)
+                need = weights[0].scratch_bytes(m)
+                scratch = torch.empty(max(need, 4), dtype=torch.uint8, device="cuda")
+                torch.cuda.synchronize()
+                for i in range(copies):
+                    weights[i].linear_into(x, m, out, scratch=scratch, scratch_bytes=need)
+                rt.synchronize()
+                iters = 2 * copies
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    for i in range(iters):
+                        weights[i % copies].linear_into(x, m, out, scratch=scratch, scratch_bytes=need)
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                with torch.cuda.stream(stream):
+                    graph.replay()
+                    a.record()
+                    graph.replay()
+                    graph.replay()
+                    b.record()
+                rt.synchronize()
+                us = a.elapsed_time(b) / (2 * iters) * 1e3
+                algorithmic = packed_bytes + 4 * m * k + 4 * m * n
+                flops = 2.0 * m * n * k
+                rows_out.append({"codec": name, "rows": n, "columns": k, "vectors": m, "us": us, "gbs": algorithmic / us / 1e3,
+                                 "hbm_frac": algorithmic / us / 1e3 / peaks["hbm_gbs"], "tflops": flops / us / 1e6})
+                del graph
+            for w in weights:
+                w.close()
+            torch.cuda.empty_cache()
+    print(json.dumps({"metric": "quantized linear microbench, HBM GB/s and TFLOP/s per shape", "unit": "GB/s", "n_gpus": 1,
+                      "data": "synthetic", "config": {"workload": "tcgen05 dequant linear, graph replays over > 300 MB of weight copies per shape"},
+                      "peak": peaks, "peak_kind": peak_kind, "table": rows_out}), flush=True)
+
+
 def run_gpu_arm(args, rank, world):
     import torch
     import torch.distributed as dist
@@ -326,6 +450,11 @@ def run_gpu_arm(args, rank, world):
             ident = torch.frombuffer(bytearray(et.tensor_parallel_id()), dtype=torch.uint8).cuda()
         dist.broadcast(ident, src=0)
         dec.set_tensor_parallel(rank, world, bytes(ident.cpu().tolist()))
+        if args.tp_allreduce == "peer":  # one-shot kernel over peer memory instead of NCCL
+            mine = torch.frombuffer(bytearray(dec.peer_exchange_handle()), dtype=torch.uint8).cuda()
+            table = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(table, mine)
+            dec.use_peer_allreduce([bytes(t.cpu().tolist()) for t in table])
     pool = et.NativeKvPool(rt, model["layers"], model["kv_heads"], model["head_dim"], max_tokens, BLOCK, et.KV_F16)
     rng = np.random.default_rng(3 if tp else 3 + rank)  # tensor-parallel ranks decode the same sequences
     prompts = rng.integers(0, model["vocab"], size=(BATCH, PROMPT)).astype(np.uint32)
@@ -420,7 +549,7 @@ def run_gpu_arm(args, rank, world):
                                    f"{K} greedy steps, f16 KV 16-token pages",
                        "global_batch": BATCH * jobs,
                        "parallelism": "single GPU" if world == 1 else (f"tp{world}: rows of q/k/v/gate/up and columns of o/down cut over the ranks, "
-                                                                       f"NCCL all-reduce of [batch, d_model] f32 after o and down, head replicated"
+                                                                       f"{args.tp_allreduce} all-reduce of [batch, d_model] f32 after o and down, head replicated"
                                                                        if tp else f"{world} independent replicas"),
                        "l2": "per-step working set (weights 4.2 GB + KV) exceeds the 126 MB L2; no flush needed"},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -452,7 +581,12 @@ def main():
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--tp-allreduce", default="peer", choices=["peer", "nccl"],
+                    help="--parallelism tp: all-reduce by the library's one-shot peer-memory kernel or by NCCL")
     ap.add_argument("--layers", type=int, default=0, help="debug: fewer layers than the 8B shape (the result is then not a bench value)")
+    ap.add_argument("--workload", default="decode", choices=["decode", "attention", "linear"],
+                    help="decode: the headline 8B-shape decode step (the bench contract); attention / linear: the paged-attention and "
+                         "quantized-matmul microbenchmarks, one extra JSON line each (single GPU)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--parallelism", default="replicas", choices=["replicas", "tp"],
                     help="N > 1: N independent replicas, each decoding its own batch (weak scaling; the 8B shape fits one GPU), or "
@@ -466,6 +600,10 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
         run_reference_arm(args, rank)
+        return
+    if args.workload != "decode":
+        if rank == 0:
+            (run_attention_microbench if args.workload == "attention" else run_linear_microbench)(args)
         return
     run_gpu_arm(args, rank, world)
 

@@ -84,6 +84,13 @@ struct etc_decoder {
   // what the captured graph baked in: it is re-captured when any of these changes
   int graph_active = 0, graph_pages = 0, graph_ctx = 0;
   const etc_pool* graph_pool = nullptr;
+  // execute / executeSampled with one token per sequence replay a captured step as well: the launch list only depends
+  // on the number of active lanes and on an upper bound of the pages attended over (rounded up to 8 pages, so one
+  // capture serves 128 steps); everything else a step reads is in device buffers the host refreshes before the launch
+  cudaGraphExec_t exec_graph = nullptr;
+  int exec_graph_active = 0, exec_graph_pages = 0, exec_graph_launches = 0;
+  const etc_pool* exec_graph_pool = nullptr;
+  bool ran_eagerly = false;  // kernels configure their attributes on their first eager launch
 
   // tensor parallel: this decoder holds one rank's shard of every projection (rows of q/k/v/gate/up, columns of o/down)
   TpComm* tp = nullptr;
@@ -473,8 +480,47 @@ etc_status execute_impl(etc_decoder* dec, etc_pool* pool, etc_seq* const* seqs, 
     if (st != ETC_OK) return abort_with(st);
   }
   etc_status st = upload_step_inputs(dec, advance);
-  if (st == ETC_OK) st = enqueue_step(ctx);
   if (st != ETC_OK) return abort_with(st);
+  if (advance == 1 && dec->ran_eagerly && !uses_exact_attention(dec, pool, 1)) {
+    const int bucket = (ctx.max_pages + 7) / 8 * 8;
+    if (dec->exec_graph && (dec->exec_graph_active != active || dec->exec_graph_pages != bucket || dec->exec_graph_pool != pool)) {
+      cudaGraphExecDestroy(dec->exec_graph);
+      dec->exec_graph = nullptr;
+    }
+    if (!dec->exec_graph) {
+      StepContext sc = ctx;
+      sc.launches = 0;
+      sc.max_pages = bucket;
+      cudaGraph_t graph = nullptr;
+      cudaError_t ce = cudaStreamBeginCapture(rt->stream, cudaStreamCaptureModeThreadLocal);
+      if (ce == cudaSuccess) {
+        st = enqueue_step(sc);
+        const cudaError_t ce2 = cudaStreamEndCapture(rt->stream, &graph);
+        if (st == ETC_OK && ce2 != cudaSuccess) ce = ce2;
+      }
+      if (st == ETC_OK && ce == cudaSuccess) ce = cudaGraphInstantiate(&dec->exec_graph, graph, 0);
+      if (graph) cudaGraphDestroy(graph);
+      if (st != ETC_OK) return abort_with(st);
+      if (ce != cudaSuccess) {
+        fail(ETC_EXECUTION, std::string("kv run: graph capture failed: ") + cudaGetErrorString(ce));
+        return abort_with(ETC_EXECUTION);
+      }
+      dec->exec_graph_active = active;
+      dec->exec_graph_pages = bucket;
+      dec->exec_graph_pool = pool;
+      dec->exec_graph_launches = sc.launches;
+    }
+    const cudaError_t ce = cudaGraphLaunch(dec->exec_graph, rt->stream);
+    if (ce != cudaSuccess) {
+      fail(ETC_EXECUTION, std::string("kv run: graph launch failed: ") + cudaGetErrorString(ce));
+      return abort_with(ETC_EXECUTION);
+    }
+    ctx.launches = dec->exec_graph_launches;
+  } else {
+    st = enqueue_step(ctx);
+    if (st != ETC_OK) return abort_with(st);
+    if (advance == 1) dec->ran_eagerly = true;
+  }
   dec->launches_last_step = ctx.launches;
   rt->launches += (uint64_t)ctx.launches;
   const etc_decoder_config& c = dec->cfg;
@@ -582,6 +628,10 @@ etc_status etc_decoder_set_tensor_parallel(etc_decoder* dec, int rank, int world
     cudaGraphExecDestroy(dec->step_graph);
     dec->step_graph = nullptr;
   }
+  if (dec->exec_graph) {
+    cudaGraphExecDestroy(dec->exec_graph);
+    dec->exec_graph = nullptr;
+  }
   return ETC_OK;
 }
 
@@ -637,6 +687,10 @@ etc_status etc_decoder_tp_peer_import(etc_decoder* dec, const uint8_t* handles) 
   if (dec->step_graph) {  // captured with the NCCL all-reduces
     cudaGraphExecDestroy(dec->step_graph);
     dec->step_graph = nullptr;
+  }
+  if (dec->exec_graph) {
+    cudaGraphExecDestroy(dec->exec_graph);
+    dec->exec_graph = nullptr;
   }
   return ETC_OK;
 }
@@ -765,6 +819,7 @@ etc_status etc_decoder_destroy(etc_decoder* dec) {
   ETC_TRY(activate(rt));
   cudaStreamSynchronize(rt->stream);
   if (dec->step_graph) cudaGraphExecDestroy(dec->step_graph);
+  if (dec->exec_graph) cudaGraphExecDestroy(dec->exec_graph);
   tp_comm_destroy(dec->tp);
   for (int r = 0; r < kMaxTpRanks; ++r)
     if (dec->tp_peer_base[r]) cudaIpcCloseMemHandle(dec->tp_peer_base[r]);
