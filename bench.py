@@ -420,6 +420,100 @@ def run_linear_microbench(args):
                       "peak": peaks, "peak_kind": peak_kind, "table": rows_out}), flush=True)
 
 
+MODEL_70B = dict(layers=80, d_model=8192, q_heads=64, kv_heads=8, head_dim=128, ffn=28672, vocab=128256, rms_eps=1e-5,
+                 rope_theta=500000.0)
+
+
+def run_tp_70b(args, rank, world):
+    """Llama-3-70B-shape Q4_0 decode, batch 64, contexts ~U[1024, 8192], tensor parallel over `world` ranks. KV is written
+    straight into the pages (N(0,1) rows; a decode benchmark needs no real prefill) and the steps run device-resident."""
+    import torch
+    import torch.distributed as dist
+    import effect_torch_b200 as et
+    from effect_torch_b200 import tensor_parallel
+
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    rt = et.Runtime(local)
+    full = dict(MODEL_70B)
+    if args.layers:
+        full["layers"] = args.layers
+    model = tensor_parallel.local_config(full, world)
+    B, K, W, chunk = 64, args.steps, args.warmup, 256
+    rng = np.random.default_rng(4)  # the same contexts and tokens on every rank
+    ctx = np.sort((rng.integers(1024, 8193, size=B) // chunk) * chunk)[::-1].copy()
+    per_seq = ((int(ctx.max()) + W + K + BLOCK) // BLOCK + 1) * BLOCK
+    max_tokens = ((int(ctx.sum()) + B * (W + K + 2 * BLOCK)) // BLOCK + B) * BLOCK
+    dec = build_decoder(rt, et, torch, model, B, max_tokens, seed=40 + rank, shared_seed=4)
+    if world > 1:
+        ident = torch.zeros(128, dtype=torch.uint8, device="cuda")
+        if rank == 0:
+            ident = torch.frombuffer(bytearray(et.tensor_parallel_id()), dtype=torch.uint8).cuda()
+        dist.broadcast(ident, src=0)
+        dec.set_tensor_parallel(rank, world, bytes(ident.cpu().tolist()))
+        if args.tp_allreduce == "peer":
+            mine = torch.frombuffer(bytearray(dec.peer_exchange_handle()), dtype=torch.uint8).cuda()
+            table = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(table, mine)
+            dec.use_peer_allreduce([bytes(t.cpu().tolist()) for t in table])
+    pool = et.NativeKvPool(rt, model["layers"], model["kv_heads"], model["head_dim"], max_tokens, BLOCK, et.KV_F16)
+    seqs = [pool.makeSequence() for _ in range(B)]
+    kv = torch.randn((B, model["kv_heads"], chunk, model["head_dim"]), device="cuda", dtype=torch.float32)
+    torch.cuda.synchronize()
+    filler = np.arange(chunk, dtype=np.uint32)
+    for start in range(0, int(ctx.max()), chunk):  # sorted by length: the first `active` sequences still grow
+        active = int((ctx > start).sum())
+        for layer in range(model["layers"]):
+            rt.kv_append_into(pool, layer, seqs[:active], B, active, chunk, kv, kv, chunk)
+        for s in seqs[:active]:
+            s.commit(filler)
+    del kv
+    tok = rng.integers(0, full["vocab"], size=B).astype(np.uint32)
+    sampler = ClockSampler(local)
+    if W:
+        out, _ = dec.generate_greedy(pool, seqs, tok, W)
+        tok = out[-1]
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler.start()
+    out, device_ms = dec.generate_greedy(pool, seqs, tok, K)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    times = torch.tensor([device_ms / 1000.0], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        mine = torch.from_numpy(out.astype(np.int64)).cuda()
+        lo, hi = mine.clone(), mine.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        if not torch.equal(lo, hi):
+            raise RuntimeError("tensor-parallel ranks generated different tokens")
+    seconds = float(times.cpu()[0])
+    if rank == 0:
+        mean_ctx = float(ctx.mean()) + W + (K + 1) / 2.0
+        step_bytes = algorithmic_bytes_per_step(full, B, mean_ctx)
+        peaks, peak_kind = measured_peaks()
+        print(json.dumps({
+            "metric": "decode tokens/s, Llama-3-70B-shape Q4_0 batch 64, tensor parallel", "value": B * K / seconds, "unit": "tokens/s",
+            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": 1000.0 * seconds / K, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f16 MMA operands, f32 accumulate (Q4_0 weights, f16 KV)", "data": "synthetic",
+            "config": {"workload": f"llama3-70b-shape Q4_0 paged decode: {full['layers']} layers, batch {B}, contexts {int(ctx.min())}.."
+                                   f"{int(ctx.max())} (mean {ctx.mean():.0f}) written directly into the pages, {K} greedy steps",
+                       "global_batch": B, "parallelism": f"tp{world}, {args.tp_allreduce if world > 1 else 'no'} all-reduce, head replicated"},
+            "gpu_launches": dec.diagnostics()["launches_per_step"] * K,
+            "step_roofline": {"algorithmic_bytes_per_step_all_ranks": step_bytes, "achieved_gbs_per_rank": step_bytes / world * K / seconds / 1e9,
+                              "frac_of_" + peak_kind: step_bytes / world * K / seconds / 1e9 / peaks["hbm_gbs"]},
+            "clocks": clocks}), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def run_gpu_arm(args, rank, world):
     import torch
     import torch.distributed as dist
@@ -584,9 +678,10 @@ def main():
     ap.add_argument("--tp-allreduce", default="peer", choices=["peer", "nccl"],
                     help="--parallelism tp: all-reduce by the library's one-shot peer-memory kernel or by NCCL")
     ap.add_argument("--layers", type=int, default=0, help="debug: fewer layers than the 8B shape (the result is then not a bench value)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "attention", "linear"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "attention", "linear", "decode-70b"],
                     help="decode: the headline 8B-shape decode step (the bench contract); attention / linear: the paged-attention and "
-                         "quantized-matmul microbenchmarks, one extra JSON line each (single GPU)")
+                         "quantized-matmul microbenchmarks, one extra JSON line each (single GPU); decode-70b: the 70B shape, batch 64, "
+                         "tensor parallel over --gpus ranks")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--parallelism", default="replicas", choices=["replicas", "tp"],
                     help="N > 1: N independent replicas, each decoding its own batch (weak scaling; the 8B shape fits one GPU), or "
@@ -600,6 +695,9 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
         run_reference_arm(args, rank)
+        return
+    if args.workload == "decode-70b":
+        run_tp_70b(args, rank, world)
         return
     if args.workload != "decode":
         if rank == 0:
