@@ -106,3 +106,75 @@ class GgufFile:
         nbytes = device_tensor.numel() * device_tensor.element_size()
         _check(self.L.etc_gguf_load_tensor_device(rt.h, self.h, index, _ptr(device_tensor), nbytes, C.cast(C.byref(flag), C.c_void_p)))
         return device_tensor
+
+
+# ---- a Llama-shaped decoder straight from a GGUF file ---------------------------------------------------------------
+LLAMA_TENSORS = {  # GGUF tensor name pattern -> weight slot of the decoder (include/et_cuda.h etc_weight_slot)
+    "attn_norm": 1, "attn_q": 2, "attn_k": 3, "attn_v": 4, "attn_output": 5, "ffn_norm": 6, "ffn_gate": 7, "ffn_up": 8, "ffn_down": 9,
+}
+
+
+def llama_geometry(f: GgufFile) -> dict:
+    """Decoder geometry from the `<arch>.*` metadata keys of a Llama-family file and the embedding tensor's shape."""
+    meta = {m["key"]: m.get("value") for m in f.metadata if not m["array"]}
+    arch = f.architecture
+
+    def need(key):
+        if f"{arch}.{key}" not in meta:
+            raise BackendError(9, f"gguf: metadata key {arch}.{key} is missing")
+        return meta[f"{arch}.{key}"]
+
+    d_model, q_heads = int(need("embedding_length")), int(need("attention.head_count"))
+    embd = f.tensors[f.index("token_embd.weight")]
+    return dict(layers=int(need("block_count")), d_model=d_model, q_heads=q_heads,
+                kv_heads=int(meta.get(f"{arch}.attention.head_count_kv", q_heads)),
+                head_dim=int(meta.get(f"{arch}.attention.key_length", d_model // q_heads)), ffn=int(need("feed_forward_length")),
+                vocab=int(embd.logical_shape[0]), rms_eps=float(meta.get(f"{arch}.attention.layer_norm_rms_epsilon", 1e-5)),
+                rope_theta=float(meta.get(f"{arch}.rope.freq_base", 10000.0)))
+
+
+def load_llama_decoder(rt, path: str, *, batch: int, max_tokens: int, block_size: int = 16, kv_dtype=None, exact: bool = False,
+                       max_advance: int = 1, rope_layout=None, window=None):
+    """Builds an `Executable` whose weights are streamed from `path` into device memory (packed tensors stay packed and are
+    re-tiled on the device at finalize). Tensors: token_embd, blk.N.{attn_norm, attn_q, attn_k, attn_v, attn_output,
+    ffn_norm, ffn_gate, ffn_up, ffn_down}, output_norm, output (falls back to token_embd when the head is tied).
+    Returns (executable, geometry)."""
+    import torch
+
+    from . import HALF_SPLIT, KV_F16, W_HEAD, W_OUT_NORM, W_TOK_EMBD, Executable
+
+    f = GgufFile(path)
+    try:
+        g = llama_geometry(f)
+        dec = Executable(rt, layers=g["layers"], d_model=g["d_model"], q_heads=g["q_heads"], kv_heads=g["kv_heads"], head_dim=g["head_dim"],
+                         ffn=g["ffn"], vocab=g["vocab"], rms_eps=g["rms_eps"], rope_theta=g["rope_theta"],
+                         rope_layout=HALF_SPLIT if rope_layout is None else rope_layout, window=window, batch=batch, max_tokens=max_tokens,
+                         block_size=block_size, kv_dtype=KV_F16 if kv_dtype is None else kv_dtype, exact=exact, max_advance=max_advance)
+        names = {t.name: i for i, t in enumerate(f.tensors)}
+
+        def bind(slot, layer, name):
+            if name not in names:
+                raise BackendError(9, f'gguf: tensor "{name}" is missing')
+            info = f.tensors[names[name]]
+            if info.codec == 0:
+                buf = torch.empty(info.byte_len // 4, dtype=torch.float32, device=f"cuda:{rt.device}")
+            else:
+                buf = torch.empty(info.byte_len, dtype=torch.uint8, device=f"cuda:{rt.device}")
+            torch.cuda.synchronize()
+            f.load_tensor_device(rt, names[name], buf)
+            if len(info.logical_shape) == 1:
+                dec.set_weight(slot, layer, buf, codec=0, rows=1, columns=info.logical_shape[0])
+            else:
+                rows = int(np.prod(info.logical_shape[:-1]))
+                dec.set_weight(slot, layer, buf, codec=info.codec, rows=rows, columns=info.logical_shape[-1])
+
+        bind(W_TOK_EMBD, 0, "token_embd.weight")
+        for layer in range(g["layers"]):
+            for stem, slot in LLAMA_TENSORS.items():
+                bind(slot, layer, f"blk.{layer}.{stem}.weight")
+        bind(W_OUT_NORM, 0, "output_norm.weight")
+        bind(W_HEAD, 0, "output.weight" if "output.weight" in names else "token_embd.weight")
+        dec.finalize()
+        return dec, g
+    finally:
+        f.close()
