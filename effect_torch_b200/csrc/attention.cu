@@ -294,6 +294,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attention_mma_kernel(AttnArgs
   constexpr int DTILES = D / 8;    // n-tiles of the PV product
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
+  // the kernel that follows (split merge or output projection) may be launched under this one's tail
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int split = blockIdx.x, kv_head = blockIdx.y, lane_id = blockIdx.z;
   const LaneInfo info = a.lanes[lane_id];
   const int G = a.q_heads / a.kv_heads;
@@ -492,6 +494,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attention_mma_kernel(AttnArgs
 // Combines split partials: out = sum_s 2^(m_s - m) O_s / sum_s 2^(m_s - m) l_s. grid (Hq, B).
 __global__ void attention_merge_kernel(const float* __restrict__ partial, int q_heads, int splits, int D,
                                        float* __restrict__ out, __half* __restrict__ out_xh) {
+  // the output projection that follows may start its set-up and weight loads now
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int head = blockIdx.x, lane_id = blockIdx.y;
   const float* base = partial + ((size_t)lane_id * q_heads + head) * splits * (D + 2);
   float m = -INFINITY;

@@ -94,6 +94,8 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const float* __restrict__ 
 template <bool XH>
 __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ weight,
                                                            double eps, int n, float* __restrict__ out, __half* __restrict__ out_xh) {
+  // the linear that follows may start its set-up and weight loads now (it waits for this kernel before reading the norm)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   __shared__ double partial[8];
   __shared__ double scale_s;
   const int row = blockIdx.x;

@@ -188,6 +188,7 @@ __global__ void __launch_bounds__(UmmaCfg<NV>::kThreads) qlinear_umma_kernel(Umm
     // ------------------------------------------------------------------ epilogue (first group)
     if (group != 0) ok = false;
     if (ok) ok = mbar_wait(done, 0, abort_flag);
+    grid_dependency_wait();  // outputs, residual and scratch may still be in use by the kernel before this one
     ok = __all_sync(0xffffffffu, ok);  // warp-uniform: the epilogue below shuffles across the warp
     if (ok) {
       tc_fence_after();
@@ -233,6 +234,7 @@ __global__ void __launch_bounds__(UmmaCfg<NV>::kThreads) qlinear_umma_kernel(Umm
   } else if (warp == 4 * kGroups) {
     // ------------------------------------------------------------------ activation loader (one lane)
     if (lane == 0) {
+      grid_dependency_wait();  // the activations come from the kernel before this one; weights do not, the dequant warps run ahead
       int issued = 0;
       for (int i = 0; i < nstages; ++i) {
         const int s = i % kStages;
@@ -366,8 +368,19 @@ cudaError_t launch_umma_pass(const UmmaArgs& args, int tiles, int splits, cudaSt
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  kernel<<<dim3((unsigned)tiles, (unsigned)splits), UmmaCfg<NV>::kThreads, smem, stream>>>(args);
-  return cudaGetLastError();
+  // launched so that it may start under the tail of the previous kernel: set-up, weight loads and their expansion do not
+  // depend on it (the kernel waits on the grid dependency before it reads activations or writes results)
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3((unsigned)tiles, (unsigned)splits);
+  config.blockDim = dim3((unsigned)UmmaCfg<NV>::kThreads);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, kernel, args);
 }
 
 }  // namespace
