@@ -15,6 +15,7 @@
 
 #include <algorithm>
 
+#include "chain.cuh"
 #include "kernels.h"
 
 namespace etc {
@@ -294,8 +295,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attention_mma_kernel(AttnArgs
   constexpr int DTILES = D / 8;    // n-tiles of the PV product
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
-  // the kernel that follows (split merge or output projection) may be launched under this one's tail
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  chain_release();  // the next kernel of the step may be scheduled; it waits for this one before touching memory
+  chain_wait();
   const int split = blockIdx.x, kv_head = blockIdx.y, lane_id = blockIdx.z;
   const LaneInfo info = a.lanes[lane_id];
   const int G = a.q_heads / a.kv_heads;
@@ -494,8 +495,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attention_mma_kernel(AttnArgs
 // Combines split partials: out = sum_s 2^(m_s - m) O_s / sum_s 2^(m_s - m) l_s. grid (Hq, B).
 __global__ void attention_merge_kernel(const float* __restrict__ partial, int q_heads, int splits, int D,
                                        float* __restrict__ out, __half* __restrict__ out_xh) {
-  // the output projection that follows may start its set-up and weight loads now
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  chain_release();  // the next kernel of the step may be scheduled; it waits for this one before touching memory
+  chain_wait();
   const int head = blockIdx.x, lane_id = blockIdx.y;
   const float* base = partial + ((size_t)lane_id * q_heads + head) * splits * (D + 2);
   float m = -INFINITY;
@@ -557,8 +558,7 @@ static cudaError_t launch_attention_mma_t(const PoolView& pool, const AttnArgs& 
     configured = true;
   }
   dim3 grid((unsigned)splits, (unsigned)pool.kv_heads, (unsigned)batch);
-  kernel<<<grid, kAttnWarps * 32, smem, stream>>>(args);
-  return cudaGetLastError();
+  return launch_chained(kernel, grid, dim3(kAttnWarps * 32), smem, stream, args);
 }
 
 cudaError_t launch_attention_mma(const PoolView& pool, const float* q, const LaneInfo* lanes, const int* tables,
@@ -583,8 +583,8 @@ cudaError_t launch_attention_mma(const PoolView& pool, const float* q, const Lan
   if (launches) ++*launches;
   if (plan.splits > 1) {
     dim3 grid((unsigned)q_heads, (unsigned)batch);
-    attention_merge_kernel<<<grid, std::min(128, pool.head_dim), 0, stream>>>(scratch, q_heads, plan.splits, pool.head_dim, out, out_xh);
-    e = cudaGetLastError();
+    e = launch_chained(attention_merge_kernel, grid, dim3((unsigned)std::min(128, pool.head_dim)), 0, stream, (const float*)scratch, q_heads, plan.splits,
+                       pool.head_dim, out, out_xh);
     if (e != cudaSuccess) return e;
     if (launches) ++*launches;
   }
@@ -605,6 +605,8 @@ __device__ __forceinline__ void pool_store(const PoolView& p, void* slab, size_t
 __global__ void rope_append_kernel(PoolView pool, const float* __restrict__ qkv, const LaneInfo* __restrict__ lanes,
                                    const int* __restrict__ tables, const double* __restrict__ inv_freq, int layout,
                                    int q_heads, float* __restrict__ q_out) {
+  chain_release();  // the next kernel of the step may be scheduled; it waits for this one before touching memory
+  chain_wait();
   const int head = blockIdx.x, lane_id = blockIdx.y;
   const LaneInfo info = lanes[lane_id];
   const int D = pool.head_dim, half = D / 2;
@@ -644,13 +646,15 @@ cudaError_t launch_rope_append(const PoolView& pool, const float* qkv, const Lan
                                cudaStream_t stream) {
   if (batch == 0) return cudaSuccess;
   dim3 grid((unsigned)(q_heads + 2 * pool.kv_heads), (unsigned)batch);
-  rope_append_kernel<<<grid, std::max(32, pool.head_dim / 2), 0, stream>>>(pool, qkv, lanes, tables, inv_freq, layout, q_heads, q_out);
-  return cudaGetLastError();
+  return launch_chained(rope_append_kernel, grid, dim3((unsigned)std::max(32, pool.head_dim / 2)), 0, stream, pool, qkv, lanes, tables, inv_freq, layout, q_heads,
+                        q_out);
 }
 
 __global__ void record_step_kernel(const uint32_t* __restrict__ tokens, uint32_t* __restrict__ ids,
                                    uint32_t* __restrict__ history, int* step_counter, LaneInfo* lanes, int64_t* cursors,
                                    int batch, long long window) {
+  chain_release();  // the next kernel of the step may be scheduled; it waits for this one before touching memory
+  chain_wait();
   const int step = *step_counter;
   for (int i = threadIdx.x; i < batch; i += blockDim.x) {
     const uint32_t tok = tokens[i];
@@ -667,8 +671,7 @@ __global__ void record_step_kernel(const uint32_t* __restrict__ tokens, uint32_t
 }
 cudaError_t launch_record_step(const uint32_t* tokens, uint32_t* ids, uint32_t* history, int* step_counter, LaneInfo* lanes,
                                int64_t* cursors, int batch, long long window, cudaStream_t stream) {
-  record_step_kernel<<<1, 128, 0, stream>>>(tokens, ids, history, step_counter, lanes, cursors, batch, window);
-  return cudaGetLastError();
+  return launch_chained(record_step_kernel, dim3(1), dim3(128), 0, stream, tokens, ids, history, step_counter, lanes, cursors, batch, window);
 }
 
 // Debug/test read-back of logical token rows (row = block*block_size + offset) as f32

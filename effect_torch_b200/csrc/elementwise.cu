@@ -11,6 +11,7 @@
 
 #include <algorithm>
 
+#include "chain.cuh"
 #include "kernels.h"
 
 namespace etc {
@@ -94,8 +95,8 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const float* __restrict__ 
 template <bool XH>
 __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ weight,
                                                            double eps, int n, float* __restrict__ out, __half* __restrict__ out_xh) {
-  // the linear that follows may start its set-up and weight loads now (it waits for this kernel before reading the norm)
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  chain_release();  // the next kernel of the step may be scheduled; it waits for this one before touching memory
+  chain_wait();
   __shared__ double partial[8];
   __shared__ double scale_s;
   const int row = blockIdx.x;
@@ -150,7 +151,7 @@ cudaError_t launch_rmsnorm(const float* x, const float* weight, double eps, int6
                            cudaStream_t stream) {
   if (rows == 0) return cudaSuccess;
   if (rmsnorm_fast_ok(x, weight, n) && ((uintptr_t)out % 16) == 0)
-    rmsnorm_rows_kernel<false><<<(unsigned)rows, 256, 0, stream>>>(x, weight, eps, (int)n, out, nullptr);
+    return launch_chained(rmsnorm_rows_kernel<false>, dim3((unsigned)rows), dim3(256), 0, stream, x, weight, eps, (int)n, out, (__half*)nullptr);
   else
     rmsnorm_kernel<<<(unsigned)rows, 256, 0, stream>>>(x, weight, eps, n, out);
   return cudaGetLastError();
@@ -160,8 +161,7 @@ cudaError_t launch_rmsnorm_xh8(const float* x, const float* weight, double eps, 
                                cudaStream_t stream) {
   if (rows == 0) return cudaSuccess;
   if (rows > 32 || n % 8 != 0 || !rmsnorm_fast_ok(x, weight, n)) return cudaErrorInvalidValue;
-  rmsnorm_rows_kernel<true><<<(unsigned)rows, 256, 0, stream>>>(x, weight, eps, (int)n, nullptr, out_xh);
-  return cudaGetLastError();
+  return launch_chained(rmsnorm_rows_kernel<true>, dim3((unsigned)rows), dim3(256), 0, stream, x, weight, eps, (int)n, (float*)nullptr, out_xh);
 }
 
 // --------------------------------------------------------------------------------------------
@@ -240,6 +240,8 @@ cudaError_t launch_add(const float* a, const float* b, int64_t n, float* out, cu
 // --------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, int64_t vocab,
                                                       uint32_t* __restrict__ tokens, DeviceStatus* status) {
+  chain_release();  // the next kernel of the step may be scheduled; it waits for this one before touching memory
+  chain_wait();
   __shared__ float best_v[32];
   __shared__ long long best_i[32];
   __shared__ long long bad_s[32];
@@ -311,14 +313,15 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
 cudaError_t launch_argmax(const float* logits, int64_t rows, int64_t vocab, uint32_t* tokens, DeviceStatus* status,
                           cudaStream_t stream) {
   if (rows == 0) return cudaSuccess;
-  argmax_kernel<<<(unsigned)rows, 1024, 0, stream>>>(logits, vocab, tokens, status);
-  return cudaGetLastError();
+  return launch_chained(argmax_kernel, dim3((unsigned)rows), dim3(1024), 0, stream, logits, vocab, tokens, status);
 }
 
 // Dense f32 embedding gather with the same bounds rule as the quantized embedding.
 template <typename Index>
 __global__ void embedding_f32_kernel(const Index* __restrict__ indexes, int64_t count, const float* __restrict__ table,
                                      int64_t rows, int64_t columns, float* __restrict__ out, DeviceStatus* status) {
+  chain_release();  // the next kernel of the step may be scheduled; it waits for this one before touching memory
+  chain_wait();
   const int64_t i = blockIdx.y;
   const long long row = (long long)indexes[i];
   if (row < 0 || row >= rows) {
@@ -336,9 +339,9 @@ cudaError_t launch_embedding_f32(const void* indexes, int index_is_i64, int64_t 
   if (count == 0) return cudaSuccess;
   dim3 grid((unsigned)std::min<int64_t>((columns + 255) / 256, 32), (unsigned)count);
   if (index_is_i64)
-    embedding_f32_kernel<long long><<<grid, 256, 0, stream>>>((const long long*)indexes, count, table, rows, columns, out, status);
+    return launch_chained(embedding_f32_kernel<long long>, grid, dim3(256), 0, stream, (const long long*)indexes, count, table, rows, columns, out, status);
   else
-    embedding_f32_kernel<unsigned int><<<grid, 256, 0, stream>>>((const unsigned int*)indexes, count, table, rows, columns, out, status);
+    return launch_chained(embedding_f32_kernel<unsigned int>, grid, dim3(256), 0, stream, (const unsigned int*)indexes, count, table, rows, columns, out, status);
   return cudaGetLastError();
 }
 

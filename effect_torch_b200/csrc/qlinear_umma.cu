@@ -21,11 +21,14 @@
 // Every mbarrier wait is bounded: on expiry the thread raises the abort flag and the status word, all
 // roles fall through to the teardown, TMEM is freed and the kernel returns.
 //
-// Roofline: HBM-bound for NV <= 32 (bytes = rows*K/32*{18,34} + 2*NV*K + 4*V*rows); tensor-bound for NV = 256.
+// Roofline: algorithmic bytes = rows*K/32*{18,34} + 2*NV*K + 4*V*rows. At NV <= 32 the kernel is bound by the rate at
+// which an SM retires tcgen05.mma instructions (about 100 cycles each for any N <= 128, i.e. 2048 weights per 100
+// cycles), below what HBM could feed; at NV = 256 it is tensor-throughput bound.
 #include <cuda_fp16.h>
 
 #include <algorithm>
 
+#include "chain.cuh"
 #include "kernels.h"
 #include "tc05.cuh"
 
@@ -36,10 +39,8 @@ namespace {
 constexpr int kUmmaRows = 128;
 constexpr int kDequantThreads = 128;  // one TMEM lane (weight row) per thread of a dequant group
 
-// Pipeline shape per vector padding. For decode (NV = 32) the kernel is bound by how fast warps can expand
-// packed weights, so two groups of four dequant warps alternate over short stages (2 blocks) in a 6-deep
-// ring and two CTAs share an SM (256 TMEM columns each); for wide passes the MMAs dominate and one group
-// with 4-block stages suffices.
+// Pipeline shape: stages of four 32-value blocks in a ring of three (TMEM for the expanded weights, shared memory for
+// the activations); for NV <= 64 two CTAs share an SM (256 TMEM columns each) and overlap each other's phases.
 template <int NV>
 struct UmmaCfg {
   static constexpr int kGroups = 1;
@@ -87,6 +88,7 @@ __global__ void __launch_bounds__(UmmaCfg<NV>::kThreads) qlinear_umma_kernel(Umm
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 3 * kStages + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
+  chain_release();  // the next kernel (split-K sum or the step's next operator) may be scheduled already; it waits for this one
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile = blockIdx.x, split = blockIdx.y;
   const int kb0 = split * a.blocks_per_split;
@@ -188,7 +190,7 @@ __global__ void __launch_bounds__(UmmaCfg<NV>::kThreads) qlinear_umma_kernel(Umm
     // ------------------------------------------------------------------ epilogue (first group)
     if (group != 0) ok = false;
     if (ok) ok = mbar_wait(done, 0, abort_flag);
-    grid_dependency_wait();  // outputs, residual and scratch may still be in use by the kernel before this one
+    chain_wait();  // outputs, residual and scratch may still be in use by the kernel before this one
     ok = __all_sync(0xffffffffu, ok);  // warp-uniform: the epilogue below shuffles across the warp
     if (ok) {
       tc_fence_after();
@@ -234,7 +236,7 @@ __global__ void __launch_bounds__(UmmaCfg<NV>::kThreads) qlinear_umma_kernel(Umm
   } else if (warp == 4 * kGroups) {
     // ------------------------------------------------------------------ activation loader (one lane)
     if (lane == 0) {
-      grid_dependency_wait();  // the activations come from the kernel before this one; weights do not, the dequant warps run ahead
+      chain_wait();  // the activations come from the kernel before this one; weights do not, the dequant warps run ahead
       int issued = 0;
       for (int i = 0; i < nstages; ++i) {
         const int s = i % kStages;
@@ -368,19 +370,8 @@ cudaError_t launch_umma_pass(const UmmaArgs& args, int tiles, int splits, cudaSt
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  // launched so that it may start under the tail of the previous kernel: set-up, weight loads and their expansion do not
-  // depend on it (the kernel waits on the grid dependency before it reads activations or writes results)
-  cudaLaunchConfig_t config = {};
-  config.gridDim = dim3((unsigned)tiles, (unsigned)splits);
-  config.blockDim = dim3((unsigned)UmmaCfg<NV>::kThreads);
-  config.dynamicSmemBytes = smem;
-  config.stream = stream;
-  cudaLaunchAttribute attribute[1];
-  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attribute[0].val.programmaticStreamSerializationAllowed = 1;
-  config.attrs = attribute;
-  config.numAttrs = 1;
-  return cudaLaunchKernelEx(&config, kernel, args);
+  // chained: set-up, weight loads and their expansion do not depend on the previous kernel and start under its tail
+  return launch_chained(kernel, dim3((unsigned)tiles, (unsigned)splits), dim3((unsigned)UmmaCfg<NV>::kThreads), smem, stream, args);
 }
 
 }  // namespace

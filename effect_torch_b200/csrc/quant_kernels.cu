@@ -10,6 +10,7 @@
 #include <algorithm>
 
 #include "codecs.cuh"
+#include "chain.cuh"
 #include "kernels.h"
 
 namespace etc {
@@ -599,6 +600,8 @@ __global__ void __launch_bounds__(kTiledWarps * 32, 2) qlinear_tiled_kernel(Tile
 __global__ void qlinear_reduce_kernel(const float* __restrict__ scratch, int splits, int vpad, int vectors, int rows,
                                       int rows_padded, const float* __restrict__ bias, const float* __restrict__ residual,
                                       int epilogue, float* __restrict__ out, __half* __restrict__ out_xh) {
+  chain_release();  // the next kernel of the step may be scheduled; it waits for this one before touching memory
+  chain_wait();
   const int out_cols = epilogue == ETC_EPILOGUE_SWIGLU ? rows / 2 : rows;
   const int64_t total = (int64_t)vectors * out_cols;
   for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
@@ -668,9 +671,8 @@ cudaError_t launch_qlinear_reduce(const float* scratch, int splits, int vpad, in
   const int64_t total = (int64_t)vectors * out_cols;
   if (total == 0) return cudaSuccess;
   const unsigned grid = (unsigned)std::min<int64_t>((total + 255) / 256, 148 * 8);
-  qlinear_reduce_kernel<<<grid, 256, 0, stream>>>(scratch, splits, vpad, vectors, rows, rows_padded, bias, residual, epilogue, out,
-                                                  vectors <= 32 ? out_xh : nullptr);
-  return cudaGetLastError();
+  return launch_chained(qlinear_reduce_kernel, dim3(grid), dim3(256), 0, stream, scratch, splits, vpad, vectors, rows, rows_padded, bias, residual,
+                        epilogue, out, vectors <= 32 ? out_xh : (__half*)nullptr);
 }
 
 // Scratch layout of the tcgen05 path: [xh8 activations, rounded to 256 B][split-K partials].

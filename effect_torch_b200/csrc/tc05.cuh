@@ -175,13 +175,6 @@ __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
 }
-// Programmatic dependent launch. A kernel launched with the programmatic-serialization attribute may start while its
-// predecessor in the stream is still running (once every CTA of the predecessor has called grid_launch_dependents or
-// exited); grid_dependency_wait blocks until the predecessor has completed and its writes are visible. Every thread
-// calls it before it touches anything an earlier kernel produces or still reads; both are no-ops in a plain launch.
-__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-
 // Makes this thread's earlier generic-proxy writes to shared memory visible to the async proxy (tensor core reads).
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
