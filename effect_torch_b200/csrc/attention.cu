@@ -270,7 +270,8 @@ struct AttnArgs {
   const LaneInfo* lanes;
   const int* tables;
   float* out;              // [B, Hq, D] f32 (splits == 1)
-  __half* out_xh;          // optional f16 copy of out in [Hq*D/8][32][8] order (B <= 32): the o-projection's B operand
+  __half* out_xh;          // optional f16 copy of out in [Hq*D/8][out_xh_nv][8] order: the o-projection's B operand
+  int out_xh_nv;
   float* partial;          // [B, Hq, splits, D + 2] f32: O unnormalised, then m (log2 domain), l
   int q_heads, kv_heads;
   int pages_per_split;
@@ -482,7 +483,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attention_mma_kernel(AttnArgs
       a.out[((size_t)lane_id * a.q_heads + head) * D + d] = val;
       if (a.out_xh) {
         const int k = head * D + d;
-        a.out_xh[((size_t)(k >> 3) * 32 + lane_id) * 8 + (k & 7)] = __float2half_rn(fminf(fmaxf(val, -65504.f), 65504.f));
+        a.out_xh[((size_t)(k >> 3) * a.out_xh_nv + lane_id) * 8 + (k & 7)] = __float2half_rn(fminf(fmaxf(val, -65504.f), 65504.f));
       }
     } else {
       float* dst = a.partial + (((size_t)lane_id * a.q_heads + head) * nsplits + split) * (D + 2);
@@ -494,7 +495,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attention_mma_kernel(AttnArgs
 
 // Combines split partials: out = sum_s 2^(m_s - m) O_s / sum_s 2^(m_s - m) l_s. grid (Hq, B).
 __global__ void attention_merge_kernel(const float* __restrict__ partial, int q_heads, int splits, int D,
-                                       float* __restrict__ out, __half* __restrict__ out_xh) {
+                                       float* __restrict__ out, __half* __restrict__ out_xh, int xh_nv) {
   chain_release();  // the next kernel of the step may be scheduled; it waits for this one before touching memory
   chain_wait();
   const int head = blockIdx.x, lane_id = blockIdx.y;
@@ -513,7 +514,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ partial, int q_
     out[((size_t)lane_id * q_heads + head) * D + d] = val;
     if (out_xh) {
       const int k = head * D + d;
-      out_xh[((size_t)(k >> 3) * 32 + lane_id) * 8 + (k & 7)] = __float2half_rn(fminf(fmaxf(val, -65504.f), 65504.f));
+      out_xh[((size_t)(k >> 3) * xh_nv + lane_id) * 8 + (k & 7)] = __float2half_rn(fminf(fmaxf(val, -65504.f), 65504.f));
     }
   }
 }
@@ -563,11 +564,12 @@ static cudaError_t launch_attention_mma_t(const PoolView& pool, const AttnArgs& 
 
 cudaError_t launch_attention_mma(const PoolView& pool, const float* q, const LaneInfo* lanes, const int* tables,
                                  int batch, int q_heads, double scale, long long op_window, float* out,
-                                 const AttnPlan& plan, float* scratch, cudaStream_t stream, int* launches, __half* out_xh) {
+                                 const AttnPlan& plan, float* scratch, cudaStream_t stream, int* launches, __half* out_xh, int xh_nv) {
   if (batch == 0) return cudaSuccess;
-  if (batch > 32) out_xh = nullptr;
+  if (batch > xh_nv) out_xh = nullptr;
   AttnArgs args;
   args.out_xh = out_xh;
+  args.out_xh_nv = xh_nv;
   args.k = pool.k; args.v = pool.v; args.q = q; args.lanes = lanes; args.tables = tables; args.out = out;
   args.partial = scratch; args.q_heads = q_heads; args.kv_heads = pool.kv_heads;
   args.pages_per_split = plan.pages_per_split;
@@ -584,7 +586,7 @@ cudaError_t launch_attention_mma(const PoolView& pool, const float* q, const Lan
   if (plan.splits > 1) {
     dim3 grid((unsigned)q_heads, (unsigned)batch);
     e = launch_chained(attention_merge_kernel, grid, dim3((unsigned)std::min(128, pool.head_dim)), 0, stream, (const float*)scratch, q_heads, plan.splits,
-                       pool.head_dim, out, out_xh);
+                       pool.head_dim, out, out_xh, xh_nv);
     if (e != cudaSuccess) return e;
     if (launches) ++*launches;
   }

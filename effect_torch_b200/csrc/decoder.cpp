@@ -54,6 +54,7 @@ struct etc_decoder {
   // f16 activation hand-off between kernels of the one-token fast path ([K/8][32][8] order, rows >= batch stay zero)
   __half *xh_norm = nullptr, *xh_att = nullptr, *xh_act = nullptr;
   bool xh_path = false;
+  int xh_nv = 32;  // row stride of the hand-off layout: the batch padded to 32, 64 or 128
   float* lin_scratch = nullptr;
   size_t lin_scratch_bytes = 0;
   float* attn_scratch = nullptr;
@@ -199,7 +200,7 @@ etc_status run_linear(StepContext& s, const BoundWeight& raw, etc_qweight* tiled
   cudaStream_t stream = d->rt->stream;
   if (tiled_w) {
     ETC_CUDA(launch_qlinear_tiled(tiled_w->tiled, x, vectors, nullptr, residual, epilogue, out, d->lin_scratch,
-                                  d->rt->d_status, d->rt->sm_count, stream, &s.launches, xh_ready, out_xh));
+                                  d->rt->d_status, d->rt->sm_count, stream, &s.launches, xh_ready, out_xh, d->xh_nv));
     return ETC_OK;
   }
   float* target = epilogue == ETC_EPILOGUE_RESIDUAL ? d->proj : out;
@@ -268,7 +269,7 @@ etc_status enqueue_step(StepContext& s) {
     const PoolView view = s.pool->view(l);
     // one-token steps of a tiled model hand activations from kernel to kernel as f16 in the tensor-core operand order
     const bool xh = d->xh_path && T == 1;
-    if (xh) ETC_CUDA(launch_rmsnorm_xh8(d->hidden, (const float*)d->attn_norm[li].d_raw, c.rms_eps, rows, c.d_model, d->xh_norm, stream));
+    if (xh) ETC_CUDA(launch_rmsnorm_xh8(d->hidden, (const float*)d->attn_norm[li].d_raw, c.rms_eps, rows, c.d_model, d->xh_norm, stream, d->xh_nv));
     else ETC_CUDA(launch_rmsnorm(d->hidden, (const float*)d->attn_norm[li].d_raw, c.rms_eps, rows, c.d_model, d->normed, stream));
     ++s.launches;
     const float *qp, *kp, *vp;
@@ -293,7 +294,7 @@ etc_status enqueue_step(StepContext& s) {
       ++s.launches;
       const AttnPlan plan = plan_attention(B, Hq, Hkv, D, std::max(1, s.max_pages), d->rt->sm_count);
       ETC_CUDA(launch_attention_mma(view, d->qr, d->d_lanes, d->d_tables, B, Hq, scale, c.window, d->attl, plan,
-                                    d->attn_scratch, stream, &s.launches, xh ? d->xh_att : nullptr));
+                                    d->attn_scratch, stream, &s.launches, xh ? d->xh_att : nullptr, d->xh_nv));
     } else {
       ETC_CUDA(launch_heads_first(qp, d->qh, B, T, Hq, D, stride_q, stream));
       ETC_CUDA(launch_heads_first(kp, d->kh, B, T, Hkv, D, stride_kv, stream));
@@ -308,7 +309,7 @@ etc_status enqueue_step(StepContext& s) {
     }
     const bool xh_o = xh && fast_attention;
     ETC_TRY(project_into_hidden(s, d->wo[li], d->tiled ? d->t_o[li] : nullptr, d->attl, rows, xh_o ? d->xh_att : nullptr, 0));
-    if (xh) ETC_CUDA(launch_rmsnorm_xh8(d->hidden, (const float*)d->ffn_norm[li].d_raw, c.rms_eps, rows, c.d_model, d->xh_norm, stream));
+    if (xh) ETC_CUDA(launch_rmsnorm_xh8(d->hidden, (const float*)d->ffn_norm[li].d_raw, c.rms_eps, rows, c.d_model, d->xh_norm, stream, d->xh_nv));
     else ETC_CUDA(launch_rmsnorm(d->hidden, (const float*)d->ffn_norm[li].d_raw, c.rms_eps, rows, c.d_model, d->normed, stream));
     ++s.launches;
     if (d->tiled) {
@@ -323,7 +324,7 @@ etc_status enqueue_step(StepContext& s) {
     ETC_TRY(project_into_hidden(s, d->down[li], d->tiled ? d->t_down[li] : nullptr, d->act, rows, xh ? d->xh_act : nullptr, 1));
   }
   const bool xh_head = d->xh_path && T == 1;
-  if (xh_head) ETC_CUDA(launch_rmsnorm_xh8(d->hidden, (const float*)d->out_norm.d_raw, c.rms_eps, rows, c.d_model, d->xh_norm, stream));
+  if (xh_head) ETC_CUDA(launch_rmsnorm_xh8(d->hidden, (const float*)d->out_norm.d_raw, c.rms_eps, rows, c.d_model, d->xh_norm, stream, d->xh_nv));
   else ETC_CUDA(launch_rmsnorm(d->hidden, (const float*)d->out_norm.d_raw, c.rms_eps, rows, c.d_model, d->normed, stream));
   ++s.launches;
   // LastTokenRow then the head: only the selected row of each lane reaches the head projection
@@ -782,15 +783,18 @@ etc_status etc_decoder_finalize(etc_decoder* dec) {
           need = std::max(need, tiled_scratch_bytes(w->tiled, std::min<int64_t>(v, (int64_t)R), rt->sm_count));
     for (int64_t v : probes)
       need = std::max(need, tiled_scratch_bytes(dec->t_head->tiled, std::min<int64_t>(v, c.batch), rt->sm_count));
-    dec->xh_path = c.batch <= 32 && c.d_model % 8 == 0 && c.ffn % 8 == 0 && (c.q_heads * c.head_dim) % 8 == 0 &&
-                   c.d_model <= 8192 && dec->t_head->tiled.layout != kLayoutMma16;
+    dec->xh_nv = hand_off_stride(c.batch) ? hand_off_stride(c.batch) : 32;
+    dec->xh_path = hand_off_stride(c.batch) != 0 && c.d_model % 8 == 0 && c.ffn % 8 == 0 && (c.q_heads * c.head_dim) % 8 == 0 &&
+                   c.d_model <= 8192 &&
+                   (dec->t_head->tiled.layout == kLayoutUmma128 || (dec->t_head->tiled.layout == kLayoutStream256 && c.batch <= 32));
     if (dec->xh_path) {
-      ETC_TRY(dalloc(dec, &dec->xh_norm, (size_t)c.d_model * 32));
-      ETC_TRY(dalloc(dec, &dec->xh_att, qw * 32));
-      ETC_TRY(dalloc(dec, &dec->xh_act, (size_t)c.ffn * 32));
-      ETC_CUDA(cudaMemsetAsync(dec->xh_norm, 0, (size_t)c.d_model * 32 * sizeof(__half), rt->stream));
-      ETC_CUDA(cudaMemsetAsync(dec->xh_att, 0, qw * 32 * sizeof(__half), rt->stream));
-      ETC_CUDA(cudaMemsetAsync(dec->xh_act, 0, (size_t)c.ffn * 32 * sizeof(__half), rt->stream));
+      const size_t nv = (size_t)dec->xh_nv;
+      ETC_TRY(dalloc(dec, &dec->xh_norm, (size_t)c.d_model * nv));
+      ETC_TRY(dalloc(dec, &dec->xh_att, qw * nv));
+      ETC_TRY(dalloc(dec, &dec->xh_act, (size_t)c.ffn * nv));
+      ETC_CUDA(cudaMemsetAsync(dec->xh_norm, 0, (size_t)c.d_model * nv * sizeof(__half), rt->stream));
+      ETC_CUDA(cudaMemsetAsync(dec->xh_att, 0, qw * nv * sizeof(__half), rt->stream));
+      ETC_CUDA(cudaMemsetAsync(dec->xh_act, 0, (size_t)c.ffn * nv * sizeof(__half), rt->stream));
       ETC_CUDA(cudaStreamSynchronize(rt->stream));
     }
     dec->lin_scratch_bytes = need;

@@ -94,7 +94,8 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const float* __restrict__ 
 // B-operand layout of the tcgen05 linear, instead of f32 row-major.
 template <bool XH>
 __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ weight,
-                                                           double eps, int n, float* __restrict__ out, __half* __restrict__ out_xh) {
+                                                           double eps, int n, float* __restrict__ out, __half* __restrict__ out_xh,
+                                                           int xh_nv) {
   chain_release();  // the next kernel of the step may be scheduled; it waits for this one before touching memory
   chain_wait();
   __shared__ double partial[8];
@@ -136,7 +137,7 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restri
       __half2 h01 = __floats2half2_rn(sat(r0), sat(r1)), h23 = __floats2half2_rn(sat(r2), sat(r3));
       const int k = 4 * c;
       uint2 packed = make_uint2(*reinterpret_cast<uint32_t*>(&h01), *reinterpret_cast<uint32_t*>(&h23));
-      *reinterpret_cast<uint2*>(out_xh + ((size_t)(k >> 3) * 32 + row) * 8 + (k & 7)) = packed;
+      *reinterpret_cast<uint2*>(out_xh + ((size_t)(k >> 3) * xh_nv + row) * 8 + (k & 7)) = packed;
     } else {
       reinterpret_cast<float4*>(out + (size_t)row * n)[c] = make_float4(r0, r1, r2, r3);
     }
@@ -151,17 +152,17 @@ cudaError_t launch_rmsnorm(const float* x, const float* weight, double eps, int6
                            cudaStream_t stream) {
   if (rows == 0) return cudaSuccess;
   if (rmsnorm_fast_ok(x, weight, n) && ((uintptr_t)out % 16) == 0)
-    return launch_chained(rmsnorm_rows_kernel<false>, dim3((unsigned)rows), dim3(256), 0, stream, x, weight, eps, (int)n, out, (__half*)nullptr);
+    return launch_chained(rmsnorm_rows_kernel<false>, dim3((unsigned)rows), dim3(256), 0, stream, x, weight, eps, (int)n, out, (__half*)nullptr, 32);
   else
     rmsnorm_kernel<<<(unsigned)rows, 256, 0, stream>>>(x, weight, eps, n, out);
   return cudaGetLastError();
 }
 
 cudaError_t launch_rmsnorm_xh8(const float* x, const float* weight, double eps, int64_t rows, int64_t n, __half* out_xh,
-                               cudaStream_t stream) {
+                               cudaStream_t stream, int xh_nv) {
   if (rows == 0) return cudaSuccess;
-  if (rows > 32 || n % 8 != 0 || !rmsnorm_fast_ok(x, weight, n)) return cudaErrorInvalidValue;
-  return launch_chained(rmsnorm_rows_kernel<true>, dim3((unsigned)rows), dim3(256), 0, stream, x, weight, eps, (int)n, (float*)nullptr, out_xh);
+  if (rows > xh_nv || n % 8 != 0 || !rmsnorm_fast_ok(x, weight, n)) return cudaErrorInvalidValue;
+  return launch_chained(rmsnorm_rows_kernel<true>, dim3((unsigned)rows), dim3(256), 0, stream, x, weight, eps, (int)n, (float*)nullptr, out_xh, xh_nv);
 }
 
 // --------------------------------------------------------------------------------------------

@@ -56,10 +56,10 @@ TiledPlan plan_tiled(const TiledWeight& w, int64_t vectors, int sm_count);
 cudaError_t launch_qlinear_mma16(const TiledWeight& w, const float* x, int64_t vectors, const float* bias,
                                  const float* residual, int epilogue, float* out, float* scratch, int sm_count,
                                  cudaStream_t stream, int* launches);
-// out_xh (optional, vectors <= 32): the result also stored as f16 in [cols/8][32][8] order for the next linear.
+// out_xh (optional): the result also stored as f16 in [cols/8][xh_nv][8] order for the next linear.
 cudaError_t launch_qlinear_reduce(const float* scratch, int splits, int vpad, int vectors, int rows, int rows_padded,
                                   const float* bias, const float* residual, int epilogue, float* out, __half* out_xh,
-                                  cudaStream_t stream);
+                                  cudaStream_t stream, int xh_nv = 32);
 
 // tcgen05 path (qlinear_umma.cu)
 struct UmmaPlan {
@@ -73,7 +73,7 @@ cudaError_t launch_repack_umma(const TiledWeight& w, const RepackParts& parts, c
 // x: f32 [vectors, K], converted to xh8 into `xh` first — unless xh_ready (already [K/8][32][8] f16, vectors <= 32) is given.
 cudaError_t launch_qlinear_umma(const TiledWeight& w, const float* x, const __half* xh_ready, int64_t vectors, const float* bias,
                                 const float* residual, int epilogue, float* out, __half* out_xh, __half* xh, float* scratch,
-                                DeviceStatus* status, int sm_count, cudaStream_t stream, int* launches);
+                                DeviceStatus* status, int sm_count, cudaStream_t stream, int* launches, int xh_nv = 32);
 
 // stream-K tcgen05 path (qlinear_stream.cu): up to kStreamMaxVectors vectors per pass
 constexpr int kStreamMaxVectors = 128;
@@ -92,14 +92,17 @@ cudaError_t launch_qlinear_stream(const TiledWeight& w, const float* x, const __
 
 // Layout-independent front end. `scratch` must hold tiled_scratch_bytes(w, vectors, sm_count).
 size_t tiled_scratch_bytes(const TiledWeight& w, int64_t vectors, int sm_count);
-// xh_ready / out_xh: optional f16 activation hand-off between linears (tcgen05 layout only, vectors <= 32).
+// xh_ready / out_xh: optional f16 activation hand-off between kernels, [K/8][xh_nv][8] with xh_nv = hand_off_stride(batch)
+// (tcgen05 layouts; the 128-row layout takes up to 128 vectors that way, the stream-K layout 32).
 cudaError_t launch_qlinear_tiled(const TiledWeight& w, const float* x, int64_t vectors, const float* bias,
                                  const float* residual, int epilogue, float* out, void* scratch, DeviceStatus* status,
                                  int sm_count, cudaStream_t stream, int* launches, const __half* xh_ready = nullptr,
-                                 __half* out_xh = nullptr);
-// RMSNorm whose output is stored as xh8 f16 [n/8][32][8] (rows <= 32); out_f32 optional.
+                                 __half* out_xh = nullptr, int xh_nv = 32);
+// Row stride of the f16 hand-off layout for `vectors` rows: 32, 64 or 128 (0: no hand-off above 128 vectors).
+inline int hand_off_stride(int64_t vectors) { return vectors <= 32 ? 32 : (vectors <= 64 ? 64 : (vectors <= 128 ? 128 : 0)); }
+// RMSNorm whose output is stored as f16 [n/8][xh_nv][8] (rows <= xh_nv).
 cudaError_t launch_rmsnorm_xh8(const float* x, const float* weight, double eps, int64_t rows, int64_t n, __half* out_xh,
-                               cudaStream_t stream);
+                               cudaStream_t stream, int xh_nv = 32);
 
 // ---- tensor-parallel all-reduce over peer memory (tp_kernels.cu) -----------------------------
 constexpr int kMaxTpRanks = 8;
@@ -173,7 +176,7 @@ bool attention_mma_supported(const PoolView& pool, int q_heads, int tokens);
 cudaError_t launch_attention_mma(const PoolView& pool, const float* q, const LaneInfo* lanes, const int* tables,
                                  int batch, int q_heads, double scale, long long op_window, float* out,
                                  const AttnPlan& plan, float* scratch, cudaStream_t stream, int* launches,
-                                 __half* out_xh = nullptr);
+                                 __half* out_xh = nullptr, int xh_nv = 32);
 // Fused RoPE(q), RoPE(k) and KV append for one-token steps: qkv [B, (Hq+2*Hkv)*D] f32 (the fused
 // projection output) -> q_out [B,Hq,D] f32 rotated, K/V rows written to the pool.
 cudaError_t launch_rope_append(const PoolView& pool, const float* qkv, const LaneInfo* lanes, const int* tables,

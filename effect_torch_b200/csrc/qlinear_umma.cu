@@ -395,7 +395,7 @@ UmmaPlan plan_umma(const TiledWeight& w, int64_t vectors, int sm_count) {
   const int kblocks = (int)(w.columns / 32);
   const int kStageBlocks = stage_blocks_for(p.nv);
   const int stages = (kblocks + kStageBlocks - 1) / kStageBlocks;
-  const int ctas_per_sm = p.nv <= 32 ? 2 : 1;
+  const int ctas_per_sm = p.nv <= 64 ? 2 : 1;
   const int target = std::max(1, sm_count) * ctas_per_sm;
   int splits = std::max(1, target / std::max(1, p.tiles));
   splits = std::min(splits, std::max(1, stages / 2));  // at least two stages per split
@@ -410,7 +410,7 @@ UmmaPlan plan_umma(const TiledWeight& w, int64_t vectors, int sm_count) {
 // qlinear_reduce_kernel lives in quant_kernels.cu
 cudaError_t launch_qlinear_umma(const TiledWeight& w, const float* x, const __half* xh_ready, int64_t vectors, const float* bias,
                                 const float* residual, int epilogue, float* out, __half* out_xh, __half* xh, float* scratch,
-                                DeviceStatus* status, int sm_count, cudaStream_t stream, int* launches) {
+                                DeviceStatus* status, int sm_count, cudaStream_t stream, int* launches, int xh_nv) {
   const int out_cols = (int)(epilogue == ETC_EPILOGUE_SWIGLU ? w.rows / 2 : w.rows);
   for (int64_t v0 = 0; v0 < vectors; v0 += 256) {
     const int64_t chunk = std::min<int64_t>(256, vectors - v0);
@@ -419,7 +419,7 @@ cudaError_t launch_qlinear_umma(const TiledWeight& w, const float* x, const __ha
     const int total = (K / 8) * plan.nv;
     const unsigned cgrid = (unsigned)std::min((total + 255) / 256, 148 * 4);
     const float* xin = x ? x + v0 * w.columns : nullptr;
-    const bool ready = xh_ready != nullptr && vectors <= 32;  // producer already stored xh8 with 32 padded rows
+    const bool ready = xh_ready != nullptr && vectors <= 128 && plan.nv == xh_nv;  // the producer stored the f16 layout with this row stride
     if (!ready) switch (plan.nv) {
       case 32: convert_xh8_kernel<32><<<cgrid, 256, 0, stream>>>(xin, (int)chunk, K, xh); break;
       case 64: convert_xh8_kernel<64><<<cgrid, 256, 0, stream>>>(xin, (int)chunk, K, xh); break;
@@ -433,8 +433,8 @@ cudaError_t launch_qlinear_umma(const TiledWeight& w, const float* x, const __ha
     args.quants = reinterpret_cast<const uint4*>(w.quants);
     args.scales = w.scales;
     args.xh = ready ? xh_ready : xh;
-    args.out_xh = vectors <= 32 ? out_xh : nullptr;
-    args.out_xh_nv = 32;
+    args.out_xh = vectors <= xh_nv ? out_xh : nullptr;
+    args.out_xh_nv = xh_nv;
     args.bias = bias;
     args.residual = residual ? residual + v0 * out_cols : nullptr;
     args.out = out + v0 * out_cols;
@@ -457,7 +457,7 @@ cudaError_t launch_qlinear_umma(const TiledWeight& w, const float* x, const __ha
     if (launches) ++*launches;
     if (plan.splits > 1) {
       e = launch_qlinear_reduce(scratch, plan.splits, plan.nv, (int)chunk, (int)w.rows, (int)w.rows_padded, bias, args.residual,
-                                epilogue, args.out, args.out_xh, stream);
+                                epilogue, args.out, args.out_xh, stream, xh_nv);
       if (e != cudaSuccess) return e;
       if (launches) ++*launches;
     }

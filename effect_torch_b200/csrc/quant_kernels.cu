@@ -599,7 +599,7 @@ __global__ void __launch_bounds__(kTiledWarps * 32, 2) qlinear_tiled_kernel(Tile
 // Sums the split-K partials in split order (deterministic) and applies bias / epilogue.
 __global__ void qlinear_reduce_kernel(const float* __restrict__ scratch, int splits, int vpad, int vectors, int rows,
                                       int rows_padded, const float* __restrict__ bias, const float* __restrict__ residual,
-                                      int epilogue, float* __restrict__ out, __half* __restrict__ out_xh) {
+                                      int epilogue, float* __restrict__ out, __half* __restrict__ out_xh, int xh_nv) {
   chain_release();  // the next kernel of the step may be scheduled; it waits for this one before touching memory
   chain_wait();
   const int out_cols = epilogue == ETC_EPILOGUE_SWIGLU ? rows / 2 : rows;
@@ -617,15 +617,15 @@ __global__ void qlinear_reduce_kernel(const float* __restrict__ scratch, int spl
       if (bias) { gsum += bias[r_gate]; usum += bias[r_up]; }
       const float act = silu_tanh_form(gsum) * usum;
       if (out) out[idx] = act;
-      if (out_xh)  // f16 copy in [cols/8][32][8] order: the next linear's B operand
-        out_xh[((size_t)(c >> 3) * 32 + v) * 8 + (c & 7)] = __float2half_rn(fminf(fmaxf(act, -65504.f), 65504.f));
+      if (out_xh)  // f16 copy in [cols/8][xh_nv][8] order: the next linear's B operand
+        out_xh[((size_t)(c >> 3) * xh_nv + v) * 8 + (c & 7)] = __float2half_rn(fminf(fmaxf(act, -65504.f), 65504.f));
     } else {
       float sum = 0.f;
       for (int s = 0; s < splits; ++s) sum += scratch[((size_t)s * vpad + v) * rows_padded + c];
       if (bias) sum += bias[c];
       const float val = epilogue == ETC_EPILOGUE_RESIDUAL ? residual[idx] + sum : sum;
       if (out) out[idx] = val;
-      if (out_xh) out_xh[((size_t)(c >> 3) * 32 + v) * 8 + (c & 7)] = __float2half_rn(fminf(fmaxf(val, -65504.f), 65504.f));
+      if (out_xh) out_xh[((size_t)(c >> 3) * xh_nv + v) * 8 + (c & 7)] = __float2half_rn(fminf(fmaxf(val, -65504.f), 65504.f));
     }
   }
 }
@@ -666,13 +666,13 @@ static cudaError_t launch_tiled_pass(const TiledWeight& w, const TiledPlan& plan
 
 cudaError_t launch_qlinear_reduce(const float* scratch, int splits, int vpad, int vectors, int rows, int rows_padded,
                                   const float* bias, const float* residual, int epilogue, float* out, __half* out_xh,
-                                  cudaStream_t stream) {
+                                  cudaStream_t stream, int xh_nv) {
   const int out_cols = epilogue == ETC_EPILOGUE_SWIGLU ? rows / 2 : rows;
   const int64_t total = (int64_t)vectors * out_cols;
   if (total == 0) return cudaSuccess;
   const unsigned grid = (unsigned)std::min<int64_t>((total + 255) / 256, 148 * 8);
   return launch_chained(qlinear_reduce_kernel, dim3(grid), dim3(256), 0, stream, scratch, splits, vpad, vectors, rows, rows_padded, bias, residual,
-                        epilogue, out, vectors <= 32 ? out_xh : (__half*)nullptr);
+                        epilogue, out, vectors <= xh_nv ? out_xh : (__half*)nullptr, xh_nv);
 }
 
 // Scratch layout of the tcgen05 path: [xh8 activations, rounded to 256 B][split-K partials].
@@ -702,11 +702,12 @@ size_t tiled_scratch_bytes(const TiledWeight& w, int64_t vectors, int sm_count) 
 
 cudaError_t launch_qlinear_tiled(const TiledWeight& w, const float* x, int64_t vectors, const float* bias,
                                  const float* residual, int epilogue, float* out, void* scratch, DeviceStatus* status,
-                                 int sm_count, cudaStream_t stream, int* launches, const __half* xh_ready, __half* out_xh) {
+                                 int sm_count, cudaStream_t stream, int* launches, const __half* xh_ready, __half* out_xh, int xh_nv) {
   if (w.layout == kLayoutStream256) {
     size_t xh_region = 0;
     for (int64_t v0 = 0; v0 < vectors; v0 += kStreamMaxVectors)
       xh_region = std::max(xh_region, stream_xh_region(plan_stream(w, std::min<int64_t>(kStreamMaxVectors, vectors - v0), sm_count)));
+    if (xh_nv != 32) { xh_ready = nullptr; out_xh = nullptr; }  // this layout hands activations over for up to 32 vectors only
     return launch_qlinear_stream(w, x, xh_ready, vectors, bias, residual, epilogue, out, out_xh, reinterpret_cast<__half*>(scratch),
                                  reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + xh_region), status, sm_count, stream,
                                  launches);
@@ -718,7 +719,7 @@ cudaError_t launch_qlinear_tiled(const TiledWeight& w, const float* x, int64_t v
       xh_region = std::max(xh_region, umma_xh_region(plan_umma(w, std::min<int64_t>(256, vectors - v0), sm_count)));
     return launch_qlinear_umma(w, x, xh_ready, vectors, bias, residual, epilogue, out, out_xh, reinterpret_cast<__half*>(scratch),
                                reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + xh_region), status, sm_count, stream,
-                               launches);
+                               launches, xh_nv);
   }
   return launch_qlinear_mma16(w, x, vectors, bias, residual, epilogue, out, reinterpret_cast<float*>(scratch), sm_count, stream,
                               launches);
@@ -765,7 +766,7 @@ cudaError_t launch_qlinear_mma16(const TiledWeight& w, const float* x, int64_t v
       const int64_t total = chunk * out_cols;
       const unsigned grid = (unsigned)std::min<int64_t>((total + 255) / 256, 148 * 8);
       qlinear_reduce_kernel<<<grid, 256, 0, stream>>>(scratch, plan.splits, plan.nt * 8, (int)chunk, (int)w.rows,
-                                                      (int)w.rows_padded, bias, args.residual, epilogue, args.out, nullptr);
+                                                      (int)w.rows_padded, bias, args.residual, epilogue, args.out, nullptr, 32);
       e = cudaGetLastError();
       if (e != cudaSuccess) return e;
       if (launches) ++*launches;

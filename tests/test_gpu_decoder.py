@@ -185,3 +185,29 @@ def test_sliding_window_decoder_matches_the_oracle():
     assert gs.cursor == os_.cursor == 70
     np.testing.assert_array_equal(gs.blocks[0], os_.blocks)
     assert gs.blocks[1] == os_.head
+
+
+@pytest.mark.parametrize("batch", [40, 70])
+def test_wide_batches_keep_the_f16_hand_off_path(batch):
+    """33..128 sequences per step: activations still travel between kernels in the tensor-core operand layout, with a
+    row stride of 64 or 128; teacher-forced logits against the oracle like the narrow case."""
+    cfg = helpers.TINY_Q
+    w = helpers.make_weights(cfg, seed=9, codec=orc.Q4_0)
+    rng = np.random.default_rng(batch)
+    max_tokens = batch * 48
+    odec = helpers.oracle_decoder(cfg, w, batch=batch)
+    gdec = gpu_decoder(cfg, w, batch=batch, max_tokens=max_tokens, kv_dtype=et.KV_F16, exact=False, max_advance=8)
+    opool = orc.Pool(cfg["layers"], cfg["kv_heads"], cfg["head_dim"], max_tokens, 16, orc.F16)
+    gpool = et.NativeKvPool(runtime(), cfg["layers"], cfg["kv_heads"], cfg["head_dim"], max_tokens, 16, et.KV_F16)
+    oseqs = [opool.make_sequence() for _ in range(batch)]
+    gseqs = [gpool.makeSequence() for _ in range(batch)]
+    for advance in (8, 1, 1, 1):
+        toks = rng.integers(0, cfg["vocab"], size=(batch, advance)).astype(np.uint32)
+        ol, _ = odec.execute(opool, oseqs, toks)
+        gl = gdec.execute(gpool, gseqs, toks)
+        assert helpers.rel_err(gl, ol) <= LOGIT_TOL, f"advance {advance}"
+    # fewer active sequences than the batch: padded lanes stay out of the result
+    toks = rng.integers(0, cfg["vocab"], size=(batch - 5, 1)).astype(np.uint32)
+    ol, _ = odec.execute(opool, oseqs[:batch - 5], toks)
+    gl = gdec.execute(gpool, gseqs[:batch - 5], toks)
+    assert helpers.rel_err(gl, ol) <= LOGIT_TOL
