@@ -652,10 +652,10 @@ def run_gpu_arm(args, rank, world):
             "step_roofline": {"algorithmic_bytes_per_step": step_bytes, "achieved_gbs": step_bytes * K / device_seconds / 1e9,
                               "frac_of_" + peak_kind: step_bytes * K / device_seconds / 1e9 / peaks["hbm_gbs"]},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
-                         # DRAM bytes per launch of the main kernel: ncu's read/write sums of the lm-head launch of the same kernel
-                         # (296.0 MB read for 295.5 MB of weights) scaled to this shape, plus its two split-K partial stores
-                         "traffic": int(2 * MODEL["ffn"] * (MODEL["d_model"] // 32) * 18 * (296.0 / 295.5) + 2 * 32 * 2 * MODEL["ffn"] * 4),
-                         "traffic_source": "profiles/qlinear_umma_q4_0_decode_step.md, scaled by weight bytes",
+                         # DRAM bytes per launch of the main kernel: dram__bytes_read.sum + dram__bytes_write.sum of this very launch
+                         # (grid 224, one split) from the ncu capture summarised under profiles/
+                         "traffic": 66390784 + 531968,
+                         "traffic_source": "profiles/qlinear_umma_q4_0_decode_step.md (ncu --set full, gate/up launch)",
                          "peak_kind": peak_kind,
                          "kernel": "qlinear_umma_kernel<Q4_0,32> fused gate/up [28672x4096], 32 vectors, with its f16 conversion and split-K sum launches",
                          "ms_per_launch": kernel_ms, "algorithmic_bytes_per_launch": kernel_bytes},
