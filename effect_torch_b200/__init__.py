@@ -78,6 +78,21 @@ def pool_state_bytes(layers, max_tokens, kv_heads, head_dim, dtype) -> int:
     return out.value
 
 
+def attention_plan(batch, q_heads, kv_heads, head_dim, attended_pages, sm_count=148) -> dict:
+    """Split plan of the flash-decoding kernel for tables of `attended_pages` pages (host arithmetic, no device)."""
+    splits, pps, nbytes = C.c_int(0), C.c_int(0), C.c_size_t(0)
+    _check(_lib.load().etc_kv_attention_plan(batch, q_heads, kv_heads, head_dim, attended_pages, sm_count, C.byref(splits),
+                                             C.byref(pps), C.byref(nbytes)))
+    return dict(splits=splits.value, pages_per_split=pps.value, partial_bytes=nbytes.value)
+
+
+def decoder_attention_reserve(cfg: DecoderConfig, max_advance=1, sm_count=148) -> dict:
+    """Longest block table a decoder stages per lane and the split-partial bytes it sets aside at finalize."""
+    blocks, nbytes = C.c_int(0), C.c_size_t(0)
+    _check(_lib.load().etc_decoder_attention_reserve(C.byref(cfg), max_advance, sm_count, C.byref(blocks), C.byref(nbytes)))
+    return dict(max_blocks=blocks.value, partial_bytes=nbytes.value)
+
+
 class Runtime:
     """One device + stream (makeRuntime()). Tensors passed to ops must live on this device."""
 
@@ -113,6 +128,17 @@ class Runtime:
         n = C.c_uint64(0)
         _check(self.L.etc_runtime_launch_count(self.h, C.byref(n)))
         return n.value
+
+    def capabilities(self) -> dict:
+        """dtypes and features like Capabilities (crates/runtime/src/backend.rs:181-206), plus the device's identity."""
+        caps = _lib.Capabilities()
+        _check(self.L.etc_runtime_capabilities(self.h, C.byref(caps)))
+        names = ["f32", "f64", "f16", "bf16", "u8", "u32", "i64"]
+        features = ["compilation", "async-execution", "unified-memory"]
+        return dict(dtypes=[n for i, n in enumerate(names) if caps.dtype_mask >> i & 1],
+                    features=[n for i, n in enumerate(features) if caps.feature_mask >> i & 1],
+                    device=caps.device_ordinal, sm_count=caps.sm_count, compute_capability=(caps.compute_major, caps.compute_minor),
+                    device_memory_bytes=caps.device_memory_bytes, device_name=caps.device_name.decode())
 
     @property
     def memory_bytes(self) -> int:

@@ -29,6 +29,11 @@ class DecoderConfig(C.Structure):
     ]
 
 
+class Capabilities(C.Structure):
+    _fields_ = [("dtype_mask", U32), ("feature_mask", U32), ("device_ordinal", I), ("sm_count", I), ("compute_major", I),
+                ("compute_minor", I), ("device_memory_bytes", U64), ("device_name", C.c_char * 128)]
+
+
 # name -> (restype, argtypes); restype None means etc_status (int)
 SIGNATURES = {
     "etc_last_error_message": (C.c_char_p, []),
@@ -40,6 +45,7 @@ SIGNATURES = {
     "etc_runtime_synchronize": (None, [P]),
     "etc_runtime_launch_count": (None, [P, P]),
     "etc_runtime_memory_bytes": (None, [P, P]),
+    "etc_runtime_capabilities": (None, [P, P]),
     "etc_alloc": (None, [P, SZ, P]),
     "etc_free": (None, [P, P]),
     "etc_upload": (None, [P, P, P, SZ]),
@@ -81,6 +87,8 @@ SIGNATURES = {
     "etc_seq_commit": (None, [P, P, I, I64]),
     "etc_seq_rollback": (None, [P, I64]),
     "etc_seq_frontier": (None, [P, P]),
+    "etc_kv_attention_plan": (None, [I, I, I, I, I, I, P, P, P]),
+    "etc_decoder_attention_reserve": (None, [P, I, I, P, P]),
     "etc_decoder_create": (None, [P, P, P]),
     "etc_decoder_destroy": (None, [P]),
     "etc_decoder_set_weight": (None, [P, I, I, I, P, I64, I64]),

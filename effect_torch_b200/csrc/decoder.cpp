@@ -84,13 +84,13 @@ struct etc_decoder {
   cudaGraphExec_t step_graph = nullptr;  // generate_greedy's one-token step
   // what the captured graph baked in: it is re-captured when any of these changes
   int graph_active = 0, graph_pages = 0, graph_ctx = 0;
-  const etc_pool* graph_pool = nullptr;
+  uint64_t graph_pool_uid = 0;  // the pool's serial number: a graph holds that pool's slab addresses as kernel arguments
   // execute / executeSampled with one token per sequence replay a captured step as well: the launch list only depends
   // on the number of active lanes and on an upper bound of the pages attended over (rounded up to 8 pages, so one
   // capture serves 128 steps); everything else a step reads is in device buffers the host refreshes before the launch
   cudaGraphExec_t exec_graph = nullptr;
   int exec_graph_active = 0, exec_graph_pages = 0, exec_graph_launches = 0;
-  const etc_pool* exec_graph_pool = nullptr;
+  uint64_t exec_graph_pool_uid = 0;
   bool ran_eagerly = false;  // kernels configure their attributes on their first eager launch
 
   // tensor parallel: this decoder holds one rank's shard of every projection (rows of q/k/v/gate/up, columns of o/down)
@@ -108,6 +108,18 @@ struct etc_decoder {
 namespace {
 
 bool valid_decoder(const etc_decoder* d) { return d && d->magic == kDecoderMagic; }
+
+// Live blocks a lane can stage: the pool's capacity plus the blocks a windowed sequence holds between the allocation
+// for a chunk and the eviction at its commit.
+int decoder_max_blocks(const etc_decoder_config& c, int max_advance) {
+  return c.max_tokens / c.block_size + 2 + (max_advance + c.block_size - 1) / c.block_size;
+}
+// Split-KV partials set aside at finalize: a captured step plans for the attended pages rounded up to 8, so the bound
+// covers the longest possible table rounded up the same way.
+size_t decoder_attention_reserve(const etc_decoder_config& c, int max_advance, int sm_count) {
+  const int pages = (decoder_max_blocks(c, max_advance) + 7) / 8 * 8;
+  return plan_attention_max_scratch(c.batch, c.q_heads, c.kv_heads, c.head_dim, pages, sm_count);
+}
 
 etc_status bind(etc_decoder* dec, BoundWeight& slot, int codec, const void* data, int64_t rows, int64_t columns, bool on_device) {
   etc_runtime* rt = dec->rt;
@@ -293,6 +305,10 @@ etc_status enqueue_step(StepContext& s) {
       ETC_CUDA(launch_rope_append(view, d->qkv, d->d_lanes, d->d_tables, d->d_inv_freq, c.rope_layout, B, Hq, d->qr, stream));
       ++s.launches;
       const AttnPlan plan = plan_attention(B, Hq, Hkv, D, std::max(1, s.max_pages), d->rt->sm_count);
+      if (plan.scratch_bytes > d->attn_scratch_bytes)
+        return fail(ETC_EXECUTION, "kv attention: split plan for " + std::to_string(s.max_pages) + " pages needs " +
+                                       std::to_string(plan.scratch_bytes) + " bytes of partials, the decoder holds " +
+                                       std::to_string(d->attn_scratch_bytes));
       ETC_CUDA(launch_attention_mma(view, d->qr, d->d_lanes, d->d_tables, B, Hq, scale, c.window, d->attl, plan,
                                     d->attn_scratch, stream, &s.launches, xh ? d->xh_att : nullptr, d->xh_nv));
     } else {
@@ -484,7 +500,7 @@ etc_status execute_impl(etc_decoder* dec, etc_pool* pool, etc_seq* const* seqs, 
   if (st != ETC_OK) return abort_with(st);
   if (advance == 1 && dec->ran_eagerly && !uses_exact_attention(dec, pool, 1)) {
     const int bucket = (ctx.max_pages + 7) / 8 * 8;
-    if (dec->exec_graph && (dec->exec_graph_active != active || dec->exec_graph_pages != bucket || dec->exec_graph_pool != pool)) {
+    if (dec->exec_graph && (dec->exec_graph_active != active || dec->exec_graph_pages != bucket || dec->exec_graph_pool_uid != pool->uid)) {
       cudaGraphExecDestroy(dec->exec_graph);
       dec->exec_graph = nullptr;
     }
@@ -508,7 +524,7 @@ etc_status execute_impl(etc_decoder* dec, etc_pool* pool, etc_seq* const* seqs, 
       }
       dec->exec_graph_active = active;
       dec->exec_graph_pages = bucket;
-      dec->exec_graph_pool = pool;
+      dec->exec_graph_pool_uid = pool->uid;
       dec->exec_graph_launches = sc.launches;
     }
     const cudaError_t ce = cudaGraphLaunch(dec->exec_graph, rt->stream);
@@ -563,6 +579,27 @@ etc_status execute_impl(etc_decoder* dec, etc_pool* pool, etc_seq* const* seqs, 
 
 
 extern "C" {
+
+etc_status etc_kv_attention_plan(int batch, int q_heads, int kv_heads, int head_dim, int attended_pages, int sm_count,
+                                 int* splits, int* pages_per_split, size_t* partial_bytes) {
+  if (batch <= 0 || q_heads <= 0 || kv_heads <= 0 || head_dim <= 0 || attended_pages <= 0 || sm_count <= 0)
+    return fail(ETC_INVALID_ARGUMENT, "kv attention plan: every argument must be positive");
+  const AttnPlan p = plan_attention(batch, q_heads, kv_heads, head_dim, attended_pages, sm_count);
+  if (splits) *splits = p.splits;
+  if (pages_per_split) *pages_per_split = p.pages_per_split;
+  if (partial_bytes) *partial_bytes = p.scratch_bytes;
+  return ETC_OK;
+}
+
+etc_status etc_decoder_attention_reserve(const etc_decoder_config* config, int max_advance, int sm_count, int* max_blocks,
+                                         size_t* partial_bytes) {
+  if (!config || max_advance <= 0 || sm_count <= 0 || config->block_size <= 0 || config->max_tokens <= 0 || config->batch <= 0 ||
+      config->q_heads <= 0 || config->kv_heads <= 0 || config->head_dim <= 0)
+    return fail(ETC_INVALID_ARGUMENT, "decoder attention reserve: configuration, chunk length and SM count must be positive");
+  if (max_blocks) *max_blocks = decoder_max_blocks(*config, max_advance);
+  if (partial_bytes) *partial_bytes = decoder_attention_reserve(*config, max_advance, sm_count);
+  return ETC_OK;
+}
 
 etc_status etc_decoder_create(etc_runtime* rt, const etc_decoder_config* config, etc_decoder** out) {
   ETC_TRY(activate(rt));
@@ -769,9 +806,7 @@ etc_status etc_decoder_finalize(etc_decoder* dec) {
   ETC_TRY(dalloc(dec, &dec->d_tokens, (size_t)c.batch));
   ETC_TRY(dalloc(dec, &dec->d_step_counter, 1));
   ETC_TRY(dalloc(dec, &dec->d_lanes, (size_t)c.batch));
-  // live blocks per lane: the pool's capacity plus the blocks a windowed sequence holds between the
-  // allocation for a chunk and the eviction at its commit
-  dec->max_blocks = c.max_tokens / c.block_size + 2 + (dec->max_advance + c.block_size - 1) / c.block_size;
+  dec->max_blocks = decoder_max_blocks(c, dec->max_advance);
   ETC_TRY(dalloc(dec, &dec->d_tables, (size_t)c.batch * dec->max_blocks));
   if (tiled) {
     size_t need = 0;
@@ -799,8 +834,7 @@ etc_status etc_decoder_finalize(etc_decoder* dec) {
     }
     dec->lin_scratch_bytes = need;
     if (need) ETC_TRY(dalloc(dec, &dec->lin_scratch, need / sizeof(float)));
-    // split-KV partials: the split count never exceeds the plan for the longest possible table
-    const size_t attn_need = plan_attention_max_scratch(c.batch, c.q_heads, c.kv_heads, c.head_dim, dec->max_blocks, rt->sm_count);
+    const size_t attn_need = decoder_attention_reserve(c, dec->max_advance, rt->sm_count);
     dec->attn_scratch_bytes = attn_need;
     ETC_TRY(dalloc(dec, &dec->attn_scratch, attn_need / sizeof(float) + 1));
   }
@@ -921,7 +955,7 @@ etc_status etc_decoder_generate_greedy(etc_decoder* dec, etc_pool* pool, etc_seq
   if (st != ETC_OK) return abort_with(st);
   if (steps > 1) {
     if (dec->step_graph && (dec->graph_active != active || dec->graph_pages != final_pages || dec->graph_ctx != ctx.max_ctx ||
-                            dec->graph_pool != pool)) {
+                            dec->graph_pool_uid != pool->uid)) {
       cudaGraphExecDestroy(dec->step_graph);
       dec->step_graph = nullptr;
     }
@@ -943,7 +977,7 @@ etc_status etc_decoder_generate_greedy(etc_decoder* dec, etc_pool* pool, etc_seq
       dec->graph_active = active;
       dec->graph_pages = final_pages;
       dec->graph_ctx = ctx.max_ctx;
-      dec->graph_pool = pool;
+      dec->graph_pool_uid = pool->uid;
     }
     for (int sidx = 1; sidx < steps; ++sidx) {
       e = cudaGraphLaunch(dec->step_graph, rt->stream);

@@ -530,13 +530,17 @@ etc_status etc_gguf_load_tensor_device(etc_runtime* rt, const etc_gguf* file, in
         cudaEventRecord(landed[slot], rt->stream) != cudaSuccess)
       st = fail(ETC_TRANSFER, "gguf: device copy failed");
   }
-  const std::string message = last_error();
-  if (cudaStreamSynchronize(rt->stream) != cudaSuccess && st == ETC_OK) st = fail(ETC_TRANSFER, "gguf: device copy failed");
+  // the message of a failure above is only kept when there was one (a stale text of an earlier call must not leak out)
+  std::string message = st != ETC_OK ? last_error() : std::string();
+  if (cudaStreamSynchronize(rt->stream) != cudaSuccess && st == ETC_OK) {
+    st = ETC_TRANSFER;
+    message = "gguf: device copy failed";
+  }
   for (int b = 0; b < 2; ++b) {
     if (staging[b]) cudaFreeHost(staging[b]);
     if (landed[b]) cudaEventDestroy(landed[b]);
   }
-  if (st != ETC_OK && !message.empty()) return fail(st, message);
+  if (st != ETC_OK) return fail(st, message);
   if (st == ETC_OK && cancelled_flag && *cancelled_flag) return fail(ETC_CANCELLED, "gguf: operation aborted");
   return st;
 }

@@ -197,6 +197,8 @@ etc_status etc_pool_create(etc_runtime* rt, int layers, int kv_heads, int head_d
     return fail(ETC_INVALID_ARGUMENT, "kv pool: capacity " + std::to_string(max_tokens) +
                                           " must be a positive multiple of block size " + std::to_string(block_size));
   etc_pool* p = new etc_pool();
+  static std::atomic<uint64_t> next_uid{1};
+  p->uid = next_uid.fetch_add(1);
   p->rt = rt;
   p->layers = layers; p->kv_heads = kv_heads; p->head_dim = head_dim;
   p->max_tokens = max_tokens; p->block_size = block_size; p->dtype = dtype;

@@ -42,6 +42,7 @@ struct BlockStore {
 
 struct etc_pool {
   uint32_t magic = etc::kPoolMagic;
+  uint64_t uid = 0;  // process-wide serial number: captured graphs key on it, never on the handle's address
   etc_runtime* rt = nullptr;
   int layers = 0, kv_heads = 0, head_dim = 0, max_tokens = 0, block_size = 0, dtype = 0;
   size_t layer_elems = 0;   // elements per layer slab

@@ -597,9 +597,11 @@ __global__ void __launch_bounds__(kTiledWarps * 32, 2) qlinear_tiled_kernel(Tile
 }
 
 // Sums the split-K partials in split order (deterministic) and applies bias / epilogue.
+// `residual` and `out` may be the same buffer (the decoder adds projections onto its hidden state in place), so
+// neither carries a no-alias promise.
 __global__ void qlinear_reduce_kernel(const float* __restrict__ scratch, int splits, int vpad, int vectors, int rows,
-                                      int rows_padded, const float* __restrict__ bias, const float* __restrict__ residual,
-                                      int epilogue, float* __restrict__ out, __half* __restrict__ out_xh, int xh_nv) {
+                                      int rows_padded, const float* __restrict__ bias, const float* residual,
+                                      int epilogue, float* out, __half* __restrict__ out_xh, int xh_nv) {
   chain_release();  // the next kernel of the step may be scheduled; it waits for this one before touching memory
   chain_wait();
   const int out_cols = epilogue == ETC_EPILOGUE_SWIGLU ? rows / 2 : rows;

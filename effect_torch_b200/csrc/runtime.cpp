@@ -5,6 +5,7 @@
 #include <cstring>
 
 #include "common.h"
+#include "weights.h"
 
 namespace etc {
 
@@ -183,12 +184,33 @@ etc_status etc_runtime_create(int device_ordinal, etc_runtime** out) {
   if (e == cudaSuccess) e = cudaMalloc((void**)&rt->d_status, sizeof(DeviceStatus));
   if (e == cudaSuccess) e = cudaMemset(rt->d_status, 0, sizeof(DeviceStatus));
   if (e == cudaSuccess) e = cudaMallocHost((void**)&rt->h_status, sizeof(DeviceStatus));
+  // reserve the fixed scratch array of the allocation-free linear now, not inside its first call
+  if (e == cudaSuccess) e = static_scratch_prepare(device_ordinal);
   if (e != cudaSuccess) {
     delete rt;
     return fail(ETC_UNAVAILABLE, std::string("runtime setup failed: ") + cudaGetErrorString(e));
   }
   std::memset(rt->h_status, 0, sizeof(DeviceStatus));
   *out = rt;
+  return ETC_OK;
+}
+
+etc_status etc_runtime_capabilities(etc_runtime* rt, etc_capabilities* out) {
+  ETC_TRY(activate(rt));
+  if (!out) return fail(ETC_INVALID_ARGUMENT, "out is null");
+  cudaDeviceProp prop;
+  ETC_CUDA(cudaGetDeviceProperties(&prop, rt->device));
+  std::memset(out, 0, sizeof(*out));
+  // f64 appears inside kernels (norms, rotary angles, the exact attention) but is not a tensor dtype of this backend
+  out->dtype_mask = (1u << ETC_DTYPE_F32) | (1u << ETC_DTYPE_F16) | (1u << ETC_DTYPE_BF16) | (1u << ETC_DTYPE_U8) |
+                    (1u << ETC_DTYPE_U32) | (1u << ETC_DTYPE_I64);
+  out->feature_mask = 0x3u;  // compilation (the decoder plan) and asynchronous execution (stream launches)
+  out->device_ordinal = rt->device;
+  out->sm_count = rt->sm_count;
+  out->compute_major = prop.major;
+  out->compute_minor = prop.minor;
+  out->device_memory_bytes = (uint64_t)prop.totalGlobalMem;
+  std::strncpy(out->device_name, prop.name, sizeof(out->device_name) - 1);
   return ETC_OK;
 }
 

@@ -6,6 +6,12 @@
 // The array is shared by every call in the process that targets the same device, so two calls that overlap in
 // time (different streams, different threads) race on it; callers serialise them. Nothing in the array has to be
 // zero when a call starts: the linear writes every partial sum and every converted activation it later reads.
+//
+// When the 16 MiB are taken: the array belongs to this translation unit's device module, which the CUDA runtime
+// loads lazily. Looking up the array's device address loads the module, and that is the moment the driver reserves
+// the memory on the current device. etc_runtime_create therefore calls static_scratch_prepare, so the reservation
+// happens while the runtime is being created, before a host divides the remaining device memory among its own
+// pools, and can fail there with a clear error instead of inside the first allocation-free call.
 #include <mutex>
 
 #include "kernels.h"
@@ -34,6 +40,15 @@ cudaError_t static_scratch_for_device(int device, void** out) {
 }
 
 }  // namespace
+
+namespace etc {
+// Set-up step, once per device, with that device current (called by etc_runtime_create).
+cudaError_t static_scratch_prepare(int device) {
+  if (device < 0 || device >= kMaxDevices) return cudaSuccess;  // the entry point itself refuses such ordinals
+  void* ignored = nullptr;
+  return static_scratch_for_device(device, &ignored);
+}
+}  // namespace etc
 
 extern "C" {
 

@@ -87,3 +87,27 @@ def shard_weights(weights: dict, cfg: dict, rank: int, world: int) -> dict:
             local[name] = columns(layer[name])
         out["layers"].append(local)
     return out
+
+
+def all_ranks_ok(ok: bool, group=None) -> bool:
+    """Step-status exchange over the host transport (a torch.distributed group, gloo or nccl-backed): True only when
+    every rank's step succeeded. A rank observes only its own device status word, so a step in which one rank's bounded
+    wait ran out (or any other rank-local failure) is reported as ETC_OK on the others; every rank calls this after
+    each tensor-parallel step and treats the step as failed when it returns False."""
+    import torch
+    import torch.distributed as dist
+
+    flag = torch.tensor([1 if ok else 0], dtype=torch.int32)
+    backend = dist.get_backend(group)
+    if backend == "nccl":
+        flag = flag.cuda()
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+    return bool(int(flag.item()))
+
+
+def barrier_before_teardown(group=None) -> None:
+    """Host barrier every rank passes before destroying a decoder whose exchange region its peers have mapped: a peer
+    may still be reading this rank's partial sums until its own step has been synchronised."""
+    import torch.distributed as dist
+
+    dist.barrier(group=group)

@@ -101,6 +101,23 @@ ETC_API etc_status etc_runtime_launch_count(etc_runtime* rt, uint64_t* out);
  * external_memory_bytes, crates/runtime-cpu/src/napi/mod.rs:2373-2376). */
 ETC_API etc_status etc_runtime_memory_bytes(etc_runtime* rt, uint64_t* out);
 
+/* Capabilities (crates/runtime/src/backend.rs:168-206: the dtypes and optional features a backend reports).
+ * dtype_mask has bit i set for etc_dtype_bit i; feature_mask bit 0 = compilation, bit 1 = asynchronous execution,
+ * bit 2 = unified memory (never set: device memory is separate). device_name receives a NUL-terminated copy. */
+typedef enum etc_dtype_bit {
+  ETC_DTYPE_F32 = 0, ETC_DTYPE_F64 = 1, ETC_DTYPE_F16 = 2, ETC_DTYPE_BF16 = 3, ETC_DTYPE_U8 = 4, ETC_DTYPE_U32 = 5, ETC_DTYPE_I64 = 6
+} etc_dtype_bit;
+typedef struct etc_capabilities {
+  uint32_t dtype_mask;
+  uint32_t feature_mask;
+  int device_ordinal;
+  int sm_count;
+  int compute_major, compute_minor;
+  uint64_t device_memory_bytes;
+  char device_name[128];
+} etc_capabilities;
+ETC_API etc_status etc_runtime_capabilities(etc_runtime* rt, etc_capabilities* out);
+
 /* Device buffers (NativeTensor storage; crates/runtime/src/backend.rs:215-221). */
 ETC_API etc_status etc_alloc(etc_runtime* rt, size_t bytes, void** out_d_ptr);
 ETC_API etc_status etc_free(etc_runtime* rt, void* d_ptr);
@@ -170,9 +187,11 @@ ETC_API etc_status etc_qlinear_tiled_into(etc_runtime* rt, const etc_qweight* w,
  * neither device nor pinned memory, for callers that must not allocate while they run. No counterpart in the
  * reference, whose backends allocate per operation. Results equal etc_qlinear_tiled_into's. A call that needs more
  * than etc_qlinear_tiled_static_max_bytes of scratch is rejected with ETC_INVALID_ARGUMENT (the message gives both
- * sizes). The first call on each device also looks up the array's device address, so make that first call before
- * any stream capture begins. All calls on a device share the array: calls that overlap in time race, serialise them.
- * Nothing in the array needs to be zero. */
+ * sizes). The array's 16 MiB are reserved on a device when etc_runtime_create runs for it (that is when its device
+ * address is looked up, which loads the module holding it), so create the runtime before dividing the remaining
+ * device memory among your own pools; the entry point looks the address up again only if that step was skipped, and
+ * that look-up should not happen during a stream capture. All calls on a device share the array: calls that overlap in
+ * time race, serialise them. Nothing in the array needs to be zero. */
 ETC_API etc_status etc_qlinear_tiled_static_max_bytes(size_t* max_bytes);
 ETC_API etc_status etc_qlinear_tiled_static_into(etc_runtime* rt, const etc_qweight* w, const float* d_x, int64_t vectors,
                                                  const float* d_bias, const float* d_residual, etc_epilogue epilogue,
@@ -339,9 +358,24 @@ ETC_API etc_status etc_decoder_set_tensor_parallel(etc_decoder* dec, int rank, i
  * kernel over peer memory (CUDA IPC, plain peer loads over NVLink, 2..8 ranks on one node). Every rank exports a
  * 64-byte handle of its exchange region, the host gathers the handles of all ranks into a table [world][64] (own slot
  * ignored) and every rank imports it. The kernel's wait for its peers is bounded: a rank that never arrives turns
- * into ETC_EXECUTION at the next synchronising call, not into a hang. */
+ * into ETC_EXECUTION at the next synchronising call, not into a hang.
+ * Two duties stay with the host, because a rank only sees its own status. (1) After every step the ranks exchange
+ * their step status over the host transport; when any rank failed, every rank treats the step as failed (a rank whose
+ * own call returned ETC_OK has committed already: it releases the affected sequences and re-creates them, as it would
+ * after any other lost step). (2) Before a decoder is destroyed, or its peers re-imported, all ranks pass a host
+ * barrier: a peer may still be reading this rank's exchange region until its own step has been synchronised. */
 ETC_API etc_status etc_decoder_tp_peer_export(etc_decoder* dec, uint8_t* out_handle_64_bytes);
 ETC_API etc_status etc_decoder_tp_peer_import(etc_decoder* dec, const uint8_t* handles_world_x_64_bytes);
+
+/* Planners of the flash-decoding kernel, pure host arithmetic in the manner of the reference's `*_requirements`
+ * calls (crates/runtime-cpu/src/lib.rs:5-11). etc_kv_attention_plan: the split of `attended_pages` pages over the grid
+ * and the bytes of split partials one launch writes. etc_decoder_attention_reserve: the longest block table a decoder of
+ * this configuration stages per lane and the partial bytes it sets aside at finalize; every plan a step can ask for
+ * (any table length up to max_blocks, rounded up to 8 pages as captured steps do) fits in it. */
+ETC_API etc_status etc_kv_attention_plan(int batch, int q_heads, int kv_heads, int head_dim, int attended_pages, int sm_count,
+                                         int* splits, int* pages_per_split, size_t* partial_bytes);
+ETC_API etc_status etc_decoder_attention_reserve(const etc_decoder_config* config, int max_advance, int sm_count,
+                                                 int* max_blocks, size_t* partial_bytes);
 
 ETC_API etc_status etc_decoder_create(etc_runtime* rt, const etc_decoder_config* config, etc_decoder** out);
 ETC_API etc_status etc_decoder_destroy(etc_decoder* dec);

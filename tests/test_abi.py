@@ -61,3 +61,28 @@ def test_no_cpu_fallback_without_a_device():
         et.Runtime(0)
     assert e.value.reason == "backend-unavailable"
     assert "no CPU fallback" in str(e.value)
+
+
+def test_every_attention_plan_a_step_can_ask_for_fits_the_decoder_reserve():
+    """The decoder sets aside split-KV partials once; a captured one-token step plans for the attended pages rounded up
+    to 8. Sweep pool capacities and batches (including the geometries where the rounding adds a split: capacities whose
+    page count is 1..4 above a multiple of 8 with few lanes) and check that no plan exceeds the reserve."""
+    from effect_torch_b200 import DecoderConfig
+    for q_heads, kv_heads, head_dim in ((32, 8, 128), (8, 2, 64), (4, 4, 128)):
+        for batch in (1, 2, 3, 4, 8, 9, 32, 64):
+            for max_tokens in list(range(16, 1025, 16)) + [1600, 2048, 4096, 8192]:
+                cfg = DecoderConfig(1, q_heads * head_dim, q_heads, kv_heads, head_dim, 64, 64, 1e-5, 1e4, 0, -1, batch, max_tokens, 16,
+                                    et.KV_F16, 0)
+                for max_advance in (1, 16):
+                    reserve = et.decoder_attention_reserve(cfg, max_advance)
+                    assert reserve["max_blocks"] >= max_tokens // 16 + 2
+                    for pages in sorted({1, 8, max_tokens // 16, max_tokens // 16 + 1, reserve["max_blocks"]} |
+                                        set(range(max(1, max_tokens // 16 - 9), reserve["max_blocks"] + 1))):
+                        bucket = (pages + 7) // 8 * 8
+                        need = et.attention_plan(batch, q_heads, kv_heads, head_dim, bucket)["partial_bytes"]
+                        assert need <= reserve["partial_bytes"], (q_heads, batch, max_tokens, max_advance, pages, need, reserve)
+    # a geometry where the rounding matters: 400 tokens (25 pages), one lane, 32 query heads of 128: the 32-page plan has
+    # one split more than the 25-page plan and needs 66,560 bytes
+    assert et.attention_plan(1, 32, 8, 128, 32)["partial_bytes"] == 66560
+    cfg = DecoderConfig(1, 4096, 32, 8, 128, 64, 64, 1e-5, 1e4, 0, -1, 1, 400, 16, et.KV_F16, 0)
+    assert et.decoder_attention_reserve(cfg, 1)["partial_bytes"] >= 66560

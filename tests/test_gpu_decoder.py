@@ -211,3 +211,56 @@ def test_wide_batches_keep_the_f16_hand_off_path(batch):
     ol, _ = odec.execute(opool, oseqs[:batch - 5], toks)
     gl = gdec.execute(gpool, gseqs[:batch - 5], toks)
     assert helpers.rel_err(gl, ol) <= LOGIT_TOL
+
+
+def test_captured_step_plans_fit_the_reserved_partials_at_awkward_capacities():
+    """max_tokens = 400 (25 pages), one lane: once the context passes 384 tokens the captured step plans for 32 pages,
+    one split more than any table length up to the capacity needs. Logits must stay on the oracle through that range
+    (the partials of the extra split have to land inside the decoder's reserve)."""
+    cfg = dict(helpers.TINY_Q, layers=2)
+    w = helpers.make_weights(cfg, seed=12, codec=orc.Q4_0)
+    rng = np.random.default_rng(12)
+    odec = helpers.oracle_decoder(cfg, w, batch=1)
+    gdec = gpu_decoder(cfg, w, batch=1, max_tokens=400, kv_dtype=et.KV_F16, exact=False, max_advance=16)
+    opool = orc.Pool(cfg["layers"], cfg["kv_heads"], cfg["head_dim"], 400, 16, orc.F16)
+    gpool = et.NativeKvPool(runtime(), cfg["layers"], cfg["kv_heads"], cfg["head_dim"], 400, 16, et.KV_F16)
+    os_, gs = opool.make_sequence(), gpool.makeSequence()
+    for _ in range(23):  # 368 tokens in chunks of 16
+        toks = rng.integers(0, cfg["vocab"], size=(1, 16)).astype(np.uint32)
+        odec.execute(opool, [os_], toks, want_logits=False, want_sampled=False)
+        gdec.execute(gpool, [gs], toks)
+    canary = gdec.execute(gpool, [gs], toks[:, :1])  # eager one-token step; later ones replay a captured graph
+    odec.execute(opool, [os_], toks[:, :1])
+    assert np.isfinite(canary).all()
+    for step in range(30):  # cursor 369 .. 399: crosses 384, where the page bucket becomes 32
+        toks = rng.integers(0, cfg["vocab"], size=(1, 1)).astype(np.uint32)
+        ol, _ = odec.execute(opool, [os_], toks)
+        gl = gdec.execute(gpool, [gs], toks)
+        assert helpers.rel_err(gl, ol) <= LOGIT_TOL, f"step {step} (cursor {gs.cursor})"
+    assert gs.cursor == os_.cursor == 399
+
+
+def test_a_recreated_pool_never_replays_the_old_pools_graph():
+    """A captured step holds the pool's slab addresses. Destroying the pool and creating another one of the same
+    schema (which may land at the same host address) must re-capture: the second pool's results equal a fresh run."""
+    cfg = dict(helpers.TINY_Q, layers=2)
+    w = helpers.make_weights(cfg, seed=13, codec=orc.Q4_0)
+    rng = np.random.default_rng(13)
+    prompt = rng.integers(0, cfg["vocab"], size=(2, 8)).astype(np.uint32)
+    steps = rng.integers(0, cfg["vocab"], size=(6, 2, 1)).astype(np.uint32)
+    gdec = gpu_decoder(cfg, w, batch=2, max_tokens=128, kv_dtype=et.KV_F16, exact=False, max_advance=8)
+
+    def run(pool):
+        seqs = [pool.makeSequence() for _ in range(2)]
+        gdec.execute(pool, seqs, prompt)
+        return np.stack([gdec.execute(pool, seqs, t) for t in steps])
+
+    pool_a = et.NativeKvPool(runtime(), cfg["layers"], cfg["kv_heads"], cfg["head_dim"], 128, 16, et.KV_F16)
+    first = run(pool_a)
+    # occupy pool A's pages with other contents before it goes away, so a replay against stale addresses would show
+    pool_a.close()
+    filler = et.NativeKvPool(runtime(), cfg["layers"], cfg["kv_heads"], cfg["head_dim"], 128, 16, et.KV_F16)
+    pool_b = et.NativeKvPool(runtime(), cfg["layers"], cfg["kv_heads"], cfg["head_dim"], 128, 16, et.KV_F16)
+    second = run(pool_b)
+    np.testing.assert_array_equal(second, first)
+    del filler

@@ -106,6 +106,10 @@ def _rank_main(rank, world, port, results):
         fd, fdn, fdk = weights["layers"][0]["down"]
         full = orc.qlinear(codec, orc.silu_mul(orc.qlinear(codec, x, fg, fgn, fgk), orc.qlinear(codec, x, fu, fgn, fgk)), fd, fdn, fdk)
         results[world + rank] = helpers.rel_err(down_partial.numpy(), full)
+        # step-status exchange: rank 1 reports a failed step (as if its bounded peer wait had run out); rank 0's own call
+        # succeeded, yet both ranks must see the step as failed and roll back, and a clean step is clean on both
+        results[("agree", rank)] = (tp.all_ranks_ok(rank != 1), tp.all_ranks_ok(True))
+        tp.barrier_before_teardown()
     finally:
         dist.destroy_process_group()
 
@@ -117,5 +121,7 @@ def test_two_rank_projection_block_over_gloo_matches_the_unsharded_oracle():
     manager = mp.get_context("spawn").Manager()
     results = manager.dict()
     mp.spawn(_rank_main, args=(world, port, results), nprocs=world, join=True)
-    assert sorted(results.keys()) == [0, 1, 2, 3]
-    assert all(err <= 1e-6 for err in results.values()), dict(results)
+    numeric = {k: v for k, v in results.items() if isinstance(k, int)}
+    assert sorted(numeric.keys()) == [0, 1, 2, 3]
+    assert all(err <= 1e-6 for err in numeric.values()), dict(results)
+    assert results[("agree", 0)] == (False, True) and results[("agree", 1)] == (False, True)

@@ -27,13 +27,20 @@ def test_static_scratch_linear_equals_the_existing_entry_point_twice_in_a_row(co
     qw = et.QWeight(rt, codec, [dev(packed)], [rows], columns)
     assert qw.scratch_bytes(vectors) <= qw.static_scratch_max_bytes()
     rng = np.random.default_rng(vectors)
-    for call in range(2):  # two calls in a row share the array: the second must not see the first one's leftovers
+    for call in range(3):  # calls in a row share the array: a later one must not see an earlier one's leftovers
         x = rng.normal(size=(vectors, columns)).astype(np.float32)
         bias = rng.normal(size=rows).astype(np.float32)
         dx, dbias = dev(x), dev(bias)  # held until the results are read: the runtime's stream is not torch's
         expected, got = empty((vectors, rows)), empty((vectors, rows))
         qw.linear_into(dx, vectors, expected, bias=dbias)
+        rt.synchronize()
+        torch.cuda.synchronize()
+        free_before, tracked_before = torch.cuda.mem_get_info()[0], rt.memory_bytes
         qw.linear_static_into(dx, vectors, got, bias=dbias)
+        rt.synchronize()
+        if call > 0:  # the first call may still load kernel code; from the second on, device memory must not move at all
+            assert torch.cuda.mem_get_info()[0] == free_before, "the allocation-free linear changed the free device memory"
+            assert rt.memory_bytes == tracked_before
         np.testing.assert_array_equal(host(got), host(expected), err_msg=f"call {call}")
 
 
