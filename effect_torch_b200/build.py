@@ -16,6 +16,9 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libetcuda.so")
+# stand-alone measurement program of the tensor-core issue rates (bench.py --workload tensor-issue runs it)
+PROBE_SRC = os.path.join(CSRC, "probes", "tensor_issue_probe.cu")
+PROBE = os.path.join(HERE, "tensor_issue_probe.bin")
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 
@@ -39,7 +42,15 @@ def _stale() -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
+def build_probe(force: bool = False) -> str:
+    if force or not os.path.exists(PROBE) or os.path.getmtime(PROBE) < os.path.getmtime(PROBE_SRC):
+        host_cxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++"
+        subprocess.run([_nvcc(), "-ccbin", host_cxx, "-O3", "-std=c++17", "-lineinfo"] + ARCH_FLAGS + ["-o", PROBE, PROBE_SRC], check=True)
+    return PROBE
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
+    build_probe(force)
     if not force and not _stale():
         return LIB
     objs = []

@@ -36,7 +36,9 @@ struct TiledWeight {
   uint8_t* quants = nullptr;
   __half* scales = nullptr;
   size_t quant_bytes = 0, scale_bytes = 0;
-  int* counters = nullptr;  // kLayoutStream256: [rows_padded/256][4] arrival tickets, zero between launches
+  // arrival tickets, zero between launches: kLayoutStream256 [rows_padded/256][4]; kLayoutUmma128 [rows_padded/128]
+  // (taken by the matvec kernel's CTAs that hold part of a tile's K; the last one to arrive finishes the tile)
+  int* counters = nullptr;
 };
 struct RepackParts {
   const uint8_t* ptr[4];
@@ -74,6 +76,22 @@ cudaError_t launch_repack_umma(const TiledWeight& w, const RepackParts& parts, c
 cudaError_t launch_qlinear_umma(const TiledWeight& w, const float* x, const __half* xh_ready, int64_t vectors, const float* bias,
                                 const float* residual, int epilogue, float* out, __half* out_xh, __half* xh, float* scratch,
                                 DeviceStatus* status, int sm_count, cudaStream_t stream, int* launches, int xh_nv = 32);
+
+// small-batch matvec on the 128-row layout (qlinear_mv.cu): up to 32 vectors per pass, mma.sync fed by a bulk-copy ring
+struct MvPlan {
+  int nt = 1;  // groups of 8 vectors per pass (1, 2 or 4)
+  int tiles = 1, groups = 1, spt = 1, units = 1, upc = 1, grid = 1;  // row groups of 1-2 tiles, stages per group, (group, stage) units, units per CTA
+  size_t xh_bytes = 0;       // f16 activations [K/8][nt*8][8] when the caller passes f32 rows (rounded to 256 bytes)
+  size_t partial_bytes = 0;  // [grid][2][nt*8][128] f32 partial tiles of runs that cover part of a tile's K
+};
+MvPlan plan_mv(const TiledWeight& w, int64_t vectors, int sm_count);
+// Largest vector count the front end routes to the matvec kernel (the tcgen05 kernel takes over above it).
+int mv_max_vectors();
+// x f32 [vectors, K] (converted into the head of `scratch` first), or xh_ready in the f16 hand-off layout with row stride
+// xh_nv; scratch holds xh_bytes + partial_bytes of the plan; w.counters holds the tile tickets.
+cudaError_t launch_qlinear_mv(const TiledWeight& w, const float* x, const __half* xh_ready, int64_t vectors, const float* bias,
+                              const float* residual, int epilogue, float* out, __half* out_xh, void* scratch,
+                              DeviceStatus* status, int sm_count, cudaStream_t stream, int* launches, int xh_nv = 32);
 
 // stream-K tcgen05 path (qlinear_stream.cu): up to kStreamMaxVectors vectors per pass
 constexpr int kStreamMaxVectors = 128;

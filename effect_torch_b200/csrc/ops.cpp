@@ -166,6 +166,7 @@ etc_status build_qweight(etc_runtime* rt, int codec, const void* const* parts, c
     w->tiled.scale_bytes = 0;
     counter_bytes = (size_t)(w->tiled.rows_padded / 256) * 4 * sizeof(int);
   }
+  if (w->tiled.layout == kLayoutUmma128) counter_bytes = (size_t)(w->tiled.rows_padded / 128) * sizeof(int);
   etc_status st = rt->device_alloc(w->tiled.quant_bytes, (void**)&w->tiled.quants);
   if (st == ETC_OK && w->tiled.scale_bytes) st = rt->device_alloc(w->tiled.scale_bytes, (void**)&w->tiled.scales);
   if (st == ETC_OK && counter_bytes) {

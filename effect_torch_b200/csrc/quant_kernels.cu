@@ -691,6 +691,10 @@ size_t tiled_scratch_bytes(const TiledWeight& w, int64_t vectors, int sm_count) 
     }
     return need;
   }
+  if (w.layout == kLayoutUmma128 && w.counters && vectors <= mv_max_vectors()) {
+    const MvPlan p = plan_mv(w, vectors, sm_count);
+    return p.xh_bytes + p.partial_bytes;
+  }
   if (w.layout == kLayoutUmma128) {
     size_t need = 0;
     for (int64_t v0 = 0; v0 < vectors; v0 += 256) {
@@ -714,6 +718,9 @@ cudaError_t launch_qlinear_tiled(const TiledWeight& w, const float* x, int64_t v
                                  reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + xh_region), status, sm_count, stream,
                                  launches);
   }
+  if (w.layout == kLayoutUmma128 && w.counters && vectors <= mv_max_vectors())
+    return launch_qlinear_mv(w, x, xh_ready, vectors, bias, residual, epilogue, out, out_xh, scratch, status, sm_count, stream,
+                             launches, xh_nv);
   if (w.layout == kLayoutUmma128) {
     // the xh8 region is sized for the widest pass of this call
     size_t xh_region = 0;
