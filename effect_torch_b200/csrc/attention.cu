@@ -552,12 +552,8 @@ static cudaError_t launch_attention_mma_t(const PoolView& pool, const AttnArgs& 
   constexpr size_t merge = (size_t)kAttnWarps * 16 * (D + 2) * sizeof(float);
   constexpr size_t smem = ring > merge ? ring : merge;
   auto kernel = attention_mma_kernel<D, BF16>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-    configured = true;
-  }
+  const cudaError_t attr = opt_in_shared_memory(kernel, smem);
+  if (attr != cudaSuccess) return attr;
   dim3 grid((unsigned)splits, (unsigned)pool.kv_heads, (unsigned)batch);
   return launch_chained(kernel, grid, dim3(kAttnWarps * 32), smem, stream, args);
 }

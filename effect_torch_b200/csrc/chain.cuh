@@ -8,6 +8,8 @@
 
 #include <cuda_runtime.h>
 
+#include <mutex>
+#include <set>
 #include <utility>
 
 namespace etc {
@@ -28,6 +30,23 @@ inline cudaError_t launch_chained(void (*kernel)(KernelArgs...), dim3 grid, dim3
   config.attrs = attribute;
   config.numAttrs = 1;
   return cudaLaunchKernelEx(&config, kernel, std::forward<Args>(args)...);
+}
+
+// Opts a kernel in to `bytes` of dynamic shared memory once per (kernel, device): the attribute belongs to the function
+// on a device, so a process that drives several GPUs has to set it on each. Thread-safe.
+template <typename Kernel>
+inline cudaError_t opt_in_shared_memory(Kernel kernel, size_t bytes) {
+  static std::mutex mutex;
+  static std::set<std::pair<const void*, int>> configured;  // kernels of one signature share this instantiation
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return e;
+  const std::pair<const void*, int> key(reinterpret_cast<const void*>(kernel), device);
+  std::lock_guard<std::mutex> lock(mutex);
+  if (configured.count(key)) return cudaSuccess;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (e == cudaSuccess) configured.insert(key);
+  return e;
 }
 
 }  // namespace etc

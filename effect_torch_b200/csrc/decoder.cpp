@@ -820,8 +820,7 @@ etc_status etc_decoder_finalize(etc_decoder* dec) {
       need = std::max(need, tiled_scratch_bytes(dec->t_head->tiled, std::min<int64_t>(v, c.batch), rt->sm_count));
     dec->xh_nv = hand_off_stride(c.batch) ? hand_off_stride(c.batch) : 32;
     dec->xh_path = hand_off_stride(c.batch) != 0 && c.d_model % 8 == 0 && c.ffn % 8 == 0 && (c.q_heads * c.head_dim) % 8 == 0 &&
-                   c.d_model <= 8192 &&
-                   (dec->t_head->tiled.layout == kLayoutUmma128 || (dec->t_head->tiled.layout == kLayoutStream256 && c.batch <= 32));
+                   c.d_model <= 8192;
     if (dec->xh_path) {
       const size_t nv = (size_t)dec->xh_nv;
       ETC_TRY(dalloc(dec, &dec->xh_norm, (size_t)c.d_model * nv));

@@ -20,24 +20,21 @@ cudaError_t launch_qlinear_generic(int codec, const float* x, int64_t vectors, i
 cudaError_t launch_qembedding(int codec, const void* indexes, int index_is_i64, int64_t count, const uint8_t* weight,
                               int64_t rows, int64_t columns, float* out, DeviceStatus* status, cudaStream_t stream);
 
-// Tiled (tensor-core) weight layout: see quant_kernels.cu for the byte map.
-enum TiledLayout : int {
-  kLayoutMma16 = 0,   // 16-row tiles for the mma.sync kernel (quant_kernels.cu)
-  kLayoutUmma128 = 1, // 128-row tiles streamed per thread for the tcgen05 kernel (qlinear_umma.cu)
-  kLayoutStream256 = 2 // 256-row tiles, payload and scales of a block in one chunk, for the stream-K tcgen05 kernel (qlinear_stream.cu)
-};
+// Tiled weights (Q4_0 / Q8_0): 128-row tiles. For row tile t and 32-column block kb the 128 rows' 16 (Q4_0) or 32
+// (Q8_0) payload bytes are contiguous ([tile][block][row][bytes]; Q4_0 nibbles pre-ordered so that masks give f16 pairs
+// in column order), scales are [tile][block][row] f16. Same byte count as the GGUF encoding; rows padded to 128 with
+// zero scales. Both linear kernels (qlinear_mv.cu, qlinear_umma.cu) read this one layout.
 struct TiledWeight {
-  int layout = kLayoutMma16;
   int codec = 0;
-  int64_t rows = 0;         // logical rows (outputs) as seen by the mma tiles (after concatenation/interleave)
-  int64_t rows_padded = 0;  // multiple of 16
+  int64_t rows = 0;         // logical rows (outputs) after concatenation / interleave
+  int64_t rows_padded = 0;  // multiple of 128
   int64_t columns = 0;      // multiple of 64
   int interleave8 = 0;
   uint8_t* quants = nullptr;
   __half* scales = nullptr;
   size_t quant_bytes = 0, scale_bytes = 0;
-  // arrival tickets, zero between launches: kLayoutStream256 [rows_padded/256][4]; kLayoutUmma128 [rows_padded/128]
-  // (taken by the matvec kernel's CTAs that hold part of a tile's K; the last one to arrive finishes the tile)
+  // [rows_padded/128] arrival tickets, zero between launches: taken by the matvec kernel's CTAs that hold part of a row
+  // group's K; the last one to arrive finishes the group
   int* counters = nullptr;
 };
 struct RepackParts {
@@ -47,17 +44,6 @@ struct RepackParts {
 };
 cudaError_t launch_repack(const TiledWeight& w, const RepackParts& parts, cudaStream_t stream);
 
-struct TiledPlan {
-  int nt = 4;        // n-tiles of 8 input vectors held per pass (1, 2 or 4)
-  int splits = 1;    // split-K factor (grid.y)
-  int grid_x = 1;
-  size_t scratch_bytes = 0;  // splits > 1: [splits][nt*8][rows_padded] f32
-};
-TiledPlan plan_tiled(const TiledWeight& w, int64_t vectors, int sm_count);
-// mma.sync path: one pass handles up to 32 vectors; the launcher loops passes. epilogue: etc_epilogue.
-cudaError_t launch_qlinear_mma16(const TiledWeight& w, const float* x, int64_t vectors, const float* bias,
-                                 const float* residual, int epilogue, float* out, float* scratch, int sm_count,
-                                 cudaStream_t stream, int* launches);
 // out_xh (optional): the result also stored as f16 in [cols/8][xh_nv][8] order for the next linear.
 cudaError_t launch_qlinear_reduce(const float* scratch, int splits, int vpad, int vectors, int rows, int rows_padded,
                                   const float* bias, const float* residual, int epilogue, float* out, __half* out_xh,
@@ -93,25 +79,10 @@ cudaError_t launch_qlinear_mv(const TiledWeight& w, const float* x, const __half
                               const float* residual, int epilogue, float* out, __half* out_xh, void* scratch,
                               DeviceStatus* status, int sm_count, cudaStream_t stream, int* launches, int xh_nv = 32);
 
-// stream-K tcgen05 path (qlinear_stream.cu): up to kStreamMaxVectors vectors per pass
-constexpr int kStreamMaxVectors = 128;
-struct StreamPlan {
-  int nvp = 32;  // vectors per pass padded to 32
-  int tiles = 1, spt = 1, total_units = 1, units_per_cta = 1, grid = 1, slot_mode = 0, own_sum = 1;
-  size_t xh_bytes = 0;       // f16 activations in [K/8][nvp][8] order
-  size_t partial_bytes = 0;  // partial sums of ranges that cover part of a tile
-};
-StreamPlan plan_stream(const TiledWeight& w, int64_t vectors, int sm_count);
-size_t stream_weight_bytes(int codec, int64_t rows_padded, int64_t columns);
-cudaError_t launch_repack_stream(const TiledWeight& w, const RepackParts& parts, cudaStream_t stream);
-cudaError_t launch_qlinear_stream(const TiledWeight& w, const float* x, const __half* xh_ready, int64_t vectors, const float* bias,
-                                  const float* residual, int epilogue, float* out, __half* out_xh, __half* xh, float* partials,
-                                  DeviceStatus* status, int sm_count, cudaStream_t stream, int* launches);
-
-// Layout-independent front end. `scratch` must hold tiled_scratch_bytes(w, vectors, sm_count).
+// Front end of the tiled linear. `scratch` must hold tiled_scratch_bytes(w, vectors, sm_count).
 size_t tiled_scratch_bytes(const TiledWeight& w, int64_t vectors, int sm_count);
 // xh_ready / out_xh: optional f16 activation hand-off between kernels, [K/8][xh_nv][8] with xh_nv = hand_off_stride(batch)
-// (tcgen05 layouts; the 128-row layout takes up to 128 vectors that way, the stream-K layout 32).
+// (up to 128 vectors).
 cudaError_t launch_qlinear_tiled(const TiledWeight& w, const float* x, int64_t vectors, const float* bias,
                                  const float* residual, int epilogue, float* out, void* scratch, DeviceStatus* status,
                                  int sm_count, cudaStream_t stream, int* launches, const __half* xh_ready = nullptr,

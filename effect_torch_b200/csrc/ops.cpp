@@ -147,12 +147,7 @@ etc_status build_qweight(etc_runtime* rt, int codec, const void* const* parts, c
   etc_qweight* w = new etc_qweight();
   w->rt = rt;
   w->tiled.codec = codec;
-  // The tcgen05 kernel with 128-row tiles is the default; ETC_TILED_LAYOUT=stream256 selects the stream-K tcgen05 kernel
-  // (weights on the MMA's N side), ETC_TILED_LAYOUT=mma16 the mma.sync kernel, both kept for comparison.
-  const char* layout_env = std::getenv("ETC_TILED_LAYOUT");
-  const std::string layout_name = layout_env ? layout_env : "";
-  w->tiled.layout = layout_name == "mma16" ? kLayoutMma16 : (layout_name == "stream256" ? kLayoutStream256 : kLayoutUmma128);
-  const int64_t row_tile = w->tiled.layout == kLayoutStream256 ? 256 : (w->tiled.layout == kLayoutUmma128 ? 128 : 16);
+  const int64_t row_tile = 128;
   w->tiled.rows = rows;
   w->tiled.rows_padded = (rows + row_tile - 1) / row_tile * row_tile;
   w->tiled.columns = columns;
@@ -160,13 +155,7 @@ etc_status build_qweight(etc_runtime* rt, int codec, const void* const* parts, c
   const int64_t kblocks = columns / 32;
   w->tiled.quant_bytes = (size_t)w->tiled.rows_padded * kblocks * (codec == ETC_CODEC_Q4_0 ? 16 : 32);
   w->tiled.scale_bytes = (size_t)w->tiled.rows_padded * kblocks * 2;
-  size_t counter_bytes = 0;
-  if (w->tiled.layout == kLayoutStream256) {  // payload and scales share one array of chunks
-    w->tiled.quant_bytes = stream_weight_bytes(codec, w->tiled.rows_padded, columns);
-    w->tiled.scale_bytes = 0;
-    counter_bytes = (size_t)(w->tiled.rows_padded / 256) * 4 * sizeof(int);
-  }
-  if (w->tiled.layout == kLayoutUmma128) counter_bytes = (size_t)(w->tiled.rows_padded / 128) * sizeof(int);
+  const size_t counter_bytes = (size_t)(w->tiled.rows_padded / 128) * sizeof(int);
   etc_status st = rt->device_alloc(w->tiled.quant_bytes, (void**)&w->tiled.quants);
   if (st == ETC_OK && w->tiled.scale_bytes) st = rt->device_alloc(w->tiled.scale_bytes, (void**)&w->tiled.scales);
   if (st == ETC_OK && counter_bytes) {

@@ -1,47 +1,49 @@
-// Dequant matvec for small decode batches (up to 32 input vectors) on Q4_0 / Q8_0 weights: the HBM-bound member of
-// the quantized-linear family.
+// Dequant matvec for small decode batches (up to 16 input vectors) on Q4_0 / Q8_0 weights.
 //
 //   out[v, r] = sum_k x[v, k] * deq(W[r, k])        (quantized_linear, crates/runtime-cpu/src/quantized.rs:419-499)
 //
 // Why a second kernel beside the tcgen05 one: one tcgen05.mma retires 128 weight rows x 16 columns in about 130 cycles
-// whatever the number of vectors, which caps that kernel at 0.4 of what HBM delivers for Q4_0; the legacy tensor path
-// (mma.sync m16n8k16: one instruction per 256 weights and 8 vectors, 0.46 instructions per cycle per SM, the same
-// physical pipe) spends half the pipe time per weight at 32 vectors and almost none at 8. It reads the same 128-row
-// tile layout, so a weight has one copy in HBM.
+// whatever the number of vectors (measured: 131 cycles for every N <= 128 at 1965 MHz), which caps that kernel at 0.4 of
+// what HBM delivers for Q4_0. The legacy tensor path (mma.sync m16n8k16: one instruction per 256 weights and 8
+// vectors, 0.46 instructions per cycle per SM on the same physical pipe) needs a quarter of the pipe at 16 vectors and
+// an eighth at 8, so there the work is bounded by the dequantisation instructions and by memory, not by the pipe. It
+// reads the same 128-row tile layout, so a weight has one copy in HBM.
 //
-// Data flow per CTA (8 consumer warps + 1 copy warp, two CTAs per SM):
-//   * the copy warp fills a ring of 4 stages in shared memory. A stage is a row group (one 128-row layout tile, or two
-//     adjacent ones at 32 vectors) x 8, 4 or 2 blocks of 32 columns: per layout tile the packed weights
-//     [block][128 rows][16 or 32 B] and the scales [block][128] f16 are each contiguous, so they arrive as bulk copies
-//     (cp.async.bulk, completion counted in bytes on the stage's mbarrier); the stage's activations (f16, hand-off
-//     layout [K/8][stride][8]) arrive as 16-byte cp.async copies issued by all 32 lanes, which arrive on the same
-//     mbarrier when they land. Weights do not depend on the previous kernel of the stream, so under programmatic
-//     dependent launch the first stages' weights stream in while that kernel is still finishing; activations follow
-//     after the grid dependency wait.
-//   * consumer warp w owns rows 16w..16w+15 of every layout tile of the group (one or two m16 tiles) for the whole K
-//     range of the CTA: nothing is summed across warps. It fetches packed words with ldmatrix.x4 (lane (g, t) receives
-//     word t of rows g and g+8, which is exactly the A-fragment ownership of mma.m16n8k16), splices nibbles / bytes
-//     into f16 mantissas (lop3 / prmt + one hsub2 or hfma2), reads the B fragments of a block with 16-byte
-//     shared-memory loads (groups padded so that the four t lanes hit different banks) and issues two MMAs per block and
-//     8 vectors. Up to 16 vectors the integer codes go through the MMA unscaled and the f32 block scale is applied to
-//     the block's partial sums (4 FFMA per 8 vectors); at 32 the scale is multiplied into the f16 weights instead,
-//     which is cheaper per vector. Inside a block, lane t owns logical columns 8t..8t+7 (Q4_0) or 4t..4t+3 and
-//     16+4t..16+4t+3 (Q8_0) on both operands, so no data is shuffled between lanes.
-//   * work is cut stream-K style: units (row group, stage) in group-major order, an equal contiguous run per CTA. A
-//     run's segment that covers its group's whole K applies the epilogue straight from the accumulator registers
-//     (SwiGLU pairs a gate row g with its up row g+8 inside one thread); otherwise the CTA stores its partial sums and
-//     takes a ticket on the group: the last CTA to arrive adds the pieces in CTA order (deterministic) and applies the
-//     epilogue. Nobody waits for another CTA.
-// Every mbarrier wait is bounded; on expiry the abort flag is raised, all roles run their loops dry (barriers keep
-// matching), the copy warp lets its copies land, and the status word reports 3. Tickets of groups that were in flight
-// at that moment may be left non-zero: weights that were used by a call that ended with that status must be rebuilt.
+// Data flow per CTA (8 consumer warps + 1 copy warp; three CTAs per SM at 8 vectors, two at 16):
+//   * the copy warp fills a ring of 3 or 4 stages in shared memory. A stage is one 128-row layout tile x 8 (Q4_0) or 4
+//     (Q8_0) blocks of 32 columns: the packed weights [block][128 rows][16 or 32 B] and the scales [block][128] f16 are
+//     each contiguous in the layout, so they arrive as two bulk copies (cp.async.bulk, completion counted in bytes on
+//     the stage's mbarrier); the stage's activations (f16, hand-off layout [K/8][stride][8]) arrive as 16-byte cp.async
+//     copies issued by all 32 lanes, which arrive on the same mbarrier when they land. Weights do not depend on the
+//     previous kernel of the stream, so under programmatic dependent launch the first stage's weights are requested
+//     before the grid dependency wait; the rest of the ring follows once that stage has landed, so that every CTA's
+//     first stage is served ahead of everybody's second and the consumers start early.
+//   * consumer warp w owns rows 16w..16w+15 of the tile for the whole K range of the CTA: nothing is summed across
+//     warps. It fetches the packed words of two blocks with one ldmatrix.x4 (lane (g, t) receives word t of rows g and
+//     g+8, which is exactly the A-fragment ownership of mma.m16n8k16), splices nibbles / bytes into f16 mantissas (one
+//     three-input logic op or byte permute, then one hsub2 / hfma2 that removes the splice bias and the code offset; the
+//     constants live in registers because the two-immediate forms cost an extra instruction each), reads the B
+//     fragments of a block with 16-byte shared-memory loads (column groups padded so that the four t lanes hit
+//     different banks) and issues two MMAs per block and 8 vectors. The integer codes go through the MMA unscaled; the
+//     f32 block scale is applied to the block's partial sums (4 FFMA per 8 vectors). Inside a block, lane t owns logical
+//     columns 8t..8t+7 (Q4_0) or 4t..4t+3 and 16+4t..16+4t+3 (Q8_0) on both operands, so no data moves between lanes.
+//   * work is cut stream-K style: units (tile, stage) in tile-major order, an equal contiguous run per CTA. A run's
+//     segment that covers its tile's whole K applies the epilogue straight from the accumulator registers (SwiGLU pairs
+//     a gate row g with its up row g+8 inside one thread). Only the first and the last segment of a run can cover part
+//     of a tile's K: the consumers store such partial sums and go on; the copy warp draws a ticket on the tile once the
+//     piece is stored; at the end of its run a CTA that drew a tile's last ticket adds the tile's pieces in CTA order
+//     (deterministic) and applies the epilogue. Nobody waits for another CTA.
+// Every mbarrier wait is bounded; on expiry the abort flag is raised, all roles run their loops dry, the copy warp lets
+// its copies land, and the status word reports 3. Tickets of tiles that were in flight at that moment may be left
+// non-zero: weights that were used by a call that ended with that status must be rebuilt.
 //
-// Roofline: HBM up to 16 vectors; at 32 vectors the legacy tensor path (0.46 instructions per cycle per SM, four per
-// 256 weights) allows 0.74 of the Q4_0 HBM rate. Algorithmic bytes = rows*K/32*{18,34} + activation and output bytes.
+// Roofline: HBM. Algorithmic bytes = rows*K/32*{18,34} + activation and output bytes. Measured at 8 vectors, Q4_0:
+// 0.61 of the copy bandwidth on [128256 x 4096], 0.41 on [28672 x 4096], 0.30 on [14336 x 4096] (where ramp-up and the
+// last tickets are a third of the run); the steady state is bounded by instruction issue (about 33 instructions per
+// 512 weights at 1.7 instructions per cycle per SM), not by the ring, which alone streams at 0.85-0.93.
 #include <cuda_fp16.h>
 
 #include <algorithm>
-#include <cstdlib>
 
 #include "chain.cuh"
 #include "kernels.h"
@@ -61,13 +63,14 @@ constexpr int kMvThreads = kMvConsumerThreads + 32;
 template <int CODEC, int NT>
 struct MvCfg {
   static constexpr int kNV = NT * 8;
-  static constexpr int kMT = NT == 4 ? 2 : 1;  // m16 tiles per warp (one in each of kMT layout tiles)
+  static_assert(NT == 1 || NT == 2, "one pass takes 8 or 16 vectors");
+  static constexpr int kMT = 1;  // m16 tiles per warp
   static constexpr int kGroupTiles = kMT * (kMvConsumerWarps / 8);  // layout tiles per row group: 8 warps cover one tile's rows
   static constexpr int kGroupRows = kGroupTiles * kMvRows;
-  static constexpr int kStageBlocks = CODEC == 2 ? (NT == 4 ? 4 : 8) : (NT == 4 ? 2 : 4);
+  static constexpr int kStageBlocks = CODEC == 2 ? 8 : 4;
   static constexpr int kCtasPerSm = NT == 1 ? 3 : 2;
   static constexpr int kStages = NT == 1 ? 3 : 4;
-  static constexpr bool kScaleWeights = NT == 4;  // scale in f16 on the weights instead of on block sums
+  static constexpr bool kScaleWeights = false;  // the f32 block scale is applied to the block's sums, not to the f16 weights
   static constexpr uint32_t kBlockQBytes = CODEC == 2 ? 2048 : 4096;
   static constexpr uint32_t kTileQBytes = kStageBlocks * kBlockQBytes;  // one layout tile's share of a stage
   static constexpr uint32_t kTileSBytes = kStageBlocks * 256;
@@ -101,16 +104,8 @@ struct MvArgs {
   // Splice constants, passed as arguments so that they live in (uniform) registers: with literals the compiler emits
   // two-immediate forms that cost an extra instruction each (a three-input logic op or an f16x2 fma takes one immediate).
   uint32_t c_magic, c_bias_lo, c_sixteenth, c_bias_hi, c_bias_q8, c_perm_fill;
-  int debug;
-  long long* trace;  // development aid: per-CTA time stamps [grid][16], null in normal use
 };
 
-__device__ __forceinline__ long long global_ns() {
-  long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-__device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(kMvConsumerThreads) : "memory"); }
 
 __device__ __forceinline__ void ldmatrix_x4(const void* smem_row, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -267,13 +262,6 @@ __global__ void __launch_bounds__(kMvThreads, (MvCfg<CODEC, NT>::kCtasPerSm)) ql
 
   chain_release();  // the next kernel of the stream may be scheduled; it waits for this one before touching its data
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  long long* trace = a.trace ? a.trace + (size_t)blockIdx.x * 16 : nullptr;
-  if (trace && threadIdx.x == 0) {
-    trace[0] = global_ns();
-    unsigned smid;
-    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-    trace[11] = smid;
-  }
   const int u0 = blockIdx.x * a.upc;
   const int u1 = min(a.units, u0 + a.upc);
   // A run covers the tail of its first group, whole groups, and the head of its last group. Only the first and the last
@@ -310,7 +298,7 @@ __global__ void __launch_bounds__(kMvThreads, (MvCfg<CODEC, NT>::kCtasPerSm)) ql
       unsigned char* dst = ring + (size_t)s * Cfg::kStageBytes;
       mbar_arrive_expect_tx(bar, (uint32_t)(tiles_here * valid) * (Cfg::kBlockQBytes + 256u));
       for (int m = 0; m < tiles_here; ++m) {
-        const size_t block_index = (size_t)((a.debug & 4) ? m : group * TG + m) * a.kblocks + kb;  // debug bit 4: L2-resident weights
+        const size_t block_index = (size_t)(group * TG + m) * a.kblocks + kb;
         bulk_copy_g2s(dst + (size_t)m * Cfg::kTileQBytes, a.quants + block_index * Cfg::kBlockQBytes, (uint32_t)valid * Cfg::kBlockQBytes, bar);
         bulk_copy_g2s(dst + Cfg::kStageQBytes + (size_t)m * Cfg::kTileSBytes, a.scales + block_index * kMvRows, (uint32_t)valid * 256u, bar);
       }
@@ -337,7 +325,6 @@ __global__ void __launch_bounds__(kMvThreads, (MvCfg<CODEC, NT>::kCtasPerSm)) ql
       weights_issued = 1;
     }
     chain_wait();
-    if (trace && lane == 0) trace[6] = global_ns();
     int st = st_first;
     for (int i = 0; i < n; ++i) {
       const int s = i % STAGES;
@@ -355,7 +342,7 @@ __global__ void __launch_bounds__(kMvThreads, (MvCfg<CODEC, NT>::kCtasPerSm)) ql
       const int valid = min(KS, a.kblocks - kb);
       unsigned char* xdst = ring + (size_t)s * Cfg::kStageBytes + Cfg::kStageQBytes + Cfg::kStageSBytes;
       const __half* xsrc = a.xh + (size_t)kb * 4 * a.xh_nv * 8;
-      for (int c = lane; c < valid * 4 * NV && !(a.debug & 2); c += 32) {
+      for (int c = lane; c < valid * 4 * NV; c += 32) {
         const int grp = c / NV, row = c - grp * NV;
         cp_async_16(xdst + (size_t)grp * GS + row * 16, xsrc + ((size_t)grp * a.xh_nv + row) * 8);
       }
@@ -371,7 +358,6 @@ __global__ void __launch_bounds__(kMvThreads, (MvCfg<CODEC, NT>::kCtasPerSm)) ql
       if (++st == a.spt) st = 0;
     }
     cp_async_wait_all();
-    if (trace && lane == 0) trace[7] = global_ns();
     if (lane == 0) {
       take_ticket(0, true);
       take_ticket(1, true);
@@ -395,9 +381,6 @@ __global__ void __launch_bounds__(kMvThreads, (MvCfg<CODEC, NT>::kCtasPerSm)) ql
     bool alive = true;
 
     chain_wait();  // outputs, partials and tickets belong to the stream's earlier kernels until here
-    const bool tr = trace && threadIdx.x == 0;
-    long long wait_cycles = 0, seg_cycles = 0;
-    if (tr) trace[1] = global_ns();
     int group = group_first, st = st_first;
 #pragma unroll
     for (int m = 0; m < MT; ++m)
@@ -409,13 +392,11 @@ __global__ void __launch_bounds__(kMvThreads, (MvCfg<CODEC, NT>::kCtasPerSm)) ql
       const int i = u - u0, s = i % STAGES;
       const uint32_t parity = (uint32_t)(i / STAGES) & 1;
       const int valid = min(KS, a.kblocks - st * KS);
-      const long long tw0 = tr ? clock64() : 0;
       if (alive) alive = mbar_wait_warp(&full[s], parity, flags);
-      if (tr) { wait_cycles += clock64() - tw0; if (u == u0) trace[2] = global_ns(); }
       const unsigned char* stage_q = ring + (size_t)s * Cfg::kStageBytes;
       const __half* stage_s = reinterpret_cast<const __half*>(stage_q + Cfg::kStageQBytes);
       const unsigned char* stage_x = stage_q + Cfg::kStageQBytes + Cfg::kStageSBytes;
-      if (alive && !(a.debug & 1)) {
+      if (alive) {
         if (CODEC == 2) {
 #pragma unroll
           for (int kbl = 0; kbl < KS; kbl += 2) {
@@ -483,10 +464,8 @@ __global__ void __launch_bounds__(kMvThreads, (MvCfg<CODEC, NT>::kCtasPerSm)) ql
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty[s]);
 
-      if (tr && u + 1 == u1) trace[3] = global_ns();
       if (u + 1 == u1 || st + 1 == a.spt) {
         // ---------------------------------------------------------------- end of a group segment
-        const long long ts0 = tr ? clock64() : 0;
         const bool is_piece = (group == group_first && piece0) || (group == group_last && group != group_first && piece1);
         if (!is_piece) {
           if (!flags[0]) {
@@ -513,11 +492,9 @@ __global__ void __launch_bounds__(kMvThreads, (MvCfg<CODEC, NT>::kCtasPerSm)) ql
           for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc[m][nt][e] = 0.0f;
-        if (tr) seg_cycles += clock64() - ts0;
       }
       if (++st == a.spt) { st = 0; ++group; }
     }
-    if (tr) trace[10] = global_ns();
     // ---------------------------------------------------------------- groups this CTA drew the last ticket of
     if (piece0 || piece1) {
       if (alive) alive = mbar_wait_warp(tickets_done, 0, flags);
@@ -555,10 +532,8 @@ __global__ void __launch_bounds__(kMvThreads, (MvCfg<CODEC, NT>::kCtasPerSm)) ql
         }
       }
     }
-    if (tr) { trace[4] = global_ns(); trace[8] = wait_cycles; trace[9] = seg_cycles; }
   }
   __syncthreads();
-  if (trace && threadIdx.x == 0) trace[5] = global_ns();
   if (threadIdx.x == 0 && flags[0]) atomicCAS(a.status, 0ull, 3ull);  // a bounded wait expired
 }
 
@@ -588,48 +563,32 @@ template <int CODEC, int NT>
 cudaError_t launch_mv_pass(const MvArgs& args, int grid, cudaStream_t stream) {
   constexpr size_t smem = MvCfg<CODEC, NT>::kSmemBytes;
   auto kernel = qlinear_mv_kernel<CODEC, NT>;
-  // the shared-memory opt-in is a per-device attribute of the function
-  static bool configured[64] = {};
-  int device = 0;
-  cudaError_t e = cudaGetDevice(&device);
-  if (e != cudaSuccess) return e;
-  if (device < 0 || device >= 64 || !configured[device]) {
-    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-    if (device >= 0 && device < 64) configured[device] = true;
-  }
+  const cudaError_t attr = opt_in_shared_memory(kernel, smem);
+  if (attr != cudaSuccess) return attr;
   return launch_chained(kernel, dim3((unsigned)grid), dim3((unsigned)kMvThreads), smem, stream, args);
-}
-
-int env_int(const char* name, int fallback) {
-  const char* v = std::getenv(name);
-  return v && *v ? std::atoi(v) : fallback;
 }
 
 size_t mv_xh_region(int nt, int64_t columns) { return ((size_t)(columns / 8) * nt * 8 * 16 + 255) & ~(size_t)255; }
 
 }  // namespace
 
-int mv_max_vectors() {
-  static const int value = std::max(0, std::min(32, env_int("ETC_MV_MAX_VECTORS", 16)));
-  return value;
-}
+// Measured on a B200 (Q4_0 and Q8_0, rows x K from 4096 x 4096 to 128256 x 4096): the matvec kernel is ahead of the tcgen05
+// kernel up to 16 vectors (1.1x to 1.4x on the large shapes) and behind it at 32, where both paths are bound by the one
+// tensor pipe and the tcgen05 kernel's per-weight instruction count is lower.
+int mv_max_vectors() { return 16; }
 
 MvPlan plan_mv(const TiledWeight& w, int64_t vectors, int sm_count) {
   MvPlan p;
-  const int64_t v = std::min<int64_t>(vectors, 32);
-  p.nt = v <= 8 ? 1 : (v <= 16 ? 2 : 4);
-  const int mt = (p.nt == 4 ? 2 : 1) * (kMvConsumerWarps / 8);  // layout tiles per row group
-  const int ks = w.codec == 2 ? (p.nt == 4 ? 4 : 8) : (p.nt == 4 ? 2 : 4);
+  p.nt = vectors <= 8 ? 1 : 2;  // one pass takes up to 16 vectors
+  const int mt = kMvConsumerWarps / 8;  // layout tiles per row group
+  const int ks = w.codec == 2 ? 8 : 4;
   const int kblocks = (int)(w.columns / 32);
   p.tiles = (int)(w.rows_padded / kMvRows);
   p.groups = (p.tiles + mt - 1) / mt;
   p.spt = (kblocks + ks - 1) / ks;
   p.units = p.groups * p.spt;
-  static const int ctas_env = env_int("ETC_MV_CTAS_PER_SM", 0);
-  static const int min_units = std::max(1, env_int("ETC_MV_MIN_UNITS", 2));
-  const int target = std::max(1, sm_count) * (ctas_env > 0 ? ctas_env : (p.nt == 1 ? 3 : 2));
-  p.upc = std::max((p.units + target - 1) / target, std::min(min_units, p.spt));
+  const int target = std::max(1, sm_count) * (p.nt == 1 ? 3 : 2);  // resident CTAs: three per SM at 8 vectors, else two
+  p.upc = std::max((p.units + target - 1) / target, std::min(2, p.spt));  // at least two stages per CTA
   p.grid = (p.units + p.upc - 1) / p.upc;
   p.xh_bytes = mv_xh_region(p.nt, w.columns);
   p.partial_bytes = (size_t)p.grid * 2 * p.nt * 8 * mt * kMvRows * sizeof(float);
@@ -642,11 +601,11 @@ cudaError_t launch_qlinear_mv(const TiledWeight& w, const float* x, const __half
   if (!w.counters) return cudaErrorInvalidValue;
   const int out_cols = (int)(epilogue == ETC_EPILOGUE_SWIGLU ? w.rows / 2 : w.rows);
   const int K = (int)w.columns;
-  for (int64_t v0 = 0; v0 < vectors; v0 += 32) {
-    const int64_t chunk = std::min<int64_t>(32, vectors - v0);
+  for (int64_t v0 = 0; v0 < vectors; v0 += 16) {
+    const int64_t chunk = std::min<int64_t>(16, vectors - v0);
     const MvPlan plan = plan_mv(w, chunk, sm_count);
     const int nv = plan.nt * 8;
-    const bool single = vectors <= 32;  // the hand-off layouts hold one pass
+    const bool single = vectors <= 16;  // the hand-off layouts hold one pass
     MvArgs a;
     a.quants = w.quants;
     a.scales = w.scales;
@@ -660,11 +619,8 @@ cudaError_t launch_qlinear_mv(const TiledWeight& w, const float* x, const __half
       const unsigned cgrid = (unsigned)std::min((total + 255) / 256, 148 * 2);
       const float* xin = x + v0 * w.columns;
       cudaError_t ce;
-      switch (plan.nt) {
-        case 1: ce = launch_chained(mv_convert_kernel<8>, dim3(cgrid), dim3(256), 0, stream, xin, (int)chunk, K, xh_scratch); break;
-        case 2: ce = launch_chained(mv_convert_kernel<16>, dim3(cgrid), dim3(256), 0, stream, xin, (int)chunk, K, xh_scratch); break;
-        default: ce = launch_chained(mv_convert_kernel<32>, dim3(cgrid), dim3(256), 0, stream, xin, (int)chunk, K, xh_scratch); break;
-      }
+      if (plan.nt == 1) ce = launch_chained(mv_convert_kernel<8>, dim3(cgrid), dim3(256), 0, stream, xin, (int)chunk, K, xh_scratch);
+      else ce = launch_chained(mv_convert_kernel<16>, dim3(cgrid), dim3(256), 0, stream, xin, (int)chunk, K, xh_scratch);
       if (ce != cudaSuccess) return ce;
       if (launches) ++*launches;
       a.xh = xh_scratch;
@@ -692,18 +648,10 @@ cudaError_t launch_qlinear_mv(const TiledWeight& w, const float* x, const __half
     a.c_bias_hi = 0xD480D480u;    // -72 = 0xD480
     a.c_bias_q8 = 0x64806480u;    // 1152 = 0x6480
     a.c_perm_fill = 0x64646464u;
-    a.debug = env_int("ETC_MV_DEBUG", 0);
-    {
-      const char* t = std::getenv("ETC_MV_TRACE");
-      a.trace = t && *t ? reinterpret_cast<long long*>(std::strtoull(t, nullptr, 0)) : nullptr;
-    }
     cudaError_t e;
     const bool q4 = w.codec == 2;
-    switch (plan.nt) {
-      case 1: e = q4 ? launch_mv_pass<2, 1>(a, plan.grid, stream) : launch_mv_pass<8, 1>(a, plan.grid, stream); break;
-      case 2: e = q4 ? launch_mv_pass<2, 2>(a, plan.grid, stream) : launch_mv_pass<8, 2>(a, plan.grid, stream); break;
-      default: e = q4 ? launch_mv_pass<2, 4>(a, plan.grid, stream) : launch_mv_pass<8, 4>(a, plan.grid, stream); break;
-    }
+    if (plan.nt == 1) e = q4 ? launch_mv_pass<2, 1>(a, plan.grid, stream) : launch_mv_pass<8, 1>(a, plan.grid, stream);
+    else e = q4 ? launch_mv_pass<2, 2>(a, plan.grid, stream) : launch_mv_pass<8, 2>(a, plan.grid, stream);
     if (e != cudaSuccess) return e;
     if (launches) ++*launches;
   }

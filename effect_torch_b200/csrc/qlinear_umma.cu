@@ -21,9 +21,10 @@
 // Every mbarrier wait is bounded: on expiry the thread raises the abort flag and the status word, all
 // roles fall through to the teardown, TMEM is freed and the kernel returns.
 //
-// Roofline: algorithmic bytes = rows*K/32*{18,34} + 2*NV*K + 4*V*rows. At NV <= 32 the kernel is bound by the rate at
-// which an SM retires tcgen05.mma instructions (about 100 cycles each for any N <= 128, i.e. 2048 weights per 100
-// cycles), below what HBM could feed; at NV = 256 it is tensor-throughput bound.
+// Roofline: algorithmic bytes = rows*K/32*{18,34} + 2*NV*K + 4*V*rows. At NV <= 128 the kernel is bound by the rate at
+// which an SM retires tcgen05.mma instructions: measured 131 cycles each at 1965 MHz for every N <= 128 (M = 64 or 128,
+// A in tensor or shared memory, one to four accumulators), i.e. 2048 weights per 131 cycles = 0.39 of what HBM could
+// feed for Q4_0; at NV = 256 (138 cycles) it is tensor-throughput bound.
 #include <cuda_fp16.h>
 
 #include <algorithm>
@@ -364,12 +365,8 @@ template <int CODEC, int NV>
 cudaError_t launch_umma_pass(const UmmaArgs& args, int tiles, int splits, cudaStream_t stream) {
   constexpr size_t smem = UmmaCfg<NV>::kSmemBytes;
   auto kernel = qlinear_umma_kernel<CODEC, NV>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-    configured = true;
-  }
+  const cudaError_t attr = opt_in_shared_memory(kernel, smem);
+  if (attr != cudaSuccess) return attr;
   // chained: set-up, weight loads and their expansion do not depend on the previous kernel and start under its tail
   return launch_chained(kernel, dim3((unsigned)tiles, (unsigned)splits), dim3((unsigned)UmmaCfg<NV>::kThreads), smem, stream, args);
 }

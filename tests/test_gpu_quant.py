@@ -17,13 +17,6 @@ SCALE_FIELDS = {gv.Q4_0: [0], gv.Q8_0: [0], gv.Q2_K: [80, 82], gv.Q3_K: [108], g
 REL_TOL = 2e-3  # north-star tolerance on f16/f32 linear outputs, as max |err| / max |ref|
 
 
-@pytest.fixture(params=["stream256", "umma128", "mma16"])
-def tiled_layout(request, monkeypatch):
-    """Both tensor-core tilings: the tcgen05 kernel (default) and the mma.sync kernel; read at weight creation."""
-    monkeypatch.setenv("ETC_TILED_LAYOUT", request.param)
-    return request.param
-
-
 def random_packed(codec, rows, columns, seed):
     """Random packed bytes with finite f16 scale fields (every bit pattern of the code bytes is legal)."""
     rng = np.random.default_rng(seed)
@@ -125,7 +118,7 @@ def test_embedding_reports_out_of_range_indexes(index):
 
 
 @pytest.mark.parametrize("codec", [gv.Q4_0, gv.Q8_0])
-def test_tiling_preserves_every_weight(codec, tiled_layout):
+def test_tiling_preserves_every_weight(codec):
     """x = identity picks out single weights: the tensor-core tiling must hold the same dequantised values
     (to f16 rounding of scale*code, the operand precision of the MMA path)."""
     rng = np.random.default_rng(7)
@@ -144,7 +137,7 @@ def test_tiling_preserves_every_weight(codec, tiled_layout):
 @pytest.mark.parametrize("codec", [gv.Q4_0, gv.Q8_0])
 @pytest.mark.parametrize("rows,columns", [(256, 512), (200, 1024), (1024, 4096)])
 @pytest.mark.parametrize("vectors", [1, 5, 8, 9, 16, 32, 40, 64, 100, 300])
-def test_tiled_linear_matches_the_oracle(codec, rows, columns, vectors, tiled_layout):
+def test_tiled_linear_matches_the_oracle(codec, rows, columns, vectors):
     rng = np.random.default_rng(rows + columns + vectors)
     w = rng.normal(0, 0.02, size=(rows, columns)).astype(np.float32)
     packed = orc.quantize(codec, w)
@@ -158,7 +151,7 @@ def test_tiled_linear_matches_the_oracle(codec, rows, columns, vectors, tiled_la
 
 @pytest.mark.parametrize("codec", [gv.Q4_0, gv.Q8_0])
 @pytest.mark.parametrize("vectors", [4, 32])
-def test_tiled_linear_epilogues(codec, vectors, tiled_layout):
+def test_tiled_linear_epilogues(codec, vectors):
     rng = np.random.default_rng(9)
     d, ffn = 512, 384
     gate = rng.normal(0, 0.05, size=(ffn, d)).astype(np.float32)
