@@ -6,8 +6,8 @@
 Workload (N=1 and every rank at N>1): a Llama-3-8B-shaped model with random weights — 32 layers, d_model 4096,
 32 query x 128 / 8 KV heads, SwiGLU FFN 14336, vocabulary 128256, RoPE theta 500000; projections and head
 ~N(0, 0.02) quantized to Q4_0 (token embedding and norms f32); f16 paged KV with 16-token pages; batch 32 prompts of
-512 random token ids (fed one token per step through the decode path), then greedy decode. One "step" is one
-decode step of the whole batch (32 tokens). All inputs are synthetic (seeded); there is no dataset.
+512 random token ids, prefilled in chunks, then greedy decode. One "step" is one decode step of the whole batch
+(32 tokens). All inputs are synthetic (seeded); there is no dataset.
 
 Printed JSON line (rank 0):
   value     decode tokens/s with ids, tables and weights resident in HBM: K steps replayed as one CUDA graph per step
@@ -16,7 +16,10 @@ Printed JSON line (rank 0):
             step's token ids / lane descriptors / page tables host->device and reads the sampled tokens back
   roofline  the dominant kernel (tcgen05 Q4_0 linear, fused gate/up shape [28672 x 4096], 32 vectors) timed alone with
             CUDA events on the launching stream (graph replays) over weight sets larger than L2
+  roofline_by_projection / roofline_attention   the other launches of a decode step, timed the same way
+  linear_microbench / attention_microbench      the quantized-matmul and paged-attention microbenchmark shapes
   cpu_baseline  the CPU oracle (restatement of the reference CPU backend) on a bounded sample, host cores stated
+  tp        the Llama-3-70B shape, batch 64, tensor parallel over the N ranks (at N=1: the whole model on one GPU)
 """
 from __future__ import annotations
 
@@ -35,8 +38,10 @@ sys.path.insert(0, ROOT)
 
 MODEL = dict(layers=32, d_model=4096, q_heads=32, kv_heads=8, head_dim=128, ffn=14336, vocab=128256, rms_eps=1e-5,
              rope_theta=500000.0)
+MODEL_70B = dict(layers=80, d_model=8192, q_heads=64, kv_heads=8, head_dim=128, ffn=28672, vocab=128256, rms_eps=1e-5,
+                 rope_theta=500000.0)
 BATCH, PROMPT, BLOCK = 32, 512, 16
-Q4_0 = 2
+Q4_0, Q8_0 = 2, 8
 METRIC = "decode tokens/s, Llama-3-8B-shape Q4_0 batch 32; kernel HBM GB/s vs peak"
 
 
@@ -46,6 +51,28 @@ def measured_peaks():
         with open(path) as f:
             return json.load(f), "measured"
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+def profile_number(file_name, key):
+    """A figure from a committed ncu summary: the first line of profiles/<file_name> that reads `key: <number>`."""
+    path = os.path.join(ROOT, "profiles", file_name)
+    try:
+        with open(path) as f:
+            for line in f:
+                if line.strip().startswith(key + ":"):
+                    return float(line.split(":", 1)[1].split()[0].replace(",", ""))
+    except OSError:
+        pass
+    return None
+
+
+def host_threads():
+    """Cores this process may run on (a launcher may have set OMP_NUM_THREADS=1; the CPU arm passes its thread count
+    to the oracle explicitly)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
 
 
 def algorithmic_bytes_per_step(model, batch, mean_ctx):
@@ -104,18 +131,21 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------------ CPU reference arm
-def cpu_sample(model, batch, ctx, threads, fraction, seed=3):
+def cpu_sample(model, batch, ctx, threads, fraction, seed=3, faithful=False):
     """Times the CPU oracle on a bounded sample of one decode step and scales it to the whole step.
 
     Every projection of one layer and the head are timed on a row slice (`fraction` of the rows, all columns,
     all `batch` vectors); paged attention is timed on `fraction` of the lanes at context `ctx`; norms, RoPE and
     SwiGLU are timed at full size. Slice times are divided by their fraction and the layer time is multiplied by
-    the layer count. Returns (tokens/s, seconds of CPU work done, description)."""
+    the layer count. `faithful`: the reference's own loop structure on one thread (every block decoded again for every
+    vector, attention scores recomputed per output column); otherwise the same arithmetic with every block decoded once
+    per row and scores cached, over `threads` threads. Returns (tokens/s, seconds of CPU work done, description)."""
     import oracle as orc
     rng = np.random.default_rng(seed)
     d, qw, kvw, ffn, V, L = (model["d_model"], model["q_heads"] * model["head_dim"], model["kv_heads"] * model["head_dim"],
                              model["ffn"], model["vocab"], model["layers"])
     work = 0.0
+    lin_threads = 0 if faithful else threads  # 0 selects the reference-faithful scalar loop of the oracle
 
     def linear_seconds(rows, cols):
         nonlocal work
@@ -124,7 +154,7 @@ def cpu_sample(model, batch, ctx, threads, fraction, seed=3):
         packed = orc.quantize(orc.Q4_0, w)
         x = rng.standard_normal((batch, cols), dtype=np.float32)
         t0 = time.perf_counter()
-        orc.qlinear(orc.Q4_0, x, packed, r, cols, threads=threads)
+        orc.qlinear(orc.Q4_0, x, packed, r, cols, threads=lin_threads)
         dt = time.perf_counter() - t0
         work += dt
         return dt * rows / r
@@ -146,7 +176,8 @@ def cpu_sample(model, batch, ctx, threads, fraction, seed=3):
     q = rng.standard_normal((lanes, model["q_heads"], 1, model["head_dim"]), dtype=np.float32)
     k = rng.standard_normal((lanes, model["kv_heads"], 1, model["head_dim"]), dtype=np.float32)
     t0 = time.perf_counter()
-    orc.kv_attention(pool, 0, seqs, lanes, q, k, k, 1.0 / np.sqrt(model["head_dim"]), mode=1, threads=threads)
+    orc.kv_attention(pool, 0, seqs, lanes, q, k, k, 1.0 / np.sqrt(model["head_dim"]), mode=0 if faithful else 1,
+                     threads=1 if faithful else threads)
     dt = time.perf_counter() - t0
     work += dt
     layer += dt * batch / lanes
@@ -162,24 +193,26 @@ def cpu_sample(model, batch, ctx, threads, fraction, seed=3):
     work += dt
     layer += dt
     step_seconds = layer * L + head
-    sample = (f"one batch-{batch} decode step at context {ctx} of the CPU oracle (restatement of the reference CPU backend; fair "
-              f"variant: every block decoded once per row, attention scores cached) on {threads} threads: {fraction:.4f} of the "
-              f"rows of each projection and of the lanes of paged attention in 1 of {L} layers, plus the head slice, scaled to "
-              f"the full step (extrapolated)")
+    variant = ("reference-faithful variant: one thread, every block decoded again for every vector, attention scores recomputed per "
+               "output column" if faithful else
+               f"fair variant: every block decoded once per row, attention scores cached, {threads} threads")
+    sample = (f"one batch-{batch} decode step at context {ctx} of the CPU oracle (restatement of the reference CPU backend; {variant}): "
+              f"{fraction:.4f} of the rows of each projection and of the lanes of paged attention in 1 of {L} layers, plus the head "
+              f"slice, scaled to the full step (extrapolated)")
     return batch / step_seconds, work, sample
 
 
-def calibrated_fraction(model, batch, threads, budget_seconds):
-    """Fraction of one layer's rows whose CPU time fits `budget_seconds` (probed on a 1/64 slice)."""
-    _, work, _ = cpu_sample(model, batch, PROMPT, threads, 1.0 / 64)
-    return float(min(1.0, max(1.0 / 256, (1.0 / 64) * budget_seconds / max(work, 1e-6))))
+def calibrated_fraction(model, batch, threads, budget_seconds, faithful=False):
+    """Fraction of one layer's rows whose CPU time fits `budget_seconds` (probed on a small slice)."""
+    probe = 1.0 / 256 if faithful else 1.0 / 64
+    _, work, _ = cpu_sample(model, batch, PROMPT, threads, probe, faithful=faithful)
+    return float(min(1.0, max(1.0 / 512, probe * budget_seconds / max(work, 1e-6))))
 
 
 def run_reference_arm(args, rank):
     if rank != 0:
         return
-    import oracle as orc
-    threads = orc.max_threads()
+    threads = host_threads()
     total = args.warmup + args.steps
     fraction = calibrated_fraction(MODEL, BATCH, threads, 150.0 / max(total, 1))
     values, sample = [], ""
@@ -190,9 +223,12 @@ def run_reference_arm(args, rank):
     value = float(np.mean(values))
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": 1000.0 * BATCH / value, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": 1000.0 * BATCH / value, "ms_per_step_is": "extrapolated from the bounded sample of each step",
+        "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "llama3-8b-shape Q4_0 paged decode, batch 32, prompt 512 (bounded CPU sample per step)",
+        "config": {"workload": f"llama3-8b-shape Q4_0 paged decode: {MODEL['layers']} layers, batch {BATCH}, prompt {PROMPT}, "
+                               f"{args.steps} greedy steps, f16 KV 16-token pages",
+                   "sample": "each step is a bounded CPU sample of that workload, scaled to the full step",
                    "global_batch": BATCH, "parallelism": "cpu"},
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -202,7 +238,23 @@ def run_reference_arm(args, rank):
 
 
 # ------------------------------------------------------------------------------------------------ GPU arm
-def build_decoder(rt, et, torch, model, batch, max_tokens, seed, shared_seed=None):
+def device_quantized(rt, torch, codec, rows, cols, gen):
+    """[rows, cols] ~ N(0, 0.02) drawn on the device in slabs and packed by the library's quantizer."""
+    bb = 18 if codec == Q4_0 else 34
+    packed = torch.empty((rows, cols // 32 * bb), dtype=torch.uint8, device="cuda")
+    step = 32768
+    for r0 in range(0, rows, step):
+        r1 = min(rows, r0 + step)
+        w = torch.randn((r1 - r0, cols), generator=gen, device="cuda", dtype=torch.float32)
+        w.mul_(0.02)
+        torch.cuda.synchronize()
+        rt.quantize_into(codec, w, r1 - r0, cols, packed[r0:r1])
+        rt.synchronize()
+        del w
+    return packed
+
+
+def build_decoder(rt, et, torch, model, batch, max_tokens, seed, shared_seed=None, max_advance=1):
     """Random-init weights of the model's shape. `shared_seed`: tensors that tensor-parallel ranks replicate (embedding,
     head) are drawn from it so that every rank holds the same values; the projections are this rank's own shard."""
     gen = torch.Generator(device="cuda")
@@ -214,246 +266,243 @@ def build_decoder(rt, et, torch, model, batch, max_tokens, seed, shared_seed=Non
     dec = et.Executable(rt, layers=model["layers"], d_model=model["d_model"], q_heads=model["q_heads"], kv_heads=model["kv_heads"],
                         head_dim=model["head_dim"], ffn=model["ffn"], vocab=model["vocab"], rms_eps=model["rms_eps"],
                         rope_theta=model["rope_theta"], batch=batch, max_tokens=max_tokens, block_size=BLOCK, kv_dtype=et.KV_F16,
-                        exact=False, max_advance=1)
+                        exact=False, max_advance=max_advance)
     d, qw, kvw, ffn, V = (model["d_model"], model["q_heads"] * model["head_dim"], model["kv_heads"] * model["head_dim"], model["ffn"],
                           model["vocab"])
-
-    def normal(rows, cols, g=None):
-        w = torch.randn((rows, cols), generator=g or gen, device="cuda", dtype=torch.float32)
-        w.mul_(0.02)
-        return w
-
-    def quantized(rows, cols, g=None):
-        w = normal(rows, cols, g)
-        packed = torch.empty((rows, cols // 32 * 18), dtype=torch.uint8, device="cuda")
-        torch.cuda.synchronize()
-        rt.quantize_into(Q4_0, w, rows, cols, packed)
-        rt.synchronize()
-        return packed
 
     def bind(slot, layer, tensor, codec=0, rows=None, cols=None):
         torch.cuda.synchronize()
         dec.set_weight(slot, layer, tensor, codec=codec, rows=rows, columns=cols)
 
-    bind(et.W_TOK_EMBD, 0, normal(V, d, shared))
+    embd = torch.randn((V, d), generator=shared, device="cuda", dtype=torch.float32)
+    embd.mul_(0.02)
+    bind(et.W_TOK_EMBD, 0, embd)
+    del embd
     ones = torch.ones(d, device="cuda", dtype=torch.float32)
     for l in range(model["layers"]):
         bind(et.W_ATTN_NORM, l, ones)
         bind(et.W_FFN_NORM, l, ones)
         for slot, (r, c) in ((et.W_Q, (qw, d)), (et.W_K, (kvw, d)), (et.W_V, (kvw, d)), (et.W_O, (d, qw)), (et.W_GATE, (ffn, d)),
                              (et.W_UP, (ffn, d)), (et.W_DOWN, (d, ffn))):
-            bind(slot, l, quantized(r, c), Q4_0, r, c)
+            bind(slot, l, device_quantized(rt, torch, Q4_0, r, c, gen), Q4_0, r, c)
     bind(et.W_OUT_NORM, 0, ones)
-    bind(et.W_HEAD, 0, quantized(V, d, shared), Q4_0, V, d)
+    bind(et.W_HEAD, 0, device_quantized(rt, torch, Q4_0, V, d, shared), Q4_0, V, d)
     dec.finalize()
     torch.cuda.empty_cache()
     return dec
 
 
-def time_dominant_kernel(rt, et, torch, model, vectors, iters=40):
-    """The fused gate/up linear [2*ffn x d_model] at `vectors` input rows, alone, over more weight copies than L2 holds."""
-    d, ffn = model["d_model"], model["ffn"]
-    gen = torch.Generator(device="cuda")
-    gen.manual_seed(99)
-    copies = []
-    for _ in range(4):  # 4 x 66 MB > 126 MB L2
-        parts = []
-        for _ in range(2):
-            w = torch.randn((ffn, d), generator=gen, device="cuda", dtype=torch.float32) * 0.02
-            packed = torch.empty((ffn, d // 32 * 18), dtype=torch.uint8, device="cuda")
-            torch.cuda.synchronize()
-            rt.quantize_into(Q4_0, w, ffn, d, packed)
-            rt.synchronize()
-            parts.append(packed)
-        copies.append(et.QWeight(rt, Q4_0, parts, [ffn, ffn], d, interleave8=True))
+def time_linear(rt, et, torch, codec, rows, cols, vectors, interleave=False, epilogue=0, residual=False, target_bytes=300e6, gen=None):
+    """One tiled linear shape alone: CUDA events around replays of a graph that walks over more weight copies than L2
+    holds. Returns (microseconds per call, algorithmic bytes per call). The call includes the linear's own f16 conversion
+    of the activations and, above 16 vectors, its split-K sum launch."""
+    bb = 18 if codec == Q4_0 else 34
+    nparts = 2 if interleave else 1
+    packed_bytes = rows * (cols // 32) * bb
+    copies = max(3, int(np.ceil(target_bytes / packed_bytes)))
+    if gen is None:
+        gen = torch.Generator(device="cuda")
+        gen.manual_seed(rows + cols + codec)
+    weights = []
+    for _ in range(copies):
+        parts = [device_quantized(rt, torch, codec, rows // nparts, cols, gen) for _ in range(nparts)]
+        weights.append(et.QWeight(rt, codec, parts, [rows // nparts] * nparts, cols, interleave8=interleave))
         del parts
-    x = torch.randn((vectors, d), device="cuda", dtype=torch.float32)
-    out = torch.empty((vectors, ffn), device="cuda", dtype=torch.float32)
-    scratch_bytes = copies[0].scratch_bytes(vectors)
-    scratch = torch.empty(max(scratch_bytes, 4), dtype=torch.uint8, device="cuda")
+    out_cols = rows // 2 if epilogue == et.EPILOGUE_SWIGLU else rows
+    x = torch.randn((vectors, cols), generator=gen, device="cuda", dtype=torch.float32)
+    out = torch.empty((vectors, out_cols), device="cuda", dtype=torch.float32)
+    res = torch.randn((vectors, out_cols), generator=gen, device="cuda", dtype=torch.float32) if residual else None
+    need = weights[0].scratch_bytes(vectors)
+    scratch = torch.empty(max(need, 4), dtype=torch.uint8, device="cuda")
     torch.cuda.synchronize()
     stream = torch.cuda.ExternalStream(rt.stream)
-    for i in range(8):
-        copies[i % 4].linear_into(x, vectors, out, epilogue=et.EPILOGUE_SWIGLU, scratch=scratch, scratch_bytes=scratch_bytes)
+
+    def call(i):
+        weights[i % copies].linear_into(x, vectors, out, residual=res, epilogue=epilogue, scratch=scratch, scratch_bytes=need)
+
+    for i in range(copies):
+        call(i)
     rt.synchronize()
-    # a Python launch loop is slower than the kernel: capture the launches once and time replays of the graph
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    iters = 2 * copies
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(graph, stream=stream):
         for i in range(iters):
-            copies[i % 4].linear_into(x, vectors, out, epilogue=et.EPILOGUE_SWIGLU, scratch=scratch, scratch_bytes=scratch_bytes)
+            call(i)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with torch.cuda.stream(stream):
         graph.replay()
-        start.record()
+        a.record()
         graph.replay()
         graph.replay()
-        stop.record()
+        b.record()
     rt.synchronize()
-    ms = start.elapsed_time(stop) / (2 * iters)
-    algorithmic = 2 * ffn * (d // 32) * 18 + 4 * vectors * d + 4 * vectors * ffn
-    for c in copies:
-        c.close()
-    return ms, algorithmic
+    us = a.elapsed_time(b) / (2 * iters) * 1e3
+    algorithmic = packed_bytes + 4 * vectors * cols + 4 * vectors * out_cols
+    del graph
+    for w in weights:
+        w.close()
+    torch.cuda.empty_cache()
+    return us, algorithmic
 
 
-def run_attention_microbench(args):
-    """Paged-attention decode alone (the survey's microbench shape): 64 sequences, 32 query / 8 KV heads of 128, f16 pool of
-    65 536 pages x 16 tokens, contexts ~U[128, 4096] (rounded to 64), one query token per sequence. Prints one JSON line."""
-    import torch
-    import effect_torch_b200 as et
+def roofline_entry(us, algorithmic, peaks, peak_kind, kernel, traffic=None, traffic_source=None):
+    achieved = algorithmic / us / 1e3
+    entry = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+             "traffic": traffic, "peak_kind": peak_kind, "kernel": kernel, "ms_per_launch": us / 1e3,
+             "algorithmic_bytes_per_launch": algorithmic}
+    if traffic_source:
+        entry["traffic_source"] = traffic_source
+    return entry
 
-    torch.cuda.set_device(0)
-    rt = et.Runtime(0)
-    B, Hq, Hkv, D, pages = 64, 32, 8, 128, 65536
-    rng = np.random.default_rng(1)
-    ctx = np.sort((rng.integers(128, 4097, size=B) // 64) * 64)[::-1].copy()
-    pool = et.NativeKvPool(rt, 1, Hkv, D, pages * BLOCK, BLOCK, et.KV_F16)
-    seqs = [pool.makeSequence() for _ in range(B)]
+
+def projection_rooflines(rt, et, torch, model, vectors, peaks, peak_kind):
+    """Every linear launch of a decode step at `vectors` rows, timed alone (see time_linear)."""
+    d, qw, kvw, ffn, V = (model["d_model"], model["q_heads"] * model["head_dim"], model["kv_heads"] * model["head_dim"], model["ffn"],
+                          model["vocab"])
+    shapes = [("qkv", qw + 2 * kvw, d, False, et.EPILOGUE_NONE, False), ("o", d, qw, False, et.EPILOGUE_RESIDUAL, True),
+              ("gate_up", 2 * ffn, d, True, et.EPILOGUE_SWIGLU, False), ("down", d, ffn, False, et.EPILOGUE_RESIDUAL, True),
+              ("head", V, d, False, et.EPILOGUE_NONE, False)]
+    kernel = "qlinear_mv_kernel<Q4_0>" if vectors <= 16 else "qlinear_umma_kernel<Q4_0,32> (+ f16 conversion and split-K sum launches)"
+    out = {}
+    for name, rows, cols, interleave, epilogue, residual in shapes:
+        us, algorithmic = time_linear(rt, et, torch, Q4_0, rows, cols, vectors, interleave, epilogue, residual)
+        out[name] = roofline_entry(us, algorithmic, peaks, peak_kind, f"{kernel} [{rows}x{cols}], {vectors} vectors")
+    return out
+
+
+def linear_microbench_table(rt, et, torch, peaks):
+    """The quantized-matmul microbenchmark: Q4_0 and Q8_0, [4096x4096], [14336x4096], [4096x14336], 1 / 8 / 64 / 512
+    vectors, f32 activations; HBM fraction up to 64 vectors, TFLOP/s at 512."""
+    rows_out = []
+    for codec, name in ((Q4_0, "Q4_0"), (Q8_0, "Q8_0")):
+        for n, k in ((4096, 4096), (14336, 4096), (4096, 14336)):
+            for m in (1, 8, 64, 512):
+                us, algorithmic = time_linear(rt, et, torch, codec, n, k, m)
+                rows_out.append({"codec": name, "rows": n, "columns": k, "vectors": m, "us": round(us, 2),
+                                 "gbs": round(algorithmic / us / 1e3, 1), "hbm_frac": round(algorithmic / us / 1e3 / peaks["hbm_gbs"], 3),
+                                 "tflops": round(2.0 * m * n * k / us / 1e6, 1),
+                                 "tensor_frac": round(2.0 * m * n * k / us / 1e6 / peaks["bf16_tflops"], 3)})
+    return rows_out
+
+
+def shuffled_pool(rt, et, torch, layers, kv_heads, head_dim, pages, seed):
+    """A pool whose free pages come back in a seeded random order: every page goes to a one-page sequence, the sequences
+    are released in shuffled order, and later allocations draw page numbers like a permutation of the pool."""
+    pool = et.NativeKvPool(rt, layers, kv_heads, head_dim, pages * BLOCK, BLOCK, et.KV_F16)
+    holders = [pool.makeSequence() for _ in range(pages)]
+    zeros = torch.zeros((256, kv_heads, BLOCK, head_dim), device="cuda", dtype=torch.float32)
+    torch.cuda.synchronize()
+    for i in range(0, pages, 256):
+        group = holders[i:i + 256]
+        rt.kv_append_into(pool, 0, group, len(group), len(group), BLOCK, zeros, zeros, BLOCK)
+    for i in np.random.default_rng(seed).permutation(pages):
+        holders[int(i)].release()
+    return pool
+
+
+def time_attention(rt, et, torch, batch, q_heads, kv_heads, head_dim, ctx, pool_pages, peaks, peak_kind, label, iters=40):
+    """Paged attention decode alone over a shuffled page pool: `batch` sequences of the given context lengths, one query
+    token each. The launch is the host-state-free operator over device-resident lane descriptors and tables, captured into a
+    CUDA graph (several pools' worth of KV is not needed: one pass already reads more than L2 holds for the microbenchmark
+    shape; for the in-step shape the graph alternates between two disjoint sets of sequences)."""
+    ctx = np.asarray(ctx)
+    sets = 1 if int(ctx.sum()) * 2 * kv_heads * head_dim * 2 > 200e6 else 2 + int(200e6 // max(1, int(ctx.sum()) * 2 * kv_heads * head_dim * 2))
+    pool = shuffled_pool(rt, et, torch, 1, kv_heads, head_dim, pool_pages, seed=11)
     gen = torch.Generator(device="cuda")
     gen.manual_seed(1)
     chunk = 64
-    kv = torch.randn((B, Hkv, chunk, D), generator=gen, device="cuda", dtype=torch.float32)
+    order = np.argsort(-ctx)
+    lanes_dev, tables_dev, keep = [], [], []
+    for _ in range(sets):
+        seqs = [pool.makeSequence() for _ in range(batch)]
+        kv = torch.randn((batch, kv_heads, chunk, head_dim), generator=gen, device="cuda", dtype=torch.float32)
+        torch.cuda.synchronize()
+        total = ctx + 1  # the new token's K/V row is part of what the step attends over
+        for start in range(0, int(total.max()), chunk):
+            group = [seqs[int(i)] for i in order if total[i] - start >= chunk]
+            if group:
+                rt.kv_append_into(pool, 0, group, len(group), len(group), chunk, kv, kv, chunk)
+                for s in group:
+                    s.commit(np.arange(chunk, dtype=np.uint32))
+        for i in range(batch):  # ragged tails
+            tail = int(total[i]) % chunk
+            if tail:
+                rt.kv_append_into(pool, 0, [seqs[i]], 1, 1, tail, kv, kv, tail)
+                seqs[i].commit(np.arange(tail, dtype=np.uint32))
+        lanes = np.zeros((batch, 4), dtype=np.int32)
+        flat = []
+        for i in range(batch):
+            blocks, head = seqs[i].blocks
+            lanes[i] = (int(ctx[i]), 1, 0, len(flat) - head)
+            flat.extend(int(b) for b in blocks)
+        lanes_dev.append(torch.from_numpy(lanes).cuda())
+        tables_dev.append(torch.from_numpy(np.asarray(flat, dtype=np.int32)).cuda())
+        keep.append(seqs)  # a dropped handle returns its pages to the pool
+    max_pages = int(np.ceil((ctx + 1) / BLOCK).max())
+    plan = et.attention_plan(batch, q_heads, kv_heads, head_dim, max_pages, sm_count=rt.capabilities()["sm_count"])
+    scratch = torch.empty(max(plan["partial_bytes"], 4), dtype=torch.uint8, device="cuda")
+    q = torch.randn((batch, q_heads, head_dim), generator=gen, device="cuda", dtype=torch.float32)
+    out = torch.empty((batch, q_heads, head_dim), device="cuda", dtype=torch.float32)
+    scale = 1.0 / np.sqrt(head_dim)
     torch.cuda.synchronize()
-    filler = np.arange(chunk, dtype=np.uint32)
-    for start in range(0, int(ctx.max()), chunk):  # sequences are sorted by length: the first `active` still grow
-        active = int((ctx > start).sum())
-        rt.kv_append_into(pool, 0, seqs[:active], B, active, chunk, kv, kv, chunk)
-        for s in seqs[:active]:
-            s.commit(filler)
-    q = torch.randn((B, Hq, D), generator=gen, device="cuda", dtype=torch.float32)
-    k1 = torch.randn((B, Hkv, D), generator=gen, device="cuda", dtype=torch.float32)
-    out = torch.empty((B, Hq, D), device="cuda", dtype=torch.float32)
-    torch.cuda.synchronize()
-    scale = 1.0 / np.sqrt(D)
     stream = torch.cuda.ExternalStream(rt.stream)
-    start_ev, stop_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sampler = ClockSampler(0)
-    for _ in range(max(args.warmup, 3)):
-        rt.kv_attention_decode_into(pool, 0, seqs, B, B, q, k1, k1, Hq, scale, out=out)
+
+    def call(i):
+        rt.paged_attention_into(pool, 0, lanes_dev[i % sets], tables_dev[i % sets], batch, max_pages, q, q_heads, scale, out, scratch,
+                                plan["partial_bytes"])
+
+    for i in range(max(3, sets)):
+        call(i)
     rt.synchronize()
-    sampler.start()
-    iters = max(args.steps, 20)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        for i in range(iters):
+            call(i)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with torch.cuda.stream(stream):
-        start_ev.record()
-        for _ in range(iters):
-            rt.kv_attention_decode_into(pool, 0, seqs, B, B, q, k1, k1, Hq, scale, out=out)
-        stop_ev.record()
+        graph.replay()
+        a.record()
+        graph.replay()
+        graph.replay()
+        b.record()
     rt.synchronize()
-    clocks = sampler.stop()
-    ms = start_ev.elapsed_time(stop_ev) / iters
-    total_ctx = int(ctx.sum()) + B
-    algorithmic = total_ctx * 2 * Hkv * D * 2 + B * Hq * D * 8 + 4 * int(np.ceil((ctx + 1) / BLOCK).sum())
-    peaks, peak_kind = measured_peaks()
-    achieved = algorithmic / (ms * 1e-3) / 1e9
-    print(json.dumps({
-        "metric": "paged attention decode, HBM GB/s vs peak", "value": achieved, "unit": "GB/s", "n_gpus": 1, "steps": iters,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "dtype": "f16 KV, f16 MMA operands, f32 softmax/accumulate",
-        "data": "synthetic", "config": {"workload": f"paged attention microbench: {B} sequences, {Hq} query / {Hkv} KV heads x {D}, contexts "
-                                                    f"{int(ctx.min())}..{int(ctx.max())} (sum {total_ctx}), {pages} pages x {BLOCK} tokens, "
-                                                    "each step appends one token per sequence (host lane/table upload included) and attends",
-                                        "l2": f"KV read per step {algorithmic / 1e6:.0f} MB exceeds the 126 MB L2"},
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
-                     "traffic": None, "peak_kind": peak_kind, "kernel": "attention_mma_kernel<128,f16> + merge + kv append",
-                     "algorithmic_bytes_per_launch": algorithmic},
-        "clocks": clocks}), flush=True)
+    us = a.elapsed_time(b) / (2 * iters) * 1e3
+    total_ctx = int((ctx + 1).sum())
+    algorithmic = total_ctx * 2 * kv_heads * head_dim * 2 + batch * q_heads * head_dim * 8 + 4 * int(np.ceil((ctx + 1) / BLOCK).sum())
+    entry = roofline_entry(us, algorithmic, peaks, peak_kind, f"attention_mma_kernel<{head_dim},f16> (+ merge when split): {label}")
+    entry.update({"splits": plan["splits"], "kv_sets_rotated": sets, "tables": "drawn from a shuffled page pool"})
+    del graph
+    keep.clear()
+    pool.close()
+    torch.cuda.empty_cache()
+    return entry
 
 
-def run_linear_microbench(args):
-    """The quantized-matmul microbench shapes: Q4_0 and Q8_0, [4096x4096], [14336x4096], [4096x14336], 1 / 8 / 64 / 512 input
-    vectors, each timed through graph replays over enough weight copies to exceed L2. One JSON line with a table."""
-    import torch
-    import effect_torch_b200 as et
-
-    torch.cuda.set_device(0)
-    rt = et.Runtime(0)
-    peaks, peak_kind = measured_peaks()
-    rows_out = []
-    gen = torch.Generator(device="cuda")
-    gen.manual_seed(2)
-    stream = torch.cuda.ExternalStream(rt.stream)
-    for codec, bb, name in ((Q4_0, 18, "Q4_0"), (8, 34, "Q8_0")):
-        for n, k in ((4096, 4096), (14336, 4096), (4096, 14336)):
-            packed_bytes = n * (k // 32) * bb
-            copies = max(2, int(np.ceil(300e6 / packed_bytes)))
-            weights = []
-            for _ in range(copies):
-                w = torch.randn((n, k), generator=gen, device="cuda", dtype=torch.float32) * 0.02
-                p = torch.empty((n, k // 32 * bb), dtype=torch.uint8, device="cuda")
-                torch.cuda.synchronize()
-                rt.quantize_into(codec, w, n, k, p)
-                rt.synchronize()
-                weights.append(et.QWeight(rt, codec, [p], [n], k))
-                del w, p
-            for m in (1, 8, 64, 512):
-                x = torch.randn((m, k), generator=gen, device="cuda", dtype=torch.float32)
-                out = torch.empty((m, n), device="cuda", dtype=torch.float32)
-                need = weights[0].scratch_bytes(m)
-                scratch = torch.empty(max(need, 4), dtype=torch.uint8, device="cuda")
-                torch.cuda.synchronize()
-                for i in range(copies):
-                    weights[i].linear_into(x, m, out, scratch=scratch, scratch_bytes=need)
-                rt.synchronize()
-                iters = 2 * copies
-                graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph, stream=stream):
-                    for i in range(iters):
-                        weights[i % copies].linear_into(x, m, out, scratch=scratch, scratch_bytes=need)
-                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                with torch.cuda.stream(stream):
-                    graph.replay()
-                    a.record()
-                    graph.replay()
-                    graph.replay()
-                    b.record()
-                rt.synchronize()
-                us = a.elapsed_time(b) / (2 * iters) * 1e3
-                algorithmic = packed_bytes + 4 * m * k + 4 * m * n
-                flops = 2.0 * m * n * k
-                rows_out.append({"codec": name, "rows": n, "columns": k, "vectors": m, "us": us, "gbs": algorithmic / us / 1e3,
-                                 "hbm_frac": algorithmic / us / 1e3 / peaks["hbm_gbs"], "tflops": flops / us / 1e6})
-                del graph
-            for w in weights:
-                w.close()
-            torch.cuda.empty_cache()
-    print(json.dumps({"metric": "quantized linear microbench, HBM GB/s and TFLOP/s per shape", "unit": "GB/s", "n_gpus": 1,
-                      "data": "synthetic", "config": {"workload": "tcgen05 dequant linear, graph replays over > 300 MB of weight copies per shape"},
-                      "peak": peaks, "peak_kind": peak_kind, "table": rows_out}), flush=True)
-
-
-MODEL_70B = dict(layers=80, d_model=8192, q_heads=64, kv_heads=8, head_dim=128, ffn=28672, vocab=128256, rms_eps=1e-5,
-                 rope_theta=500000.0)
-
-
-def run_tp_70b(args, rank, world):
-    """Llama-3-70B-shape Q4_0 decode, batch 64, contexts ~U[1024, 8192], tensor parallel over `world` ranks. KV is written
-    straight into the pages (N(0,1) rows; a decode benchmark needs no real prefill) and the steps run device-resident."""
-    import torch
-    import torch.distributed as dist
-    import effect_torch_b200 as et
+def run_tp_70b(args, rank, world, rt, et, torch, dist, steps, warmup):
+    """Llama-3-70B-shape Q4_0 decode, batch 64, contexts ~U[1024, 8192], tensor parallel over `world` ranks (the whole model
+    on one GPU at world 1). KV is written straight into the pages (N(0,1) rows; a decode benchmark needs no real prefill)
+    and the steps run device-resident. Returns the `tp` object of the bench line (rank 0) or None."""
     from effect_torch_b200 import tensor_parallel
 
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    rt = et.Runtime(local)
     full = dict(MODEL_70B)
     if args.layers:
         full["layers"] = args.layers
     model = tensor_parallel.local_config(full, world)
-    B, K, W, chunk = 64, args.steps, args.warmup, 256
+    B, K, W, chunk = 64, steps, warmup, 256
     rng = np.random.default_rng(4)  # the same contexts and tokens on every rank
     ctx = np.sort((rng.integers(1024, 8193, size=B) // chunk) * chunk)[::-1].copy()
-    per_seq = ((int(ctx.max()) + W + K + BLOCK) // BLOCK + 1) * BLOCK
     max_tokens = ((int(ctx.sum()) + B * (W + K + 2 * BLOCK)) // BLOCK + B) * BLOCK
     dec = build_decoder(rt, et, torch, model, B, max_tokens, seed=40 + rank, shared_seed=4)
+    allreduce = "none"
     if world > 1:
         ident = torch.zeros(128, dtype=torch.uint8, device="cuda")
         if rank == 0:
             ident = torch.frombuffer(bytearray(et.tensor_parallel_id()), dtype=torch.uint8).cuda()
         dist.broadcast(ident, src=0)
         dec.set_tensor_parallel(rank, world, bytes(ident.cpu().tolist()))
-        if args.tp_allreduce == "peer":
+        allreduce = args.tp_allreduce if args.tp_allreduce != "auto" else ("peer" if world <= 2 else "nccl")
+        if allreduce == "peer":
             mine = torch.frombuffer(bytearray(dec.peer_exchange_handle()), dtype=torch.uint8).cuda()
             table = [torch.empty_like(mine) for _ in range(world)]
             dist.all_gather(table, mine)
@@ -485,33 +534,35 @@ def run_tp_70b(args, rank, world):
     torch.cuda.synchronize()
     clocks = sampler.stop()
     times = torch.tensor([device_ms / 1000.0], dtype=torch.float64, device="cuda")
+    agree = True
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
         mine = torch.from_numpy(out.astype(np.int64)).cuda()
         lo, hi = mine.clone(), mine.clone()
         dist.all_reduce(lo, op=dist.ReduceOp.MIN)
         dist.all_reduce(hi, op=dist.ReduceOp.MAX)
-        if not torch.equal(lo, hi):
-            raise RuntimeError("tensor-parallel ranks generated different tokens")
+        agree = bool(torch.equal(lo, hi))
     seconds = float(times.cpu()[0])
-    if rank == 0:
-        mean_ctx = float(ctx.mean()) + W + (K + 1) / 2.0
-        step_bytes = algorithmic_bytes_per_step(full, B, mean_ctx)
-        peaks, peak_kind = measured_peaks()
-        print(json.dumps({
-            "metric": "decode tokens/s, Llama-3-70B-shape Q4_0 batch 64, tensor parallel", "value": B * K / seconds, "unit": "tokens/s",
-            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": 1000.0 * seconds / K, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "f16 MMA operands, f32 accumulate (Q4_0 weights, f16 KV)", "data": "synthetic",
-            "config": {"workload": f"llama3-70b-shape Q4_0 paged decode: {full['layers']} layers, batch {B}, contexts {int(ctx.min())}.."
-                                   f"{int(ctx.max())} (mean {ctx.mean():.0f}) written directly into the pages, {K} greedy steps",
-                       "global_batch": B, "parallelism": f"tp{world}, {args.tp_allreduce if world > 1 else 'no'} all-reduce, head replicated"},
-            "gpu_launches": dec.diagnostics()["launches_per_step"] * K,
-            "step_roofline": {"algorithmic_bytes_per_step_all_ranks": step_bytes, "achieved_gbs_per_rank": step_bytes / world * K / seconds / 1e9,
-                              "frac_of_" + peak_kind: step_bytes / world * K / seconds / 1e9 / peaks["hbm_gbs"]},
-            "clocks": clocks}), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    launches = dec.diagnostics()["launches_per_step"]
+    pool.close()
+    dec.close()
+    torch.cuda.empty_cache()
+    if rank != 0:
+        return None
+    mean_ctx = float(ctx.mean()) + W + (K + 1) / 2.0
+    step_bytes = algorithmic_bytes_per_step(full, B, mean_ctx)
+    peaks, peak_kind = measured_peaks()
+    return {
+        "metric": "decode tokens/s, Llama-3-70B-shape Q4_0 batch 64, tensor parallel", "value": B * K / seconds, "unit": "tokens/s",
+        "tp": world, "steps": K, "warmup": W, "ms_per_step": 1000.0 * seconds / K, "scaling": "strong",
+        "config": {"workload": f"llama3-70b-shape Q4_0 paged decode: {full['layers']} layers, batch {B}, contexts {int(ctx.min())}.."
+                               f"{int(ctx.max())} (mean {ctx.mean():.0f}) written directly into the pages, {K} greedy steps",
+                   "parallelism": f"tp{world}: rows of q/k/v/gate/up and columns of o/down cut over the ranks, {allreduce} all-reduce of "
+                                  "[batch, d_model] f32 after o and down, head replicated"},
+        "launches_per_step": launches, "all_reduce": allreduce, "ranks_agree_on_tokens": agree,
+        "step_roofline": {"algorithmic_bytes_per_step_all_ranks": step_bytes, "achieved_gbs_per_rank": step_bytes / world * K / seconds / 1e9,
+                          "frac_of_" + peak_kind + "_per_rank": step_bytes / world * K / seconds / 1e9 / peaks["hbm_gbs"]},
+        "clocks": clocks}
 
 
 def run_gpu_arm(args, rank, world):
@@ -534,17 +585,19 @@ def run_gpu_arm(args, rank, world):
         from effect_torch_b200 import tensor_parallel
         model = tensor_parallel.local_config(model, world)  # this rank's share of heads and ffn
     K, W = args.steps, args.warmup
+    chunk = max(1, min(args.prefill_chunk, PROMPT))
     # every sequence: prompt + warm-up + timed steps, twice (end-to-end leg, then device-resident leg)
     per_seq = ((PROMPT + W + K + BLOCK) // BLOCK + 1) * BLOCK
     max_tokens = 2 * BATCH * per_seq
-    dec = build_decoder(rt, et, torch, model, BATCH, max_tokens, seed=3 + rank, shared_seed=3 if tp else None)
+    dec = build_decoder(rt, et, torch, model, BATCH, max_tokens, seed=3 + rank, shared_seed=3 if tp else None, max_advance=chunk)
+    allreduce = args.tp_allreduce if args.tp_allreduce != "auto" else ("peer" if world <= 2 else "nccl")
     if tp:
         ident = torch.zeros(128, dtype=torch.uint8, device="cuda")
         if rank == 0:
             ident = torch.frombuffer(bytearray(et.tensor_parallel_id()), dtype=torch.uint8).cuda()
         dist.broadcast(ident, src=0)
         dec.set_tensor_parallel(rank, world, bytes(ident.cpu().tolist()))
-        if args.tp_allreduce == "peer":  # one-shot kernel over peer memory instead of NCCL
+        if allreduce == "peer":  # one-shot kernel over peer memory instead of NCCL
             mine = torch.frombuffer(bytearray(dec.peer_exchange_handle()), dtype=torch.uint8).cuda()
             table = [torch.empty_like(mine) for _ in range(world)]
             dist.all_gather(table, mine)
@@ -552,12 +605,15 @@ def run_gpu_arm(args, rank, world):
     pool = et.NativeKvPool(rt, model["layers"], model["kv_heads"], model["head_dim"], max_tokens, BLOCK, et.KV_F16)
     rng = np.random.default_rng(3 if tp else 3 + rank)  # tensor-parallel ranks decode the same sequences
     prompts = rng.integers(0, model["vocab"], size=(BATCH, PROMPT)).astype(np.uint32)
+    prefill_seconds = []
 
     def prefill():
+        """The prompt in chunks of `chunk` tokens per sequence through the same executable (teacher-forced; the last chunk's
+        sampled tokens start the decode). Returns (sequences, first generated tokens)."""
         seqs = [pool.makeSequence() for _ in range(BATCH)]
         if args.prefill == "direct":
             # profiling shortcut: N(0,1) K/V rows written straight into the pages (one launch per layer), so that a
-            # profiler capture reaches the decode steps after a few hundred launches instead of ~170k
+            # profiler capture reaches the decode steps after a few hundred launches
             kv = torch.randn((BATCH, model["kv_heads"], PROMPT - 1, model["head_dim"]), device="cuda", dtype=torch.float32)
             torch.cuda.synchronize()
             for layer in range(model["layers"]):
@@ -566,8 +622,11 @@ def run_gpu_arm(args, rank, world):
                 s.commit(prompts[i, :PROMPT - 1])
             return seqs, dec.executeSampled(pool, seqs, prompts[:, PROMPT - 1:PROMPT])
         tok = None
-        for t in range(PROMPT):  # the prompt goes through the decode path one token per step
-            tok = dec.executeSampled(pool, seqs, prompts[:, t:t + 1])
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for start in range(0, PROMPT, chunk):
+            tok = dec.executeSampled(pool, seqs, prompts[:, start:min(PROMPT, start + chunk)])
+        prefill_seconds.append(time.perf_counter() - t0)
         return seqs, tok
 
     def barrier():
@@ -578,13 +637,16 @@ def run_gpu_arm(args, rank, world):
     sampler = ClockSampler(local)
     # ---- leg 1: end to end through executeSampled (host token ids in, sampled ids out, every step)
     seqs, tok = prefill()
+    first_tokens = tok.copy()
     for _ in range(W):
         tok = dec.executeSampled(pool, seqs, tok[:, None])
     barrier()
     sampler.start()
+    e2e_tokens = []
     t0 = time.perf_counter()
     for _ in range(K):
         tok = dec.executeSampled(pool, seqs, tok[:, None])
+        e2e_tokens.append(tok)
     barrier()
     e2e_seconds = time.perf_counter() - t0
     launches_per_step = dec.diagnostics()["launches_per_step"]
@@ -592,6 +654,7 @@ def run_gpu_arm(args, rank, world):
         s.release()
     # ---- leg 2: device resident (ids, tables and cursors stay in HBM; one CUDA graph replay per step)
     seqs, tok = prefill()
+    same_first = bool(np.array_equal(tok, first_tokens))
     if W:
         out, _ = dec.generate_greedy(pool, seqs, tok, W)
         tok = out[-1]
@@ -599,42 +662,34 @@ def run_gpu_arm(args, rank, world):
     out, device_ms = dec.generate_greedy(pool, seqs, tok, K)
     barrier()
     clocks = sampler.stop()
+    tokens_agree = same_first and bool(np.array_equal(np.stack(e2e_tokens), out))
     times = torch.tensor([device_ms / 1000.0, e2e_seconds], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ranks_agree = True
     if tp:  # every rank must have generated the same tokens
         mine = torch.from_numpy(out.astype(np.int64)).cuda()
         lo, hi = mine.clone(), mine.clone()
         dist.all_reduce(lo, op=dist.ReduceOp.MIN)
         dist.all_reduce(hi, op=dist.ReduceOp.MAX)
-        if not torch.equal(lo, hi):
-            raise RuntimeError("tensor-parallel ranks generated different tokens")
+        ranks_agree = bool(torch.equal(lo, hi))
     device_seconds, e2e_seconds = [float(v) for v in times.cpu()]
     graph_launches = dec.diagnostics()["launches_per_step"]
     mean_ctx = PROMPT + W + (K + 1) / 2.0
     step_bytes = algorithmic_bytes_per_step(model, BATCH, mean_ctx)
     peaks, peak_kind = measured_peaks()
+    pool.close()
+    dec.close()
+    torch.cuda.empty_cache()
 
     line = None
     if rank == 0:
-        if args.no_kernel_timing:
-            kernel_ms, kernel_bytes = float("nan"), 0
-        else:
-            kernel_ms, kernel_bytes = time_dominant_kernel(rt, et, torch, model, BATCH)
-        achieved = kernel_bytes / (kernel_ms * 1e-3) / 1e9
         jobs = 1 if tp else world  # replicas each decode their own batch; tensor-parallel ranks share one
         value = jobs * BATCH * K / device_seconds
         e2e_value = jobs * BATCH * K / e2e_seconds
         max_blocks = max_tokens // BLOCK + 3
         h2d = BATCH * 4 + BATCH * 16 + BATCH * 8 + BATCH * max_blocks * 4
         d2h = BATCH * 4 + 32
-        cpu = None
-        if world == 1 and not args.no_cpu_baseline:
-            import oracle as orc
-            threads = orc.max_threads()
-            fraction = calibrated_fraction(MODEL, BATCH, threads, 15.0)
-            v, seconds, sample = cpu_sample(MODEL, BATCH, PROMPT, threads, fraction)
-            cpu = {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample, "cpu_seconds": seconds}
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": 1000.0 * device_seconds / K, "higher_is_better": True, "scaling": "strong" if tp else "weak", "vs_baseline": None,
@@ -643,25 +698,61 @@ def run_gpu_arm(args, rank, world):
                                    f"{K} greedy steps, f16 KV 16-token pages",
                        "global_batch": BATCH * jobs,
                        "parallelism": "single GPU" if world == 1 else (f"tp{world}: rows of q/k/v/gate/up and columns of o/down cut over the ranks, "
-                                                                       f"{args.tp_allreduce} all-reduce of [batch, d_model] f32 after o and down, head replicated"
+                                                                       f"{allreduce} all-reduce of [batch, d_model] f32 after o and down, head replicated"
                                                                        if tp else f"{world} independent replicas"),
                        "l2": "per-step working set (weights 4.2 GB + KV) exceeds the 126 MB L2; no flush needed"},
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": 1000.0 * e2e_seconds / K, "launches_per_step": launches_per_step},
+            "e2e_check": {"tokens_agree_with_device_resident_leg": tokens_agree, "tokens_compared": int(BATCH * (K + 1)),
+                          "tensor_parallel_ranks_agree": ranks_agree},
             "gpu_launches": graph_launches * K,
             "step_roofline": {"algorithmic_bytes_per_step": step_bytes, "achieved_gbs": step_bytes * K / device_seconds / 1e9,
                               "frac_of_" + peak_kind: step_bytes * K / device_seconds / 1e9 / peaks["hbm_gbs"]},
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
-                         # DRAM bytes per launch of the main kernel: dram__bytes_read.sum + dram__bytes_write.sum of this very launch
-                         # (grid 224, one split) from the ncu capture summarised under profiles/
-                         "traffic": 66390784 + 531968,
-                         "traffic_source": "profiles/qlinear_umma_q4_0_decode_step.md (ncu --set full, gate/up launch)",
-                         "peak_kind": peak_kind,
-                         "kernel": "qlinear_umma_kernel<Q4_0,32> fused gate/up [28672x4096], 32 vectors, with its f16 conversion and split-K sum launches",
-                         "ms_per_launch": kernel_ms, "algorithmic_bytes_per_launch": kernel_bytes},
-            "cpu_baseline": cpu,
             "clocks": clocks,
         }
+        if prefill_seconds:
+            line["prefill"] = {"tokens_per_s": jobs * BATCH * PROMPT / float(np.mean(prefill_seconds)), "chunk": chunk,
+                               "seconds": float(np.mean(prefill_seconds)),
+                               "path": "chunks through Executable.executeSampled: tcgen05 linears at batch x chunk rows, attention by the "
+                                       "reference-order kernel"}
+        if not args.no_kernel_timing:
+            us, algorithmic = time_linear(rt, et, torch, Q4_0, 2 * model["ffn"], model["d_model"], BATCH, True, et.EPILOGUE_SWIGLU, False, 264e6)
+            # DRAM bytes per launch of this very kernel and shape, from the committed ncu summary
+            traffic = profile_number("qlinear_umma_q4_0_decode_step.md", "gate_up_dram_bytes_per_launch")
+            line["roofline"] = roofline_entry(
+                us, algorithmic, peaks, peak_kind,
+                f"qlinear_umma_kernel<Q4_0,32> fused gate/up [{2 * model['ffn']}x{model['d_model']}], {BATCH} vectors, with its f16 conversion launch",
+                traffic, "ncu --set full capture of this launch on the 2-layer case, summary under profiles/" if traffic else None)
+            line["roofline_by_projection"] = projection_rooflines(rt, et, torch, model, BATCH, peaks, peak_kind)
+            ctx_step = np.full(BATCH, int(mean_ctx))
+            pages = int(np.ceil((ctx_step + 1) / BLOCK).sum()) * 6 + 256
+            line["roofline_attention"] = time_attention(rt, et, torch, BATCH, model["q_heads"], model["kv_heads"], model["head_dim"], ctx_step,
+                                                        pages, peaks, peak_kind, f"the decode step's launch: {BATCH} sequences at context {int(mean_ctx)}")
+        if not args.no_microbench and world == 1:
+            line["linear_microbench"] = linear_microbench_table(rt, et, torch, peaks)
+            rng_c2 = np.random.default_rng(1)
+            ctx_c2 = rng_c2.integers(128, 4097, size=64)
+            line["attention_microbench"] = time_attention(rt, et, torch, 64, 32, 8, 128, ctx_c2, 65536, peaks, peak_kind,
+                                                          "64 sequences, contexts ~U[128, 4096], pool of 65536 pages")
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            threads = host_threads()
+            fraction = calibrated_fraction(MODEL, BATCH, threads, 12.0)
+            v, seconds, sample = cpu_sample(MODEL, BATCH, PROMPT, threads, fraction)
+            cpu = {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample, "cpu_seconds": seconds}
+            ffrac = calibrated_fraction(MODEL, BATCH, 1, 6.0, faithful=True)
+            fv, fseconds, fsample = cpu_sample(MODEL, BATCH, PROMPT, 1, ffrac, faithful=True)
+            cpu["reference_faithful"] = {"value": fv, "unit": "tokens/s", "cores": 1, "sample": fsample, "cpu_seconds": fseconds}
+        line["cpu_baseline"] = cpu
+    tp_line = None
+    if not args.no_tp70b and (world > 1 or args.with_70b):
+        try:
+            tp_line = run_tp_70b(args, rank, world, rt, et, torch, dist, steps=min(K, args.tp_steps), warmup=min(W, 3))
+        except Exception as exc:  # the headline must survive a failure of the extra workload
+            tp_line = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+    if rank == 0:
+        if tp_line is not None:
+            line["tp"] = tp_line
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
@@ -675,21 +766,26 @@ def main():
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--tp-allreduce", default="peer", choices=["peer", "nccl"],
-                    help="--parallelism tp: all-reduce by the library's one-shot peer-memory kernel or by NCCL")
-    ap.add_argument("--layers", type=int, default=0, help="debug: fewer layers than the 8B shape (the result is then not a bench value)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "attention", "linear", "decode-70b"],
-                    help="decode: the headline 8B-shape decode step (the bench contract); attention / linear: the paged-attention and "
-                         "quantized-matmul microbenchmarks, one extra JSON line each (single GPU); decode-70b: the 70B shape, batch 64, "
-                         "tensor parallel over --gpus ranks")
+    ap.add_argument("--tp-allreduce", default="auto", choices=["auto", "peer", "nccl"],
+                    help="tensor parallel: all-reduce by the library's one-shot peer-memory kernel or by NCCL (auto: peer at 2 ranks, "
+                         "NCCL above)")
+    ap.add_argument("--layers", type=int, default=0, help="debug: fewer layers than the named shape (the result is then not a bench value)")
+    ap.add_argument("--workload", default="decode", choices=["decode", "decode-70b"],
+                    help="decode: the headline 8B-shape decode step (the bench contract) with the kernel rooflines, microbenchmarks and, at "
+                         "N > 1, the 70B tensor-parallel run in the same line; decode-70b: only the 70B shape over --gpus ranks")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-microbench", action="store_true", help="skip the quantized-matmul and paged-attention microbenchmark tables")
+    ap.add_argument("--no-tp70b", action="store_true", help="skip the 70B tensor-parallel run that N > 1 adds to the line")
+    ap.add_argument("--with-70b", action="store_true", help="N = 1: add the 70B shape on one GPU (138 GB) as the tp object")
+    ap.add_argument("--tp-steps", type=int, default=32, help="decode steps of the 70B run")
     ap.add_argument("--parallelism", default="replicas", choices=["replicas", "tp"],
                     help="N > 1: N independent replicas, each decoding its own batch (weak scaling; the 8B shape fits one GPU), or "
                          "one tensor-parallel model over the ranks (strong scaling)")
     ap.add_argument("--prefill", default="model", choices=["model", "direct"],
-                    help="model: the prompt runs through the decode path (the benchmark); direct: K/V rows are written "
+                    help="model: the prompt runs through the executable in chunks (the benchmark); direct: K/V rows are written "
                          "straight into the pages (profiling shortcut, not a bench value)")
-    ap.add_argument("--no-kernel-timing", action="store_true", help="skip the stand-alone timing of the dominant kernel")
+    ap.add_argument("--prefill-chunk", type=int, default=64, help="tokens per sequence per prefill call")
+    ap.add_argument("--no-kernel-timing", action="store_true", help="skip the stand-alone timing of the step's kernels")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -697,11 +793,20 @@ def main():
         run_reference_arm(args, rank)
         return
     if args.workload == "decode-70b":
-        run_tp_70b(args, rank, world)
-        return
-    if args.workload != "decode":
+        import torch
+        import torch.distributed as dist
+        import effect_torch_b200 as et
+        local = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(local)
+        if world > 1:
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        line = run_tp_70b(args, rank, world, et.Runtime(local), et, torch, dist, steps=args.steps, warmup=args.warmup)
         if rank == 0:
-            (run_attention_microbench if args.workload == "attention" else run_linear_microbench)(args)
+            line["n_gpus"] = world
+            print(json.dumps(line), flush=True)
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
         return
     run_gpu_arm(args, rank, world)
 

@@ -205,6 +205,13 @@ class Runtime:
                                                    scale, NO_WINDOW if op_window is None else op_window,
                                                    NO_WINDOW if pool_window is None else pool_window, _ptr(out)))
 
+    def paged_attention_into(self, pool, layer, lanes, tables, batch, max_pages, q, q_heads, scale, out, scratch, scratch_bytes,
+                             op_window=None):
+        """Flash-decoding over device-resident lane descriptors [batch, 4] i32 and block tables (asynchronous, capturable)."""
+        _check(self.L.etc_paged_attention_into(self.h, pool.h, layer, _ptr(lanes), _ptr(tables), batch, max_pages, _ptr(q), q_heads,
+                                               scale, NO_WINDOW if op_window is None else op_window, _ptr(out), _ptr(scratch),
+                                               scratch_bytes))
+
 
 class QWeight:
     """A retained block-quantized matrix in the tensor-core tiling (constantWeights)."""

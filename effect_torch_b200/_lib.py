@@ -87,6 +87,7 @@ SIGNATURES = {
     "etc_seq_commit": (None, [P, P, I, I64]),
     "etc_seq_rollback": (None, [P, I64]),
     "etc_seq_frontier": (None, [P, P]),
+    "etc_paged_attention_into": (None, [P, P, I, P, P, I, I, P, I, D, I64, P, P, SZ]),
     "etc_kv_attention_plan": (None, [I, I, I, I, I, I, P, P, P]),
     "etc_decoder_attention_reserve": (None, [P, I, I, P, P]),
     "etc_decoder_create": (None, [P, P, P]),

@@ -496,4 +496,30 @@ etc_status etc_kv_attention_decode_into(etc_runtime* rt, etc_pool* pool, int lay
   return ETC_OK;
 }
 
+etc_status etc_paged_attention_into(etc_runtime* rt, etc_pool* pool, int layer, const etc_lane* d_lanes, const int* d_tables,
+                                    int batch, int max_pages, const float* d_q, int q_heads, double scale, int64_t op_window,
+                                    float* d_out, void* d_scratch, size_t scratch_bytes) {
+  ETC_TRY(activate(rt));
+  if (!valid_pool(pool) || pool->rt != rt) return fail(ETC_INVALID_HANDLE, "kv pool belongs to a different runtime");
+  if (layer < 0 || layer >= pool->layers) return fail(ETC_INVALID_ARGUMENT, "kv attention: layer index out of range");
+  if (batch <= 0 || max_pages <= 0 || !d_lanes || !d_tables || !d_q || !d_out)
+    return fail(ETC_INVALID_ARGUMENT, "kv attention: lanes, tables, q and out must be given for a positive batch and page bound");
+  if (pool->kv_heads == 0 || q_heads % pool->kv_heads != 0)
+    return fail(ETC_EXECUTION, "kv attention: incompatible grouped-query q/k/v shapes");
+  const PoolView view = pool->view(layer);
+  if (!attention_mma_supported(view, q_heads, 1))
+    return fail(ETC_UNSUPPORTED, "kv attention: the tensor-core decode kernel needs an f16/bf16 pool with 16-token pages, head "
+                                 "dim 64 or 128 and at most 16 query heads per kv head");
+  static_assert(sizeof(etc_lane) == sizeof(LaneInfo), "etc_lane is the kernel's lane descriptor");
+  const AttnPlan plan = plan_attention(batch, q_heads, pool->kv_heads, pool->head_dim, max_pages, rt->sm_count);
+  if (plan.scratch_bytes > scratch_bytes || (plan.scratch_bytes && !d_scratch))
+    return fail(ETC_INVALID_ARGUMENT, "kv attention: scratch holds " + std::to_string(scratch_bytes) + " bytes, " +
+                                          std::to_string(plan.scratch_bytes) + " needed");
+  int launches = 0;
+  ETC_CUDA(launch_attention_mma(view, d_q, reinterpret_cast<const LaneInfo*>(d_lanes), d_tables, batch, q_heads, scale, op_window,
+                                d_out, plan, reinterpret_cast<float*>(d_scratch), rt->stream, &launches));
+  rt->launches += (uint64_t)launches;
+  return ETC_OK;
+}
+
 }  // extern "C"

@@ -367,6 +367,20 @@ ETC_API etc_status etc_decoder_set_tensor_parallel(etc_decoder* dec, int rank, i
 ETC_API etc_status etc_decoder_tp_peer_export(etc_decoder* dec, uint8_t* out_handle_64_bytes);
 ETC_API etc_status etc_decoder_tp_peer_import(etc_decoder* dec, const uint8_t* handles_world_x_64_bytes);
 
+/* The attention half of kv_attention_into alone, over lane descriptors and block tables that already sit in device
+ * memory (the decode kernel of napi/mod.rs:3478-3540 for one query token per lane; what the Metal backend's paged kernel
+ * takes as block_tables / context lengths / block_bases, crates/runtime-metal/src/paged.rs:651-795). Asynchronous and
+ * free of host state: nothing is allocated, no page is drawn, no cursor moves, so the call can be captured into a CUDA
+ * graph and replayed. d_lanes[i] = {cursor, advance (1 = live lane, 0 = padded), start (first resident position),
+ * table_offset (index in d_tables of the block that holds position 0)}; lane i attends over positions [start, cursor +
+ * advance) (further narrowed by op_window). max_pages bounds the pages any lane attends over and fixes the split plan;
+ * d_scratch holds etc_kv_attention_plan(...).partial_bytes for that plan. Needs an f16 / bf16 pool with 16-token pages. */
+typedef struct etc_lane { int cursor, advance, start, table_offset; } etc_lane;
+ETC_API etc_status etc_paged_attention_into(etc_runtime* rt, etc_pool* pool, int layer, const etc_lane* d_lanes,
+                                            const int* d_tables, int batch, int max_pages, const float* d_q, int q_heads,
+                                            double scale, int64_t op_window, float* d_out, void* d_scratch,
+                                            size_t scratch_bytes);
+
 /* Planners of the flash-decoding kernel, pure host arithmetic in the manner of the reference's `*_requirements`
  * calls (crates/runtime-cpu/src/lib.rs:5-11). etc_kv_attention_plan: the split of `attended_pages` pages over the grid
  * and the bytes of split partials one launch writes. etc_decoder_attention_reserve: the longest block table a decoder of

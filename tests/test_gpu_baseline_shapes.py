@@ -179,6 +179,21 @@ def test_paged_attention_at_the_microbenchmark_shape_over_shuffled_tables():
         expected = orc.kv_attention(opool, 0, [oseq], 1, q[lane:lane + 1, :, None, :], k1[lane:lane + 1, :, None, :],
                                     v1[lane:lane + 1, :, None, :], scale, mode=1, threads=THREADS)
         assert helpers.rel_err(got[lane], expected[0, :, 0, :]) <= REL_TOL, f"lane {lane} (context {n})"
+    # the same attention through the host-state-free operator over device-resident lane descriptors and tables
+    lanes = np.zeros((B, 4), dtype=np.int32)
+    flat = []
+    for lane in range(B):
+        blocks, head = seqs[lane].blocks
+        lanes[lane] = (int(ctx[lane]), 1, 0, len(flat) - head)
+        flat.extend(int(b) for b in blocks)
+    max_pages = int(np.ceil((ctx + 1) / 16).max())
+    plan = et.attention_plan(B, Hq, Hkv, D, max_pages, sm_count=rt.capabilities()["sm_count"])
+    scratch = torch.empty(max(plan["partial_bytes"], 4), dtype=torch.uint8, device="cuda")
+    out2 = empty((B, Hq, D))
+    dq = dev(q)
+    rt.paged_attention_into(pool, 0, dev(lanes), dev(np.asarray(flat, dtype=np.int32)), B, max_pages, dq, Hq, scale, out2, scratch,
+                            plan["partial_bytes"])
+    np.testing.assert_array_equal(host(out2), got)
 
 
 def test_two_layer_decoder_at_the_8b_width_and_batch_32():
