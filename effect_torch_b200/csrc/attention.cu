@@ -602,7 +602,7 @@ __device__ __forceinline__ void pool_store(const PoolView& p, void* slab, size_t
 
 __global__ void rope_append_kernel(PoolView pool, const float* __restrict__ qkv, const LaneInfo* __restrict__ lanes,
                                    const int* __restrict__ tables, const double* __restrict__ inv_freq, int layout,
-                                   int q_heads, float* __restrict__ q_out) {
+                                   int q_heads, float* __restrict__ q_out, DeferredSum sum) {
   chain_release();  // the next kernel of the step may be scheduled; it waits for this one before touching memory
   chain_wait();
   const int head = blockIdx.x, lane_id = blockIdx.y;
@@ -614,7 +614,18 @@ __global__ void rope_append_kernel(PoolView pool, const float* __restrict__ qkv,
   const float* src = qkv + lane_id * row_width + (size_t)head * D;
   const int i0 = layout == 0 ? j : 2 * j, i1 = layout == 0 ? half + j : 2 * j + 1;
   const bool is_q = head < q_heads, is_k = !is_q && head < q_heads + pool.kv_heads;
-  float r0 = src[i0], r1 = src[i1];
+  float r0, r1;
+  if (sum.splits > 0) {  // the projection left its split-K partials unsummed: add them up here, in split order
+    r0 = r1 = 0.f;
+    for (int s = 0; s < sum.splits; ++s) {
+      const float* p = sum.partials + ((size_t)s * sum.vpad + lane_id) * sum.rows_padded + (size_t)head * D;
+      r0 += p[i0];
+      r1 += p[i1];
+    }
+  } else {
+    r0 = src[i0];
+    r1 = src[i1];
+  }
   if (is_q || is_k) {
     const double angle = (double)info.cursor * inv_freq[j];
     double s, c;
@@ -641,11 +652,11 @@ __global__ void rope_append_kernel(PoolView pool, const float* __restrict__ qkv,
 
 cudaError_t launch_rope_append(const PoolView& pool, const float* qkv, const LaneInfo* lanes, const int* tables,
                                const double* inv_freq, int layout, int batch, int q_heads, float* q_out,
-                               cudaStream_t stream) {
+                               cudaStream_t stream, const DeferredSum* sum) {
   if (batch == 0) return cudaSuccess;
   dim3 grid((unsigned)(q_heads + 2 * pool.kv_heads), (unsigned)batch);
   return launch_chained(rope_append_kernel, grid, dim3((unsigned)std::max(32, pool.head_dim / 2)), 0, stream, pool, qkv, lanes, tables, inv_freq, layout, q_heads,
-                        q_out);
+                        q_out, sum ? *sum : DeferredSum());
 }
 
 __global__ void record_step_kernel(const uint32_t* __restrict__ tokens, uint32_t* __restrict__ ids,

@@ -207,12 +207,14 @@ struct StepContext {
 
 // out = x W^T (+ epilogue) for one projection, choosing the tensor-core tiling when it exists.
 etc_status run_linear(StepContext& s, const BoundWeight& raw, etc_qweight* tiled_w, const float* x, int64_t vectors, float* out,
-                      int epilogue, const float* residual, const __half* xh_ready = nullptr, __half* out_xh = nullptr) {
+                      int epilogue, const float* residual, const __half* xh_ready = nullptr, __half* out_xh = nullptr,
+                      DeferredSum* defer = nullptr) {
   etc_decoder* d = s.dec;
   cudaStream_t stream = d->rt->stream;
+  if (defer) *defer = DeferredSum();
   if (tiled_w) {
     ETC_CUDA(launch_qlinear_tiled(tiled_w->tiled, x, vectors, nullptr, residual, epilogue, out, d->lin_scratch,
-                                  d->rt->d_status, d->rt->sm_count, stream, &s.launches, xh_ready, out_xh, d->xh_nv));
+                                  d->rt->d_status, d->rt->sm_count, stream, &s.launches, xh_ready, out_xh, d->xh_nv, defer));
     return ETC_OK;
   }
   float* target = epilogue == ETC_EPILOGUE_RESIDUAL ? d->proj : out;
@@ -233,10 +235,13 @@ etc_status run_linear(StepContext& s, const BoundWeight& raw, etc_qweight* tiled
 // hidden += x W^T for the o and down projections. Under tensor parallelism every rank holds a column range of W and so
 // a partial sum: rank 0 adds the residual, the others overwrite, and the all-reduce leaves the same hidden state on
 // every rank (crates/runtime-cpu has no counterpart: the reference is single-device).
+// `defer` (single device only): the projection may leave its split-K partials unsummed for the RMSNorm that follows,
+// which then does hidden += sum itself.
 etc_status project_into_hidden(StepContext& s, const BoundWeight& raw, etc_qweight* tiled_w, const float* x, int64_t rows,
-                               const __half* xh_ready, int buffer) {
+                               const __half* xh_ready, int buffer, DeferredSum* defer = nullptr) {
   etc_decoder* d = s.dec;
   const bool sharded = d->tp_world > 1;
+  if (defer) *defer = DeferredSum();
   if (sharded && d->tp_peer) {
     // every rank leaves its partial sum in its exported buffer; the all-reduce kernel adds all of them onto hidden
     float* partial = reinterpret_cast<float*>(d->tp_region + 512 + (size_t)buffer * d->tp_partial_bytes);
@@ -247,12 +252,27 @@ etc_status project_into_hidden(StepContext& s, const BoundWeight& raw, etc_qweig
     return ETC_OK;
   }
   const int epilogue = sharded && d->tp_rank != 0 ? ETC_EPILOGUE_NONE : ETC_EPILOGUE_RESIDUAL;
-  ETC_TRY(run_linear(s, raw, tiled_w, x, rows, d->hidden, epilogue, epilogue == ETC_EPILOGUE_RESIDUAL ? d->hidden : nullptr, xh_ready));
+  ETC_TRY(run_linear(s, raw, tiled_w, x, rows, d->hidden, epilogue, epilogue == ETC_EPILOGUE_RESIDUAL ? d->hidden : nullptr, xh_ready,
+                     nullptr, sharded ? nullptr : defer));
   if (sharded) {
     std::string error;
     if (!tp_allreduce_sum(d->tp, d->hidden, (size_t)rows * d->cfg.d_model, d->rt->stream, &error)) return fail(ETC_EXECUTION, error);
     ++s.launches;
   }
+  return ETC_OK;
+}
+
+// RMSNorm of the residual stream into the f16 hand-off layout; `pending` holds the split-K partials of the projection
+// before it when that projection left them unsummed.
+etc_status norm_hand_off(StepContext& s, const BoundWeight& weight, int64_t rows, DeferredSum& pending) {
+  etc_decoder* d = s.dec;
+  const etc_decoder_config& c = d->cfg;
+  if (pending.splits > 0)
+    ETC_CUDA(launch_sum_rmsnorm_xh8(d->hidden, pending, (const float*)weight.d_raw, c.rms_eps, rows, c.d_model, d->xh_norm, d->rt->stream, d->xh_nv));
+  else
+    ETC_CUDA(launch_rmsnorm_xh8(d->hidden, (const float*)weight.d_raw, c.rms_eps, rows, c.d_model, d->xh_norm, d->rt->stream, d->xh_nv));
+  pending = DeferredSum();
+  ++s.launches;
   return ETC_OK;
 }
 
@@ -276,18 +296,25 @@ etc_status enqueue_step(StepContext& s) {
   }
   ++s.launches;
 
+  DeferredSum pending;  // partials of the last projection onto the residual stream, summed by the next RMSNorm
   for (int l = 0; l < c.layers; ++l) {
     const size_t li = (size_t)l;
     const PoolView view = s.pool->view(l);
     // one-token steps of a tiled model hand activations from kernel to kernel as f16 in the tensor-core operand order
     const bool xh = d->xh_path && T == 1;
-    if (xh) ETC_CUDA(launch_rmsnorm_xh8(d->hidden, (const float*)d->attn_norm[li].d_raw, c.rms_eps, rows, c.d_model, d->xh_norm, stream, d->xh_nv));
-    else ETC_CUDA(launch_rmsnorm(d->hidden, (const float*)d->attn_norm[li].d_raw, c.rms_eps, rows, c.d_model, d->normed, stream));
-    ++s.launches;
+    if (xh) {
+      ETC_TRY(norm_hand_off(s, d->attn_norm[li], rows, pending));
+    } else {
+      ETC_CUDA(launch_rmsnorm(d->hidden, (const float*)d->attn_norm[li].d_raw, c.rms_eps, rows, c.d_model, d->normed, stream));
+      ++s.launches;
+    }
     const float *qp, *kp, *vp;
     int64_t stride_q, stride_kv;
+    const bool fast_attention = d->tiled && !c.exact && attention_mma_supported(view, Hq, T);
+    DeferredSum qkv_sum;  // the RoPE / append kernel can sum the fused projection's partials itself
     if (d->tiled) {
-      ETC_TRY(run_linear(s, d->wq[li], d->t_qkv[li], d->normed, rows, d->qkv, ETC_EPILOGUE_NONE, nullptr, xh ? d->xh_norm : nullptr));
+      ETC_TRY(run_linear(s, d->wq[li], d->t_qkv[li], d->normed, rows, d->qkv, ETC_EPILOGUE_NONE, nullptr, xh ? d->xh_norm : nullptr,
+                         nullptr, fast_attention ? &qkv_sum : nullptr));
       qp = d->qkv; kp = d->qkv + qw; vp = d->qkv + qw + kvw;
       stride_q = stride_kv = qkvw;
     } else {
@@ -300,9 +327,8 @@ etc_status enqueue_step(StepContext& s) {
       qp = qb; kp = kb; vp = vb;
       stride_q = qw; stride_kv = kvw;
     }
-    const bool fast_attention = d->tiled && !c.exact && attention_mma_supported(view, Hq, T);
     if (fast_attention) {
-      ETC_CUDA(launch_rope_append(view, d->qkv, d->d_lanes, d->d_tables, d->d_inv_freq, c.rope_layout, B, Hq, d->qr, stream));
+      ETC_CUDA(launch_rope_append(view, d->qkv, d->d_lanes, d->d_tables, d->d_inv_freq, c.rope_layout, B, Hq, d->qr, stream, &qkv_sum));
       ++s.launches;
       const AttnPlan plan = plan_attention(B, Hq, Hkv, D, std::max(1, s.max_pages), d->rt->sm_count);
       if (plan.scratch_bytes > d->attn_scratch_bytes)
@@ -324,10 +350,14 @@ etc_status enqueue_step(StepContext& s) {
       s.launches += 8;
     }
     const bool xh_o = xh && fast_attention;
-    ETC_TRY(project_into_hidden(s, d->wo[li], d->tiled ? d->t_o[li] : nullptr, d->attl, rows, xh_o ? d->xh_att : nullptr, 0));
-    if (xh) ETC_CUDA(launch_rmsnorm_xh8(d->hidden, (const float*)d->ffn_norm[li].d_raw, c.rms_eps, rows, c.d_model, d->xh_norm, stream, d->xh_nv));
-    else ETC_CUDA(launch_rmsnorm(d->hidden, (const float*)d->ffn_norm[li].d_raw, c.rms_eps, rows, c.d_model, d->normed, stream));
-    ++s.launches;
+    ETC_TRY(project_into_hidden(s, d->wo[li], d->tiled ? d->t_o[li] : nullptr, d->attl, rows, xh_o ? d->xh_att : nullptr, 0,
+                                xh ? &pending : nullptr));
+    if (xh) {
+      ETC_TRY(norm_hand_off(s, d->ffn_norm[li], rows, pending));
+    } else {
+      ETC_CUDA(launch_rmsnorm(d->hidden, (const float*)d->ffn_norm[li].d_raw, c.rms_eps, rows, c.d_model, d->normed, stream));
+      ++s.launches;
+    }
     if (d->tiled) {
       ETC_TRY(run_linear(s, d->gate[li], d->t_gu[li], d->normed, rows, xh ? nullptr : d->act, ETC_EPILOGUE_SWIGLU, nullptr,
                          xh ? d->xh_norm : nullptr, xh ? d->xh_act : nullptr));
@@ -337,12 +367,16 @@ etc_status enqueue_step(StepContext& s) {
       ETC_CUDA(launch_swiglu(d->g, d->u, rows * c.ffn, d->act, c.exact, stream));
       ++s.launches;
     }
-    ETC_TRY(project_into_hidden(s, d->down[li], d->tiled ? d->t_down[li] : nullptr, d->act, rows, xh ? d->xh_act : nullptr, 1));
+    ETC_TRY(project_into_hidden(s, d->down[li], d->tiled ? d->t_down[li] : nullptr, d->act, rows, xh ? d->xh_act : nullptr, 1,
+                                xh ? &pending : nullptr));
   }
   const bool xh_head = d->xh_path && T == 1;
-  if (xh_head) ETC_CUDA(launch_rmsnorm_xh8(d->hidden, (const float*)d->out_norm.d_raw, c.rms_eps, rows, c.d_model, d->xh_norm, stream, d->xh_nv));
-  else ETC_CUDA(launch_rmsnorm(d->hidden, (const float*)d->out_norm.d_raw, c.rms_eps, rows, c.d_model, d->normed, stream));
-  ++s.launches;
+  if (xh_head) {
+    ETC_TRY(norm_hand_off(s, d->out_norm, rows, pending));
+  } else {
+    ETC_CUDA(launch_rmsnorm(d->hidden, (const float*)d->out_norm.d_raw, c.rms_eps, rows, c.d_model, d->normed, stream));
+    ++s.launches;
+  }
   // LastTokenRow then the head: only the selected row of each lane reaches the head projection
   // (each head output is an independent dot product, so the result equals projecting all rows first).
   const float* head_in = d->normed;

@@ -92,10 +92,12 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const float* __restrict__ 
 // Single-pass variant for n <= 8192, n % 4 == 0: the row stays in registers between the reduction and the
 // scaling (same f64 arithmetic). XH = true stores the result as f16 in [n/8][32][8] order (row < 32), the
 // B-operand layout of the tcgen05 linear, instead of f32 row-major.
-template <bool XH>
-__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ weight,
+// SUM = true first adds a projection's split-K partials (summed in split order) onto the row and stores it back: the
+// residual update the projection's own sum kernel would have done.
+template <bool XH, bool SUM>
+__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* x, const float* __restrict__ weight,
                                                            double eps, int n, float* __restrict__ out, __half* __restrict__ out_xh,
-                                                           int xh_nv) {
+                                                           int xh_nv, DeferredSum sum_in, float* x_out) {
   chain_release();  // the next kernel of the step may be scheduled; it waits for this one before touching memory
   chain_wait();
   __shared__ double partial[8];
@@ -109,6 +111,15 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restri
   for (int j = 0; j < 8; ++j) {
     const int c = threadIdx.x + 256 * j;
     v[j] = c < chunks ? src[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    if (SUM && c < chunks) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int s = 0; s < sum_in.splits; ++s) {
+        const float4 p = *reinterpret_cast<const float4*>(sum_in.partials + ((size_t)s * sum_in.vpad + row) * sum_in.rows_padded + 4 * c);
+        acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+      }
+      v[j].x += acc.x; v[j].y += acc.y; v[j].z += acc.z; v[j].w += acc.w;
+      reinterpret_cast<float4*>(x_out + (size_t)row * n)[c] = v[j];
+    }
     sum += (double)v[j].x * (double)v[j].x + (double)v[j].y * (double)v[j].y + (double)v[j].z * (double)v[j].z +
            (double)v[j].w * (double)v[j].w;
   }
@@ -152,7 +163,8 @@ cudaError_t launch_rmsnorm(const float* x, const float* weight, double eps, int6
                            cudaStream_t stream) {
   if (rows == 0) return cudaSuccess;
   if (rmsnorm_fast_ok(x, weight, n) && ((uintptr_t)out % 16) == 0)
-    return launch_chained(rmsnorm_rows_kernel<false>, dim3((unsigned)rows), dim3(256), 0, stream, x, weight, eps, (int)n, out, (__half*)nullptr, 32);
+    return launch_chained(rmsnorm_rows_kernel<false, false>, dim3((unsigned)rows), dim3(256), 0, stream, x, weight, eps, (int)n, out, (__half*)nullptr, 32,
+                          DeferredSum(), (float*)nullptr);
   else
     rmsnorm_kernel<<<(unsigned)rows, 256, 0, stream>>>(x, weight, eps, n, out);
   return cudaGetLastError();
@@ -162,7 +174,17 @@ cudaError_t launch_rmsnorm_xh8(const float* x, const float* weight, double eps, 
                                cudaStream_t stream, int xh_nv) {
   if (rows == 0) return cudaSuccess;
   if (rows > xh_nv || n % 8 != 0 || !rmsnorm_fast_ok(x, weight, n)) return cudaErrorInvalidValue;
-  return launch_chained(rmsnorm_rows_kernel<true>, dim3((unsigned)rows), dim3(256), 0, stream, x, weight, eps, (int)n, (float*)nullptr, out_xh, xh_nv);
+  return launch_chained(rmsnorm_rows_kernel<true, false>, dim3((unsigned)rows), dim3(256), 0, stream, x, weight, eps, (int)n, (float*)nullptr, out_xh, xh_nv,
+                        DeferredSum(), (float*)nullptr);
+}
+
+cudaError_t launch_sum_rmsnorm_xh8(float* x, const DeferredSum& sum, const float* weight, double eps, int64_t rows, int64_t n,
+                                   __half* out_xh, cudaStream_t stream, int xh_nv) {
+  if (rows == 0) return cudaSuccess;
+  if (rows > xh_nv || n % 8 != 0 || !rmsnorm_fast_ok(x, weight, n) || sum.splits <= 0 || sum.rows_padded % 4 != 0 || rows > sum.vpad)
+    return cudaErrorInvalidValue;
+  return launch_chained(rmsnorm_rows_kernel<true, true>, dim3((unsigned)rows), dim3(256), 0, stream, (const float*)x, weight, eps, (int)n,
+                        (float*)nullptr, out_xh, xh_nv, sum, x);
 }
 
 // --------------------------------------------------------------------------------------------

@@ -49,6 +49,13 @@ cudaError_t launch_qlinear_reduce(const float* scratch, int splits, int vpad, in
                                   const float* bias, const float* residual, int epilogue, float* out, __half* out_xh,
                                   cudaStream_t stream, int xh_nv = 32);
 
+// Split-K partials a linear left unsummed for the kernel that consumes its result (the next RMSNorm, or the RoPE /
+// KV-append kernel): [splits][vpad][rows_padded] f32, summed in split order. splits == 0: the result is already in `out`.
+struct DeferredSum {
+  const float* partials = nullptr;
+  int splits = 0, vpad = 0, rows_padded = 0;
+};
+
 // tcgen05 path (qlinear_umma.cu)
 struct UmmaPlan {
   int nv = 32;               // vectors per pass padded to the MMA N (32, 64, 128 or 256)
@@ -61,7 +68,8 @@ cudaError_t launch_repack_umma(const TiledWeight& w, const RepackParts& parts, c
 // x: f32 [vectors, K], converted to xh8 into `xh` first — unless xh_ready (already [K/8][32][8] f16, vectors <= 32) is given.
 cudaError_t launch_qlinear_umma(const TiledWeight& w, const float* x, const __half* xh_ready, int64_t vectors, const float* bias,
                                 const float* residual, int epilogue, float* out, __half* out_xh, __half* xh, float* scratch,
-                                DeviceStatus* status, int sm_count, cudaStream_t stream, int* launches, int xh_nv = 32);
+                                DeviceStatus* status, int sm_count, cudaStream_t stream, int* launches, int xh_nv = 32,
+                                DeferredSum* defer = nullptr);
 
 // small-batch matvec on the 128-row layout (qlinear_mv.cu): up to 32 vectors per pass, mma.sync fed by a bulk-copy ring
 struct MvPlan {
@@ -86,12 +94,15 @@ size_t tiled_scratch_bytes(const TiledWeight& w, int64_t vectors, int sm_count);
 cudaError_t launch_qlinear_tiled(const TiledWeight& w, const float* x, int64_t vectors, const float* bias,
                                  const float* residual, int epilogue, float* out, void* scratch, DeviceStatus* status,
                                  int sm_count, cudaStream_t stream, int* launches, const __half* xh_ready = nullptr,
-                                 __half* out_xh = nullptr, int xh_nv = 32);
+                                 __half* out_xh = nullptr, int xh_nv = 32, DeferredSum* defer = nullptr);
 // Row stride of the f16 hand-off layout for `vectors` rows: 32, 64 or 128 (0: no hand-off above 128 vectors).
 inline int hand_off_stride(int64_t vectors) { return vectors <= 32 ? 32 : (vectors <= 64 ? 64 : (vectors <= 128 ? 128 : 0)); }
 // RMSNorm whose output is stored as f16 [n/8][xh_nv][8] (rows <= xh_nv).
 cudaError_t launch_rmsnorm_xh8(const float* x, const float* weight, double eps, int64_t rows, int64_t n, __half* out_xh,
                                cudaStream_t stream, int xh_nv = 32);
+// The same after x += sum of a projection's split-K partials (x is updated in place: the residual stream).
+cudaError_t launch_sum_rmsnorm_xh8(float* x, const DeferredSum& sum, const float* weight, double eps, int64_t rows, int64_t n,
+                                   __half* out_xh, cudaStream_t stream, int xh_nv = 32);
 
 // ---- tensor-parallel all-reduce over peer memory (tp_kernels.cu) -----------------------------
 constexpr int kMaxTpRanks = 8;
@@ -170,7 +181,7 @@ cudaError_t launch_attention_mma(const PoolView& pool, const float* q, const Lan
 // projection output) -> q_out [B,Hq,D] f32 rotated, K/V rows written to the pool.
 cudaError_t launch_rope_append(const PoolView& pool, const float* qkv, const LaneInfo* lanes, const int* tables,
                                const double* inv_freq, int layout, int batch, int q_heads, float* q_out,
-                               cudaStream_t stream);
+                               cudaStream_t stream, const DeferredSum* sum = nullptr);
 // Tail of a device-resident greedy step: feeds the sampled tokens back as the next ids, appends
 // them to the history, and advances every live lane's cursor (and window start) by one.
 cudaError_t launch_record_step(const uint32_t* tokens, uint32_t* ids, uint32_t* history, int* step_counter, LaneInfo* lanes,

@@ -407,7 +407,8 @@ UmmaPlan plan_umma(const TiledWeight& w, int64_t vectors, int sm_count) {
 // qlinear_reduce_kernel lives in quant_kernels.cu
 cudaError_t launch_qlinear_umma(const TiledWeight& w, const float* x, const __half* xh_ready, int64_t vectors, const float* bias,
                                 const float* residual, int epilogue, float* out, __half* out_xh, __half* xh, float* scratch,
-                                DeviceStatus* status, int sm_count, cudaStream_t stream, int* launches, int xh_nv) {
+                                DeviceStatus* status, int sm_count, cudaStream_t stream, int* launches, int xh_nv, DeferredSum* defer) {
+  if (defer) *defer = DeferredSum();
   const int out_cols = (int)(epilogue == ETC_EPILOGUE_SWIGLU ? w.rows / 2 : w.rows);
   for (int64_t v0 = 0; v0 < vectors; v0 += 256) {
     const int64_t chunk = std::min<int64_t>(256, vectors - v0);
@@ -452,7 +453,13 @@ cudaError_t launch_qlinear_umma(const TiledWeight& w, const float* x, const __ha
     }
     if (e != cudaSuccess) return e;
     if (launches) ++*launches;
-    if (plan.splits > 1) {
+    if (plan.splits > 1 && defer && vectors <= 256 && !bias && !out_xh && epilogue != ETC_EPILOGUE_SWIGLU) {
+      // the consumer sums the partials itself (and adds the residual stream where the epilogue asks for it)
+      defer->partials = scratch;
+      defer->splits = plan.splits;
+      defer->vpad = plan.nv;
+      defer->rows_padded = (int)w.rows_padded;
+    } else if (plan.splits > 1) {
       e = launch_qlinear_reduce(scratch, plan.splits, plan.nv, (int)chunk, (int)w.rows, (int)w.rows_padded, bias, args.residual,
                                 epilogue, args.out, args.out_xh, stream, xh_nv);
       if (e != cudaSuccess) return e;

@@ -302,7 +302,9 @@ size_t tiled_scratch_bytes(const TiledWeight& w, int64_t vectors, int sm_count) 
 
 cudaError_t launch_qlinear_tiled(const TiledWeight& w, const float* x, int64_t vectors, const float* bias,
                                  const float* residual, int epilogue, float* out, void* scratch, DeviceStatus* status,
-                                 int sm_count, cudaStream_t stream, int* launches, const __half* xh_ready, __half* out_xh, int xh_nv) {
+                                 int sm_count, cudaStream_t stream, int* launches, const __half* xh_ready, __half* out_xh, int xh_nv,
+                                 DeferredSum* defer) {
+  if (defer) *defer = DeferredSum();
   if (w.counters && vectors <= mv_max_vectors())
     return launch_qlinear_mv(w, x, xh_ready, vectors, bias, residual, epilogue, out, out_xh, scratch, status, sm_count, stream,
                              launches, xh_nv);
@@ -312,7 +314,7 @@ cudaError_t launch_qlinear_tiled(const TiledWeight& w, const float* x, int64_t v
     xh_region = std::max(xh_region, umma_xh_region(plan_umma(w, std::min<int64_t>(256, vectors - v0), sm_count)));
   return launch_qlinear_umma(w, x, xh_ready, vectors, bias, residual, epilogue, out, out_xh, reinterpret_cast<__half*>(scratch),
                              reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + xh_region), status, sm_count, stream,
-                             launches, xh_nv);
+                             launches, xh_nv, defer);
 }
 
 }  // namespace etc
