@@ -205,12 +205,24 @@ class Runtime:
                                                    scale, NO_WINDOW if op_window is None else op_window,
                                                    NO_WINDOW if pool_window is None else pool_window, _ptr(out)))
 
+    def peer_allreduce_into(self, rank, world, regions, capacity, buffer, hidden, count, partial=None, two_shot=False, wait_cycles=0):
+        """hidden[:count] += sum over ranks of the partial sums in `buffer` of every region (device pointers, own rank
+        local); asynchronous. A peer that never arrives turns into BackendError(ETC_EXECUTION) at the next synchronize."""
+        arr = (C.c_void_p * world)(*[_ptr(r) for r in regions])
+        _check(self.L.etc_peer_allreduce_into(self.h, rank, world, arr, capacity, buffer, _ptr(partial), _ptr(hidden), count,
+                                              int(two_shot), wait_cycles))
+
     def paged_attention_into(self, pool, layer, lanes, tables, batch, max_pages, q, q_heads, scale, out, scratch, scratch_bytes,
                              op_window=None):
         """Flash-decoding over device-resident lane descriptors [batch, 4] i32 and block tables (asynchronous, capturable)."""
         _check(self.L.etc_paged_attention_into(self.h, pool.h, layer, _ptr(lanes), _ptr(tables), batch, max_pages, _ptr(q), q_heads,
                                                scale, NO_WINDOW if op_window is None else op_window, _ptr(out), _ptr(scratch),
                                                scratch_bytes))
+
+
+def peer_region_bytes(capacity: int) -> int:
+    """Bytes of one rank's exchange region for peer all-reduces of up to `capacity` floats."""
+    return int(_lib.load().etc_peer_region_bytes(capacity))
 
 
 class QWeight:
@@ -372,7 +384,7 @@ class Executable:
 
     def __init__(self, rt: Runtime, *, layers, d_model, q_heads, kv_heads, head_dim, ffn, vocab, rms_eps=1e-5, rope_theta=10000.0,
                  rope_layout=HALF_SPLIT, window=None, batch=1, max_tokens=256, block_size=16, kv_dtype=KV_F32, exact=False,
-                 max_advance=1):
+                 max_advance=1, vocab_global=None, head_first_row=0):
         self.rt = rt
         self.cfg = DecoderConfig(layers, d_model, q_heads, kv_heads, head_dim, ffn, vocab, rms_eps, rope_theta, rope_layout,
                                  NO_WINDOW if window is None else window, batch, max_tokens, block_size, kv_dtype, int(exact))
@@ -380,6 +392,8 @@ class Executable:
         _check(rt.L.etc_decoder_create(rt.h, C.byref(self.cfg), C.byref(h)))
         self.h = h
         _check(rt.L.etc_decoder_set_max_advance(self.h, max_advance))
+        if vocab_global is not None:  # vocabulary-parallel head: `vocab` rows of it from `head_first_row` on
+            _check(rt.L.etc_decoder_set_head_shard(self.h, vocab_global, head_first_row))
         self.vocab, self.batch = vocab, batch
 
     def close(self):

@@ -11,6 +11,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
@@ -100,6 +101,10 @@ struct etc_decoder {
   // [flags 256 B][epoch + done counters 256 B][partial 0][partial 1], opened by every peer through CUDA IPC
   unsigned char* tp_region = nullptr;
   size_t tp_partial_bytes = 0;
+  bool tp_two_shot = false;           // reduce-scatter + all-gather over peer memory (4 ranks and more)
+  long long tp_wait_cycles = kTpWaitCycles;
+  int64_t vocab_global = 0;           // > 0: the head holds rows [head_first_row, head_first_row + cfg.vocab) of this many
+  int64_t head_first_row = 0;
   void* tp_peer_base[kMaxTpRanks] = {};
   PeerView tp_view{};
   bool tp_peer = false;
@@ -160,7 +165,7 @@ etc_status set_weight(etc_decoder* dec, int slot, int layer, int codec, const vo
   int64_t er = 0, ec = 0;
   BoundWeight* target = nullptr;
   switch (slot) {
-    case ETC_W_TOK_EMBD: er = c.vocab; ec = c.d_model; target = &dec->tok_embd; break;
+    case ETC_W_TOK_EMBD: er = dec->vocab_global > 0 ? dec->vocab_global : c.vocab; ec = c.d_model; target = &dec->tok_embd; break;
     case ETC_W_ATTN_NORM: er = 1; ec = c.d_model; target = &dec->attn_norm[(size_t)layer]; break;
     case ETC_W_Q: er = qw; ec = c.d_model; target = &dec->wq[(size_t)layer]; break;
     case ETC_W_K: er = kvw; ec = c.d_model; target = &dec->wk[(size_t)layer]; break;
@@ -243,11 +248,14 @@ etc_status project_into_hidden(StepContext& s, const BoundWeight& raw, etc_qweig
   const bool sharded = d->tp_world > 1;
   if (defer) *defer = DeferredSum();
   if (sharded && d->tp_peer) {
-    // every rank leaves its partial sum in its exported buffer; the all-reduce kernel adds all of them onto hidden
-    float* partial = reinterpret_cast<float*>(d->tp_region + 512 + (size_t)buffer * d->tp_partial_bytes);
-    ETC_TRY(run_linear(s, raw, tiled_w, x, rows, partial, ETC_EPILOGUE_NONE, nullptr, xh_ready));
-    ETC_CUDA(launch_tp_allreduce(d->tp_view, buffer, d->hidden, (size_t)rows * d->cfg.d_model, reinterpret_cast<uint32_t*>(d->tp_region + 256),
-                                 reinterpret_cast<uint32_t*>(d->tp_region + 260), d->rt->d_status, d->rt->stream));
+    // every rank leaves its partial sum in its exported buffer (or, split over K, as partials the all-reduce kernel adds
+    // up first); the all-reduce kernel adds all ranks' sums onto hidden
+    float* partial = reinterpret_cast<float*>(d->tp_region + kTpHeaderBytes + (size_t)buffer * d->tp_partial_bytes);
+    DeferredSum sum;
+    ETC_TRY(run_linear(s, raw, tiled_w, x, rows, partial, ETC_EPILOGUE_NONE, nullptr, xh_ready, nullptr, &sum));
+    ETC_CUDA(launch_tp_allreduce(d->tp_view, buffer, d->hidden, (size_t)rows * d->cfg.d_model, d->cfg.d_model, sum, d->tp_two_shot,
+                                 reinterpret_cast<uint32_t*>(d->tp_region + kTpCounterOffset), d->tp_wait_cycles, d->rt->d_status,
+                                 d->rt->stream));
     ++s.launches;
     return ETC_OK;
   }
@@ -288,10 +296,10 @@ etc_status enqueue_step(StepContext& s) {
 
   // token embedding (dense gather or block-decoded rows)
   if (d->tok_embd.codec == ETC_CODEC_F32) {
-    ETC_CUDA(launch_embedding_f32(d->d_ids, 0, rows, (const float*)d->tok_embd.d_raw, c.vocab, c.d_model, d->hidden,
+    ETC_CUDA(launch_embedding_f32(d->d_ids, 0, rows, (const float*)d->tok_embd.d_raw, d->tok_embd.rows, c.d_model, d->hidden,
                                   d->rt->d_status, stream));
   } else {
-    ETC_CUDA(launch_qembedding(d->tok_embd.codec, d->d_ids, 0, rows, (const uint8_t*)d->tok_embd.d_raw, c.vocab, c.d_model,
+    ETC_CUDA(launch_qembedding(d->tok_embd.codec, d->d_ids, 0, rows, (const uint8_t*)d->tok_embd.d_raw, d->tok_embd.rows, c.d_model,
                                d->hidden, d->rt->d_status, stream));
   }
   ++s.launches;
@@ -387,8 +395,19 @@ etc_status enqueue_step(StepContext& s) {
   }
   ETC_TRY(run_linear(s, d->head, d->tiled ? d->t_head : nullptr, head_in, B, d->logits, ETC_EPILOGUE_NONE, nullptr,
                      xh_head ? d->xh_norm : nullptr));
-  ETC_CUDA(launch_argmax(d->logits, B, c.vocab, d->d_tokens, d->rt->d_status, stream));
-  ++s.launches;
+  if (d->vocab_global > 0 && d->tp_world > 1) {
+    // vocabulary-parallel head: every rank picks its best row, the ranks exchange (logit, token) pairs over peer memory
+    if (!d->tp_peer) return fail(ETC_EXECUTION, "tensor parallel: a vocabulary-parallel head needs the peer exchange regions (etc_decoder_tp_peer_import)");
+    if (B > kTpMaxPicks) return fail(ETC_UNSUPPORTED, "tensor parallel: a vocabulary-parallel head serves batches up to " + std::to_string(kTpMaxPicks));
+    ETC_CUDA(launch_argmax(d->logits, B, c.vocab, d->d_tokens, d->rt->d_status, stream,
+                           reinterpret_cast<uint2*>(d->tp_region + kTpPickOffset), (uint32_t)d->head_first_row));
+    ETC_CUDA(launch_tp_pick(d->tp_view, B, d->d_tokens, reinterpret_cast<uint32_t*>(d->tp_region + kTpCounterOffset), d->tp_wait_cycles,
+                            d->rt->d_status, stream));
+    s.launches += 2;
+  } else {
+    ETC_CUDA(launch_argmax(d->logits, B, c.vocab, d->d_tokens, d->rt->d_status, stream));
+    ++s.launches;
+  }
   return ETC_OK;
 }
 
@@ -677,6 +696,18 @@ etc_status etc_decoder_set_max_advance(etc_decoder* dec, int max_advance) {
   return ETC_OK;
 }
 
+etc_status etc_decoder_set_head_shard(etc_decoder* dec, int64_t vocab_global, int64_t first_row) {
+  if (!valid_decoder(dec)) return fail(ETC_INVALID_HANDLE, "decoder handle is invalid or destroyed");
+  if (dec->finalized || dec->tok_embd.d_raw || dec->head.d_raw)
+    return fail(ETC_COMPILATION, "compile: the head shard is fixed before the embedding and the head are bound");
+  if (vocab_global <= 0 || first_row < 0 || first_row + dec->cfg.vocab > vocab_global || vocab_global > 0xffffffffll)
+    return fail(ETC_COMPILATION, "compile: head rows [" + std::to_string(first_row) + ", " + std::to_string(first_row + dec->cfg.vocab) +
+                                     ") do not lie inside a vocabulary of " + std::to_string(vocab_global));
+  dec->vocab_global = vocab_global;
+  dec->head_first_row = first_row;
+  return ETC_OK;
+}
+
 etc_status etc_tp_unique_id(uint8_t* out_id) {
   if (!out_id) return fail(ETC_INVALID_ARGUMENT, "tensor parallel: the id buffer is null");
   std::string error;
@@ -718,7 +749,7 @@ etc_status etc_decoder_tp_peer_export(etc_decoder* dec, uint8_t* out_handle) {
   if (!dec->tp_region) {
     const size_t floats = (size_t)dec->cfg.batch * dec->max_advance * dec->cfg.d_model;
     dec->tp_partial_bytes = (floats * sizeof(float) + 255) & ~(size_t)255;
-    const size_t bytes = 512 + 2 * dec->tp_partial_bytes;
+    const size_t bytes = kTpHeaderBytes + 2 * dec->tp_partial_bytes;
     ETC_TRY(rt->device_alloc(bytes, (void**)&dec->tp_region));
     ETC_CUDA(cudaMemsetAsync(dec->tp_region, 0, bytes, rt->stream));
     ETC_CUDA(cudaStreamSynchronize(rt->stream));  // peers may write flags as soon as they hold the handle
@@ -750,12 +781,12 @@ etc_status etc_decoder_tp_peer_import(etc_decoder* dec, const uint8_t* handles) 
       dec->tp_peer_base[r] = mapped;
       base = static_cast<unsigned char*>(mapped);
     }
-    view.flags[r] = reinterpret_cast<uint32_t*>(base);
-    view.partial[r][0] = reinterpret_cast<const float*>(base + 512);
-    view.partial[r][1] = reinterpret_cast<const float*>(base + 512 + dec->tp_partial_bytes);
+    tp_view_bind(view, r, base, dec->tp_partial_bytes);
   }
   dec->tp_view = view;
   dec->tp_peer = true;
+  dec->tp_two_shot = dec->tp_world >= 4;
+  if (const char* forced = std::getenv("ETC_TP_TWO_SHOT")) dec->tp_two_shot = std::atoi(forced) != 0;
   if (dec->step_graph) {  // captured with the NCCL all-reduces
     cudaGraphExecDestroy(dec->step_graph);
     dec->step_graph = nullptr;

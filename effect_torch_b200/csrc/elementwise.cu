@@ -261,8 +261,11 @@ cudaError_t launch_add(const float* a, const float* b, int64_t n, float* out, cu
 // Greedy argmax per row: the first index of the maximum (strict >, so the lowest index wins
 // ties); a non-finite logit raises the status word with its index.
 // --------------------------------------------------------------------------------------------
+// `picks` (optional): the row's (best logit bits, index_base + index) pair, for the exchange between the ranks of a
+// vocabulary-parallel head.
 __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ logits, int64_t vocab,
-                                                      uint32_t* __restrict__ tokens, DeviceStatus* status) {
+                                                      uint32_t* __restrict__ tokens, DeviceStatus* status, uint2* picks,
+                                                      uint32_t index_base) {
   chain_release();  // the next kernel of the step may be scheduled; it waits for this one before touching memory
   chain_wait();
   __shared__ float best_v[32];
@@ -325,7 +328,8 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
     }
     if (lane == 0) {
       // a row of only -inf keeps index 0 like the reference's loop would before it errors
-      tokens[blockIdx.x] = arg == 0x7fffffffffffffffll ? 0u : (uint32_t)arg;
+      tokens[blockIdx.x] = index_base + (arg == 0x7fffffffffffffffll ? 0u : (uint32_t)arg);
+      if (picks) picks[blockIdx.x] = make_uint2(__float_as_uint(best), index_base + (arg == 0x7fffffffffffffffll ? 0u : (uint32_t)arg));
       if (bad != 0x7fffffffffffffffll && atomicCAS(&status->code, kStatusNone, kStatusNonFiniteLogit) == kStatusNone) {
         status->value = bad;
         status->bound = vocab;
@@ -334,9 +338,9 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* __restrict__ 
   }
 }
 cudaError_t launch_argmax(const float* logits, int64_t rows, int64_t vocab, uint32_t* tokens, DeviceStatus* status,
-                          cudaStream_t stream) {
+                          cudaStream_t stream, uint2* picks, uint32_t index_base) {
   if (rows == 0) return cudaSuccess;
-  return launch_chained(argmax_kernel, dim3((unsigned)rows), dim3(1024), 0, stream, logits, vocab, tokens, status);
+  return launch_chained(argmax_kernel, dim3((unsigned)rows), dim3(1024), 0, stream, logits, vocab, tokens, status, picks, index_base);
 }
 
 // Dense f32 embedding gather with the same bounds rule as the quantized embedding.

@@ -37,6 +37,13 @@ struct TiledWeight {
   // group's K; the last one to arrive finishes the group
   int* counters = nullptr;
 };
+// Split-K partials a linear left unsummed for the kernel that consumes its result (the next RMSNorm, or the RoPE /
+// KV-append kernel): [splits][vpad][rows_padded] f32, summed in split order. splits == 0: the result is already in `out`.
+struct DeferredSum {
+  const float* partials = nullptr;
+  int splits = 0, vpad = 0, rows_padded = 0;
+};
+
 struct RepackParts {
   const uint8_t* ptr[4];
   int64_t rows[4];
@@ -48,13 +55,6 @@ cudaError_t launch_repack(const TiledWeight& w, const RepackParts& parts, cudaSt
 cudaError_t launch_qlinear_reduce(const float* scratch, int splits, int vpad, int vectors, int rows, int rows_padded,
                                   const float* bias, const float* residual, int epilogue, float* out, __half* out_xh,
                                   cudaStream_t stream, int xh_nv = 32);
-
-// Split-K partials a linear left unsummed for the kernel that consumes its result (the next RMSNorm, or the RoPE /
-// KV-append kernel): [splits][vpad][rows_padded] f32, summed in split order. splits == 0: the result is already in `out`.
-struct DeferredSum {
-  const float* partials = nullptr;
-  int splits = 0, vpad = 0, rows_padded = 0;
-};
 
 // tcgen05 path (qlinear_umma.cu)
 struct UmmaPlan {
@@ -106,14 +106,32 @@ cudaError_t launch_sum_rmsnorm_xh8(float* x, const DeferredSum& sum, const float
 
 // ---- tensor-parallel all-reduce over peer memory (tp_kernels.cu) -----------------------------
 constexpr int kMaxTpRanks = 8;
+// One rank's exchange region: [0, 96) three flag arrays of kTpFlagStride words (partial ready, slice total ready, picks
+// ready), [256, 288) counters private to the owner, [1024, 1024 + 8 * kTpMaxPicks) (best logit, token) pairs, then two
+// partial-sum buffers of `partial_bytes` each from kTpHeaderBytes on.
+constexpr int kTpFlagStride = 8;
+constexpr size_t kTpCounterOffset = 256, kTpPickOffset = 1024, kTpHeaderBytes = 4096;
+constexpr int kTpMaxPicks = 256;
+constexpr long long kTpWaitCycles = 1ll << 31;  // about a second
 struct PeerView {
-  const float* partial[kMaxTpRanks][2];  // every rank's two partial-sum buffers (own: local memory, others: peer mappings)
-  uint32_t* flags[kMaxTpRanks];          // every rank's flag array [kMaxTpRanks]; entry r is written by rank r
+  float* partial[kMaxTpRanks][2];  // every rank's two partial-sum buffers (own: local memory, others: peer mappings)
+  uint32_t* flags[kMaxTpRanks];    // every rank's flag arrays; entry r of each is written by rank r
+  uint2* picks[kMaxTpRanks];       // every rank's (best logit bits, token) per lane
   int rank, world;
 };
-// hidden[0, count) += sum over ranks of partial[rank][buffer][0, count); count is a multiple of 4.
-cudaError_t launch_tp_allreduce(const PeerView& view, int buffer, float* hidden, size_t count, uint32_t* epoch_counter,
-                                uint32_t* done_counter, DeviceStatus* status, cudaStream_t stream);
+inline void tp_view_bind(PeerView& view, int r, unsigned char* base, size_t partial_bytes) {
+  view.flags[r] = reinterpret_cast<uint32_t*>(base);
+  view.picks[r] = reinterpret_cast<uint2*>(base + kTpPickOffset);
+  view.partial[r][0] = reinterpret_cast<float*>(base + kTpHeaderBytes);
+  view.partial[r][1] = reinterpret_cast<float*>(base + kTpHeaderBytes + partial_bytes);
+}
+// hidden[0, count) += sum over ranks of partial[rank][buffer][0, count); count is a multiple of 4. sum.splits > 0: this
+// rank's partial is first added up from split-K partials of a [count / columns, columns] projection result.
+cudaError_t launch_tp_allreduce(const PeerView& view, int buffer, float* hidden, size_t count, int columns, const DeferredSum& sum,
+                                bool two_shot, uint32_t* counters, long long wait_cycles, DeviceStatus* status, cudaStream_t stream);
+// tokens[b] = the token of the largest logit over all ranks' picks (lowest token on ties), b < batch <= kTpMaxPicks.
+cudaError_t launch_tp_pick(const PeerView& view, int batch, uint32_t* tokens, uint32_t* counters, long long wait_cycles,
+                           DeviceStatus* status, cudaStream_t stream);
 
 // ---- dense / elementwise (elementwise.cu) --------------------------------------------------
 cudaError_t launch_linear_f32(const float* x, int64_t m, int64_t k, const float* w, int64_t n, const float* bias,
@@ -125,7 +143,8 @@ cudaError_t launch_rope(const float* x, const int64_t* offsets, int64_t n_offset
 cudaError_t launch_swiglu(const float* gate, const float* up, int64_t n, float* out, int exact, cudaStream_t stream);
 cudaError_t launch_add(const float* a, const float* b, int64_t n, float* out, cudaStream_t stream);
 cudaError_t launch_argmax(const float* logits, int64_t rows, int64_t vocab, uint32_t* tokens, DeviceStatus* status,
-                          cudaStream_t stream);
+                          cudaStream_t stream,
+                          uint2* picks = nullptr, uint32_t index_base = 0);
 cudaError_t launch_embedding_f32(const void* indexes, int index_is_i64, int64_t count, const float* table, int64_t rows,
                                  int64_t columns, float* out, DeviceStatus* status, cudaStream_t stream);
 // [B,T,H*D] <-> [B,H,T,D] (the reshape/transpose pairs around attention)

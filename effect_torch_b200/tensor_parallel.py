@@ -1,7 +1,9 @@
 """Host-side sharding for tensor parallelism: which part of every weight a rank holds, and the local geometry its
 decoder is built with. Column-parallel projections (wq, wk, wv, gate, up) split the ROWS of the reference's [N, K]
 weights; row-parallel ones (wo, down) split K, i.e. a range of 32-value blocks of every packed row (quantized rows are
-sequences of blocks: crates/runtime-cpu/src/quantized.rs:263-292). Embedding, norms and head are replicated.
+sequences of blocks: crates/runtime-cpu/src/quantized.rs:263-292). Embedding and norms are replicated; the head is
+replicated or, with shard_head, cut by rows (vocabulary parallel: every rank scores vocab / world tokens and the ranks
+exchange their best).
 
 Works on numpy arrays and on torch tensors alike (only slicing, reshape and contiguity are used).
 """
@@ -23,13 +25,20 @@ def check_geometry(cfg: dict, world: int) -> None:
         raise ValueError("a rank's share of ffn and of q_heads * head_dim must be a multiple of 64 columns")
 
 
-def local_config(cfg: dict, world: int) -> dict:
-    """The geometry one rank's decoder and KV pool are created with."""
+def local_config(cfg: dict, world: int, shard_head: bool = False, rank: int = 0) -> dict:
+    """The geometry one rank's decoder and KV pool are created with. shard_head: `vocab` becomes this rank's number of
+    head rows and `vocab_global` / `head_first_row` say where they sit (Executable takes both)."""
     check_geometry(cfg, world)
     out = dict(cfg)
     out["q_heads"] = cfg["q_heads"] // world
     out["kv_heads"] = cfg["kv_heads"] // world
     out["ffn"] = cfg["ffn"] // world
+    if shard_head and world > 1:
+        if cfg["vocab"] % world:
+            raise ValueError(f"vocab = {cfg['vocab']} is not divisible by the {world} ranks")
+        out["vocab"] = cfg["vocab"] // world
+        out["vocab_global"] = cfg["vocab"]
+        out["head_first_row"] = rank * out["vocab"]
     return out
 
 
@@ -60,7 +69,7 @@ def shard_columns(weight, codec: int, rank: int, world: int):
     return _contiguous(weight[:, rank * per:(rank + 1) * per])
 
 
-def shard_weights(weights: dict, cfg: dict, rank: int, world: int) -> dict:
+def shard_weights(weights: dict, cfg: dict, rank: int, world: int, shard_head: bool = False) -> dict:
     """One rank's share of a weight dictionary laid out like tests/helpers.make_weights: projections are either dense
     [N, K] arrays or (packed, rows, columns) tuples."""
     check_geometry(cfg, world)
@@ -78,7 +87,8 @@ def shard_weights(weights: dict, cfg: dict, rank: int, world: int) -> dict:
             return (shard_columns(packed, codec, rank, world), n, k // world)
         return shard_columns(value, 0, rank, world)
 
-    out = {"tok_embd": weights["tok_embd"], "out_norm": weights["out_norm"], "head": weights["head"], "codec": codec, "layers": []}
+    head = rows(weights["head"]) if shard_head and world > 1 else weights["head"]
+    out = {"tok_embd": weights["tok_embd"], "out_norm": weights["out_norm"], "head": head, "codec": codec, "layers": []}
     for layer in weights["layers"]:
         local = dict(layer)
         for name in ROW_SPLIT:

@@ -345,7 +345,8 @@ ETC_API etc_status etc_gguf_load_tensor_device(etc_runtime* rt, const etc_gguf* 
                                                uint64_t dst_bytes, const volatile int* cancelled);
 
 /* Tensor parallelism (one process per GPU; no counterpart in the single-device reference). Each rank creates its
- * decoder with LOCAL geometry (q_heads/world, kv_heads/world, ffn/world; d_model and vocab whole) and binds its shard
+ * decoder with LOCAL geometry (q_heads/world, kv_heads/world, ffn/world; d_model whole; vocab whole unless the head is
+ * sharded, see etc_decoder_set_head_shard) and binds its shard
  * of every projection: a contiguous row range of wq/wk/wv/gate/up, a contiguous range of 32-value blocks of every row
  * of wo/down; embedding, norms and head are replicated, and so is the host-side page allocation, so every rank's KV
  * pool (built with the local kv_heads) holds the same page tables. Rank 0 makes the 128-byte id, the host sends it to
@@ -354,8 +355,10 @@ ETC_API etc_status etc_gguf_load_tensor_device(etc_runtime* rt, const etc_gguf* 
  * captured step graph as well); rank 0 alone adds the residual. world == 1 is accepted and changes nothing. */
 ETC_API etc_status etc_tp_unique_id(uint8_t* out_id_128_bytes);
 ETC_API etc_status etc_decoder_set_tensor_parallel(etc_decoder* dec, int rank, int world, const uint8_t* id_128_bytes);
-/* Optional, after etc_decoder_set_tensor_parallel and etc_decoder_finalize: replace the NCCL all-reduce by a one-shot
- * kernel over peer memory (CUDA IPC, plain peer loads over NVLink, 2..8 ranks on one node). Every rank exports a
+/* Optional, after etc_decoder_set_tensor_parallel and etc_decoder_finalize: replace the NCCL all-reduce by the
+ * library's kernel over peer memory (CUDA IPC, plain peer loads over NVLink, 2..8 ranks on one node): one shot at
+ * 2 ranks (every rank adds all ranks' partial sums), reduce-scatter + all-gather from 4 ranks on; the row-parallel
+ * projection's split-K partials are summed inside the same kernel. Every rank exports a
  * 64-byte handle of its exchange region, the host gathers the handles of all ranks into a table [world][64] (own slot
  * ignored) and every rank imports it. The kernel's wait for its peers is bounded: a rank that never arrives turns
  * into ETC_EXECUTION at the next synchronising call, not into a hang.
@@ -366,6 +369,23 @@ ETC_API etc_status etc_decoder_set_tensor_parallel(etc_decoder* dec, int rank, i
  * barrier: a peer may still be reading this rank's exchange region until its own step has been synchronised. */
 ETC_API etc_status etc_decoder_tp_peer_export(etc_decoder* dec, uint8_t* out_handle_64_bytes);
 ETC_API etc_status etc_decoder_tp_peer_import(etc_decoder* dec, const uint8_t* handles_world_x_64_bytes);
+/* Vocabulary-parallel head, before any weight is bound: the decoder's config.vocab is the number of head rows this rank
+ * holds, rows [first_row, first_row + config.vocab) of a head with `vocab_global` rows; the token embedding keeps
+ * vocab_global rows on every rank. Greedy steps then exchange every rank's (best logit, token) pair over the peer
+ * regions (etc_decoder_tp_peer_import is required) and keep the largest logit, on ties the lowest token, exactly what
+ * an ascending scan with a strict comparison finds on one device (crates/runtime/src/sampling.rs:88-105).
+ * etc_decoder_execute returns this rank's [active, config.vocab] slice of the logits. */
+ETC_API etc_status etc_decoder_set_head_shard(etc_decoder* dec, int64_t vocab_global, int64_t first_row);
+/* The peer-memory all-reduce as an operator of its own. A region is etc_peer_region_bytes(capacity) bytes of device
+ * memory, zeroed once before its first use; regions[r] is rank r's region as mapped in this process (own rank: local
+ * memory). hidden[0, count) += sum over ranks of the partial sums in buffer `buffer` (0 or 1) of every region; with
+ * d_partial the call first copies this rank's partial sum into its region. count is a multiple of 4, at most
+ * `capacity`. wait_cycles bounds the wait for the peers in SM clock cycles (<= 0: about one second); when it runs out
+ * the launch gives up and the next synchronising call returns ETC_EXECUTION, the runtime stays usable. */
+ETC_API size_t etc_peer_region_bytes(int64_t capacity);
+ETC_API etc_status etc_peer_allreduce_into(etc_runtime* rt, int rank, int world, void* const* regions, int64_t capacity,
+                                           int buffer, const float* d_partial, float* d_hidden, int64_t count, int two_shot,
+                                           int64_t wait_cycles);
 
 /* The attention half of kv_attention_into alone, over lane descriptors and block tables that already sit in device
  * memory (the decode kernel of napi/mod.rs:3478-3540 for one query token per lane; what the Metal backend's paged kernel

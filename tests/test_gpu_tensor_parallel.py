@@ -1,4 +1,4 @@
-"""Tensor-parallel decoder on 2 GPUs (skipped where fewer are visible): child processes, one per GPU."""
+"""Tensor-parallel decoder on 2 and 4 GPUs (skipped where fewer are visible): child processes, one per GPU."""
 import os
 import socket
 import subprocess
@@ -16,14 +16,15 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def test_two_rank_decoder_matches_the_oracle_and_itself():
+@pytest.mark.parametrize("world", [2, 4])
+def test_tensor_parallel_decoder_matches_the_oracle_and_itself(world):
     import torch
 
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")  # plain ring/tree: a child that dies must not take multicast state with it
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
            "--master-port", str(_free_port()), os.path.join(ROOT, "tests", "tp_worker.py")]
-    done = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
+    done = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=900)
     assert done.returncode == 0, done.stdout[-3000:] + done.stderr[-3000:]
     assert "tensor parallel parity ok" in done.stdout

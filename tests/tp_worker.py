@@ -1,7 +1,9 @@
 """One rank of the tensor-parallel parity check on GPUs; tests/test_gpu_tensor_parallel.py launches world_size of these
 with torch.distributed.run. Every rank builds its shard of a small Q4_0 model; rank 0 also runs the CPU oracle on the
 whole model. Checked: teacher-forced logits against the oracle (2e-3), identical tokens on all ranks, and the
-device-resident greedy loop (CUDA graph with the all-reduces captured) against step-by-step execution."""
+device-resident greedy loop (CUDA graph with the all-reduces captured) against step-by-step execution: with the NCCL
+all-reduce, with the peer-memory all-reduce (one shot at 2 ranks, reduce-scatter + all-gather from 4 on, and both
+forced), and with a vocabulary-parallel head whose ranks exchange their best logit."""
 import os
 import sys
 
@@ -22,7 +24,7 @@ def build(rt, cfg, weights, batch, max_tokens):
     dec = et.Executable(rt, layers=cfg["layers"], d_model=cfg["d_model"], q_heads=cfg["q_heads"], kv_heads=cfg["kv_heads"],
                         head_dim=cfg["head_dim"], ffn=cfg["ffn"], vocab=cfg["vocab"], rms_eps=cfg["rms_eps"],
                         rope_theta=cfg["rope_theta"], batch=batch, max_tokens=max_tokens, block_size=16, kv_dtype=et.KV_F16,
-                        exact=False, max_advance=8)
+                        exact=False, max_advance=8, vocab_global=cfg.get("vocab_global"), head_first_row=cfg.get("head_first_row", 0))
     helpers.load_into(dec, weights)
     dec.finalize()
     return dec
@@ -37,7 +39,7 @@ def main():
     B, max_tokens = 3, 512
     rt = et.Runtime(local)
     lcfg = tp.local_config(cfg, world)
-    dec = build(rt, lcfg, tp.shard_weights(weights, cfg, rank, world), B, max_tokens)
+    replicated = dec = build(rt, lcfg, tp.shard_weights(weights, cfg, rank, world), B, max_tokens)
     ident = torch.zeros(128, dtype=torch.uint8)
     if rank == 0:
         ident = torch.frombuffer(bytearray(et.tensor_parallel_id()), dtype=torch.uint8).clone()
@@ -53,7 +55,8 @@ def main():
         dist.all_gather(everyone, mine)
         return all(torch.equal(everyone[0], e) for e in everyone[1:])
 
-    def run_checks(tag):
+    def run_checks(tag, dec=None, sharded_head=False):
+        dec = dec or replicated
         seqs = [pool.makeSequence() for _ in range(B)]
         if rank == 0:
             opool = orc.Pool(cfg["layers"], cfg["kv_heads"], cfg["head_dim"], max_tokens, 16, orc.F16)
@@ -62,6 +65,11 @@ def main():
         for advance in (8, 5, 1, 1, 1):
             toks = rng.integers(0, cfg["vocab"], size=(B, advance)).astype(np.uint32)
             gl = dec.execute(pool, seqs, toks)
+            if sharded_head:  # every rank returns its slice of the vocabulary: put the slices side by side
+                mine = torch.from_numpy(gl.copy())
+                slices = [torch.empty_like(mine) for _ in range(world)]
+                dist.all_gather(slices, mine)
+                gl = torch.cat(slices, dim=1).numpy()
             if rank == 0:
                 ol, _ = odec.execute(opool, oseqs, toks)
                 err = helpers.rel_err(gl, ol)
@@ -102,8 +110,32 @@ def main():
     dist.all_gather(table, mine)
     dec.use_peer_allreduce([bytes(t.tolist()) for t in table])
     tokens_peer = run_checks("peer-memory all-reduce")
-    if world == 2 and not np.array_equal(tokens_nccl, tokens_peer):  # two ranks: both paths add in the same order
-        failures.append("the two all-reduce paths generated different tokens")
+    del tokens_nccl  # NCCL adds in its own order: equal within the logits tolerance checked above, not bit for bit
+
+    def second_decoder(tag, shard_head, two_shot):
+        """A decoder of its own (the exchange regions are per decoder) with the given head layout and all-reduce kind."""
+        os.environ["ETC_TP_TWO_SHOT"] = "1" if two_shot else "0"
+        cfg2 = tp.local_config(cfg, world, shard_head=shard_head, rank=rank)
+        dec2 = build(rt, cfg2, tp.shard_weights(weights, cfg, rank, world, shard_head=shard_head), B, max_tokens)
+        ident2 = torch.zeros(128, dtype=torch.uint8)
+        if rank == 0:
+            ident2 = torch.frombuffer(bytearray(et.tensor_parallel_id()), dtype=torch.uint8).clone()
+        dist.broadcast(ident2, src=0)
+        dec2.set_tensor_parallel(rank, world, bytes(ident2.tolist()))
+        mine = torch.frombuffer(bytearray(dec2.peer_exchange_handle()), dtype=torch.uint8).clone()
+        table = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(table, mine)
+        dec2.use_peer_allreduce([bytes(t.tolist()) for t in table])
+        tokens = run_checks(tag, dec2, sharded_head=shard_head)
+        dist.barrier()  # nobody reads this decoder's region any more
+        dec2.close()
+        return tokens
+
+    tokens_other = second_decoder("the other peer all-reduce kind", False, two_shot=world < 4)
+    tokens_vocab = second_decoder("vocabulary-parallel head", True, two_shot=world >= 4)
+    for name, got in (("the other peer all-reduce kind", tokens_other), ("the vocabulary-parallel head", tokens_vocab)):
+        if not np.array_equal(got, tokens_peer):  # one-shot and two-shot add in rank order: the same sums, the same tokens
+            failures.append(f"{name} generated different tokens from the default peer path")
 
     flag = torch.tensor([len(failures)])
     dist.all_reduce(flag)
