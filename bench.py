@@ -234,7 +234,7 @@ def run_reference_arm(args, rank):
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # ------------------------------------------------------------------------------------------------ GPU arm
@@ -266,15 +266,17 @@ def build_decoder(rt, et, torch, model, batch, max_tokens, seed, shared_seed=Non
     dec = et.Executable(rt, layers=model["layers"], d_model=model["d_model"], q_heads=model["q_heads"], kv_heads=model["kv_heads"],
                         head_dim=model["head_dim"], ffn=model["ffn"], vocab=model["vocab"], rms_eps=model["rms_eps"],
                         rope_theta=model["rope_theta"], batch=batch, max_tokens=max_tokens, block_size=BLOCK, kv_dtype=et.KV_F16,
-                        exact=False, max_advance=max_advance)
+                        exact=False, max_advance=max_advance, vocab_global=model.get("vocab_global"),
+                        head_first_row=model.get("head_first_row", 0))
     d, qw, kvw, ffn, V = (model["d_model"], model["q_heads"] * model["head_dim"], model["kv_heads"] * model["head_dim"], model["ffn"],
                           model["vocab"])
+    V_embd = model.get("vocab_global", V)
 
     def bind(slot, layer, tensor, codec=0, rows=None, cols=None):
         torch.cuda.synchronize()
         dec.set_weight(slot, layer, tensor, codec=codec, rows=rows, columns=cols)
 
-    embd = torch.randn((V, d), generator=shared, device="cuda", dtype=torch.float32)
+    embd = torch.randn((V_embd, d), generator=shared, device="cuda", dtype=torch.float32)
     embd.mul_(0.02)
     bind(et.W_TOK_EMBD, 0, embd)
     del embd
@@ -286,7 +288,8 @@ def build_decoder(rt, et, torch, model, batch, max_tokens, seed, shared_seed=Non
                              (et.W_UP, (ffn, d)), (et.W_DOWN, (d, ffn))):
             bind(slot, l, device_quantized(rt, torch, Q4_0, r, c, gen), Q4_0, r, c)
     bind(et.W_OUT_NORM, 0, ones)
-    bind(et.W_HEAD, 0, device_quantized(rt, torch, Q4_0, V, d, shared), Q4_0, V, d)
+    # a sharded head: every rank draws its own rows (the ranks only have to agree on what they replicate)
+    bind(et.W_HEAD, 0, device_quantized(rt, torch, Q4_0, V, d, gen if "vocab_global" in model else shared), Q4_0, V, d)
     dec.finalize()
     torch.cuda.empty_cache()
     return dec
@@ -488,10 +491,12 @@ def run_tp_70b(args, rank, world, rt, et, torch, dist, steps, warmup):
     full = dict(MODEL_70B)
     if args.layers:
         full["layers"] = args.layers
-    model = tensor_parallel.local_config(full, world)
+    shard_head = world > 1 and args.tp_head == "sharded"
+    model = tensor_parallel.local_config(full, world, shard_head=shard_head, rank=rank)
     B, K, W, chunk = 64, steps, warmup, 256
     rng = np.random.default_rng(4)  # the same contexts and tokens on every rank
-    ctx = np.sort((rng.integers(1024, 8193, size=B) // chunk) * chunk)[::-1].copy()
+    lo, hi = (1024, 8192) if world > 1 else (256, 1024)  # one GPU: 138 GB of weights leave room for an eighth of the KV
+    ctx = np.sort((rng.integers(lo, hi + 1, size=B) // chunk) * chunk)[::-1].copy()
     max_tokens = ((int(ctx.sum()) + B * (W + K + 2 * BLOCK)) // BLOCK + B) * BLOCK
     dec = build_decoder(rt, et, torch, model, B, max_tokens, seed=40 + rank, shared_seed=4)
     allreduce = "none"
@@ -501,12 +506,15 @@ def run_tp_70b(args, rank, world, rt, et, torch, dist, steps, warmup):
             ident = torch.frombuffer(bytearray(et.tensor_parallel_id()), dtype=torch.uint8).cuda()
         dist.broadcast(ident, src=0)
         dec.set_tensor_parallel(rank, world, bytes(ident.cpu().tolist()))
-        allreduce = args.tp_allreduce if args.tp_allreduce != "auto" else ("peer" if world <= 2 else "nccl")
+        allreduce = args.tp_allreduce if args.tp_allreduce != "auto" else "peer"
+        if shard_head and allreduce != "peer":
+            raise RuntimeError("a sharded head exchanges its picks over the peer regions: use --tp-allreduce peer or --tp-head replicated")
         if allreduce == "peer":
             mine = torch.frombuffer(bytearray(dec.peer_exchange_handle()), dtype=torch.uint8).cuda()
             table = [torch.empty_like(mine) for _ in range(world)]
             dist.all_gather(table, mine)
             dec.use_peer_allreduce([bytes(t.cpu().tolist()) for t in table])
+            allreduce = "peer memory, one shot" if world < 4 else "peer memory, reduce-scatter + all-gather"
     pool = et.NativeKvPool(rt, model["layers"], model["kv_heads"], model["head_dim"], max_tokens, BLOCK, et.KV_F16)
     seqs = [pool.makeSequence() for _ in range(B)]
     kv = torch.randn((B, model["kv_heads"], chunk, model["head_dim"]), device="cuda", dtype=torch.float32)
@@ -557,8 +565,10 @@ def run_tp_70b(args, rank, world, rt, et, torch, dist, steps, warmup):
         "tp": world, "steps": K, "warmup": W, "ms_per_step": 1000.0 * seconds / K, "scaling": "strong",
         "config": {"workload": f"llama3-70b-shape Q4_0 paged decode: {full['layers']} layers, batch {B}, contexts {int(ctx.min())}.."
                                f"{int(ctx.max())} (mean {ctx.mean():.0f}) written directly into the pages, {K} greedy steps",
-                   "parallelism": f"tp{world}: rows of q/k/v/gate/up and columns of o/down cut over the ranks, {allreduce} all-reduce of "
-                                  "[batch, d_model] f32 after o and down, head replicated"},
+                   "parallelism": "one GPU holds the whole model" if world == 1 else
+                                  f"tp{world}: rows of q/k/v/gate/up and columns of o/down cut over the ranks, {allreduce} all-reduce of "
+                                  "[batch, d_model] f32 after o and down (split-K partials summed in the same kernel), head "
+                                  + ("cut by rows, (logit, token) picks exchanged" if shard_head else "replicated")},
         "launches_per_step": launches, "all_reduce": allreduce, "ranks_agree_on_tokens": agree,
         "step_roofline": {"algorithmic_bytes_per_step_all_ranks": step_bytes, "achieved_gbs_per_rank": step_bytes / world * K / seconds / 1e9,
                           "frac_of_" + peak_kind + "_per_rank": step_bytes / world * K / seconds / 1e9 / peaks["hbm_gbs"]},
@@ -745,22 +755,43 @@ def run_gpu_arm(args, rank, world):
             cpu["reference_faithful"] = {"value": fv, "unit": "tokens/s", "cores": 1, "sample": fsample, "cpu_seconds": fseconds}
         line["cpu_baseline"] = cpu
     tp_line = None
-    if not args.no_tp70b and (world > 1 or args.with_70b):
+    if not args.no_tp70b and not args.layers:
+        free_bytes = torch.cuda.mem_get_info()[0]
         try:
+            if world == 1 and free_bytes < 168e9:
+                raise RuntimeError(f"only {free_bytes / 1e9:.0f} GB free on the device: the 70B shape needs 160 GB on one GPU")
             tp_line = run_tp_70b(args, rank, world, rt, et, torch, dist, steps=min(K, args.tp_steps), warmup=min(W, 3))
         except Exception as exc:  # the headline must survive a failure of the extra workload
             tp_line = {"error": f"{type(exc).__name__}: {exc}"[:300]}
     if rank == 0:
         if tp_line is not None:
             line["tp"] = tp_line
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
     return line
 
 
+_JSON_OUT = None
+
+
+def emit(line):
+    """The JSON line goes to the process's real stdout; everything else a library prints meanwhile (NCCL's version
+    banner for one) was sent to stderr by main()."""
+    text = json.dumps(line) + "\n"
+    if _JSON_OUT is None:
+        sys.stdout.write(text)
+        sys.stdout.flush()
+    else:
+        os.write(_JSON_OUT, text.encode())
+
+
 def main():
+    global _JSON_OUT
+    sys.stdout.flush()
+    _JSON_OUT = os.dup(1)
+    os.dup2(2, 1)  # stray prints of libraries must not mix with the one JSON line
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
@@ -769,14 +800,15 @@ def main():
     ap.add_argument("--tp-allreduce", default="auto", choices=["auto", "peer", "nccl"],
                     help="tensor parallel: all-reduce by the library's one-shot peer-memory kernel or by NCCL (auto: peer at 2 ranks, "
                          "NCCL above)")
+    ap.add_argument("--tp-head", default="sharded", choices=["sharded", "replicated"],
+                    help="tensor parallel: the head cut by rows over the ranks (every rank scores vocab / N tokens) or whole on every rank")
     ap.add_argument("--layers", type=int, default=0, help="debug: fewer layers than the named shape (the result is then not a bench value)")
     ap.add_argument("--workload", default="decode", choices=["decode", "decode-70b"],
                     help="decode: the headline 8B-shape decode step (the bench contract) with the kernel rooflines, microbenchmarks and, at "
                          "N > 1, the 70B tensor-parallel run in the same line; decode-70b: only the 70B shape over --gpus ranks")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-microbench", action="store_true", help="skip the quantized-matmul and paged-attention microbenchmark tables")
-    ap.add_argument("--no-tp70b", action="store_true", help="skip the 70B tensor-parallel run that N > 1 adds to the line")
-    ap.add_argument("--with-70b", action="store_true", help="N = 1: add the 70B shape on one GPU (138 GB) as the tp object")
+    ap.add_argument("--no-tp70b", action="store_true", help="skip the 70B-shape run (tensor parallel over the N ranks) that fills the line's tp object")
     ap.add_argument("--tp-steps", type=int, default=32, help="decode steps of the 70B run")
     ap.add_argument("--parallelism", default="replicas", choices=["replicas", "tp"],
                     help="N > 1: N independent replicas, each decoding its own batch (weak scaling; the 8B shape fits one GPU), or "
@@ -803,7 +835,7 @@ def main():
         line = run_tp_70b(args, rank, world, et.Runtime(local), et, torch, dist, steps=args.steps, warmup=args.warmup)
         if rank == 0:
             line["n_gpus"] = world
-            print(json.dumps(line), flush=True)
+            emit(line)
         if world > 1:
             dist.barrier()
             dist.destroy_process_group()
