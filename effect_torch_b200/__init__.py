@@ -205,9 +205,9 @@ class Runtime:
                                                    scale, NO_WINDOW if op_window is None else op_window,
                                                    NO_WINDOW if pool_window is None else pool_window, _ptr(out)))
 
-    def peer_allreduce_into(self, rank, world, regions, capacity, buffer, hidden, count, partial=None, two_shot=False, wait_cycles=0):
-        """hidden[:count] += sum over ranks of the partial sums in `buffer` of every region (device pointers, own rank
-        local); asynchronous. A peer that never arrives turns into BackendError(ETC_EXECUTION) at the next synchronize."""
+    def peer_allreduce_into(self, rank, world, regions, capacity, buffer, hidden, count, partial, two_shot=False, wait_cycles=0):
+        """hidden[:count] += sum over ranks of their partial sums, exchanged through `buffer` of every rank's region
+        (device pointers, own rank local); asynchronous. A peer that never arrives turns into BackendError(ETC_EXECUTION) at the next synchronize."""
         arr = (C.c_void_p * world)(*[_ptr(r) for r in regions])
         _check(self.L.etc_peer_allreduce_into(self.h, rank, world, arr, capacity, buffer, _ptr(partial), _ptr(hidden), count,
                                               int(two_shot), wait_cycles))
@@ -220,9 +220,9 @@ class Runtime:
                                                scratch_bytes))
 
 
-def peer_region_bytes(capacity: int) -> int:
-    """Bytes of one rank's exchange region for peer all-reduces of up to `capacity` floats."""
-    return int(_lib.load().etc_peer_region_bytes(capacity))
+def peer_region_bytes(capacity: int, world: int) -> int:
+    """Bytes of one rank's exchange region for peer all-reduces of up to `capacity` floats among `world` ranks."""
+    return int(_lib.load().etc_peer_region_bytes(capacity, world))
 
 
 class QWeight:
@@ -438,6 +438,21 @@ class Executable:
         """Switches the all-reduces to the one-shot kernel over peer memory; `handles[r]` is rank r's exchange handle."""
         table = (C.c_uint8 * (64 * len(handles))).from_buffer_copy(b"".join(handles))
         _check(self.rt.L.etc_decoder_tp_peer_import(self.h, table))
+
+    def peer_region(self):
+        """(device pointer, bytes) of this rank's exchange region, for hosts that map the regions themselves."""
+        ptr, size = C.c_void_p(), C.c_size_t(0)
+        _check(self.rt.L.etc_decoder_tp_region(self.h, C.byref(ptr), C.byref(size)))
+        return ptr.value, size.value
+
+    def attach_peer_regions(self, regions: list):
+        """regions[r]: rank r's region as a device tensor / pointer valid in this process (own slot ignored)."""
+        arr = (C.c_void_p * len(regions))(*[_ptr(r) for r in regions])
+        _check(self.rt.L.etc_decoder_tp_peer_attach(self.h, arr))
+
+    def set_wait_limit(self, cycles: int):
+        """Bound of the waits for a peer inside the step's kernels, in SM clock cycles."""
+        _check(self.rt.L.etc_decoder_set_wait_limit(self.h, cycles))
 
     @staticmethod
     def _seq_array(seqs):

@@ -108,7 +108,10 @@ SIGNATURES = {
     "etc_decoder_tp_peer_export": (None, [P, P]),
     "etc_decoder_tp_peer_import": (None, [P, P]),
     "etc_decoder_set_head_shard": (None, [P, I64, I64]),
-    "etc_peer_region_bytes": (SZ, [I64]),
+    "etc_decoder_tp_region": (None, [P, P, P]),
+    "etc_decoder_tp_peer_attach": (None, [P, P]),
+    "etc_decoder_set_wait_limit": (None, [P, I64]),
+    "etc_peer_region_bytes": (SZ, [I64, I]),
     "etc_peer_allreduce_into": (None, [P, I, I, P, I64, I, P, P, I64, I, I64]),
     "etc_decoder_finalize": (None, [P]),
     "etc_decoder_execute": (None, [P, P, P, I, P, I, P, P]),

@@ -248,14 +248,13 @@ etc_status project_into_hidden(StepContext& s, const BoundWeight& raw, etc_qweig
   const bool sharded = d->tp_world > 1;
   if (defer) *defer = DeferredSum();
   if (sharded && d->tp_peer) {
-    // every rank leaves its partial sum in its exported buffer (or, split over K, as partials the all-reduce kernel adds
-    // up first); the all-reduce kernel adds all ranks' sums onto hidden
-    float* partial = reinterpret_cast<float*>(d->tp_region + kTpHeaderBytes + (size_t)buffer * d->tp_partial_bytes);
+    // the all-reduce kernel sends this rank's partial sum (added up from the projection's split-K partials on the way
+    // when there are any) into the peers' regions and adds all ranks' sums onto hidden
     DeferredSum sum;
-    ETC_TRY(run_linear(s, raw, tiled_w, x, rows, partial, ETC_EPILOGUE_NONE, nullptr, xh_ready, nullptr, &sum));
-    ETC_CUDA(launch_tp_allreduce(d->tp_view, buffer, d->hidden, (size_t)rows * d->cfg.d_model, d->cfg.d_model, sum, d->tp_two_shot,
-                                 reinterpret_cast<uint32_t*>(d->tp_region + kTpCounterOffset), d->tp_wait_cycles, d->rt->d_status,
-                                 d->rt->stream));
+    ETC_TRY(run_linear(s, raw, tiled_w, x, rows, d->proj, ETC_EPILOGUE_NONE, nullptr, xh_ready, nullptr, &sum));
+    ETC_CUDA(launch_tp_allreduce(d->tp_view, buffer, d->hidden, (size_t)rows * d->cfg.d_model, d->cfg.d_model, sum, d->proj, d->tp_two_shot,
+                                 reinterpret_cast<uint32_t*>(d->tp_region + kTpCounterOffset), d->tp_wait_cycles, d->rt->sm_count,
+                                 d->rt->d_status, d->rt->stream));
     ++s.launches;
     return ETC_OK;
   }
@@ -264,6 +263,7 @@ etc_status project_into_hidden(StepContext& s, const BoundWeight& raw, etc_qweig
                      nullptr, sharded ? nullptr : defer));
   if (sharded) {
     std::string error;
+    if (!d->tp) return fail(ETC_EXECUTION, "tensor parallel: the group has neither a communicator nor attached peer regions");
     if (!tp_allreduce_sum(d->tp, d->hidden, (size_t)rows * d->cfg.d_model, d->rt->stream, &error)) return fail(ETC_EXECUTION, error);
     ++s.launches;
   }
@@ -720,11 +720,13 @@ etc_status etc_decoder_set_tensor_parallel(etc_decoder* dec, int rank, int world
   if (world < 1 || rank < 0 || rank >= world) return fail(ETC_INVALID_ARGUMENT, "tensor parallel: rank " + std::to_string(rank) + " is outside 0.." + std::to_string(world));
   if (dec->tp) return fail(ETC_COMPILATION, "tensor parallel: the decoder already has a communicator");
   if (world == 1) return ETC_OK;
-  if (!id) return fail(ETC_INVALID_ARGUMENT, "tensor parallel: the id buffer is null");
+  if (dec->tp_world > 1) return fail(ETC_COMPILATION, "tensor parallel: the decoder already belongs to a group");
   ETC_TRY(activate(dec->rt));
-  std::string error;
-  dec->tp = tp_comm_create(rank, world, id, &error);
-  if (!dec->tp) return fail(ETC_UNAVAILABLE, "tensor parallel: " + error);
+  if (id) {  // without an id there is no NCCL communicator: the ranks exchange through peer regions only
+    std::string error;
+    dec->tp = tp_comm_create(rank, world, id, &error);
+    if (!dec->tp) return fail(ETC_UNAVAILABLE, "tensor parallel: " + error);
+  }
   dec->tp_rank = rank;
   dec->tp_world = world;
   if (dec->step_graph) {  // captured without the all-reduces
@@ -738,9 +740,9 @@ etc_status etc_decoder_set_tensor_parallel(etc_decoder* dec, int rank, int world
   return ETC_OK;
 }
 
-etc_status etc_decoder_tp_peer_export(etc_decoder* dec, uint8_t* out_handle) {
-  if (!valid_decoder(dec)) return fail(ETC_INVALID_HANDLE, "decoder handle is invalid or destroyed");
-  if (!out_handle) return fail(ETC_INVALID_ARGUMENT, "tensor parallel: the handle buffer is null");
+namespace {
+
+etc_status ensure_tp_region(etc_decoder* dec) {
   if (!dec->finalized) return fail(ETC_COMPILATION, "tensor parallel: finalize the decoder before exporting its exchange region");
   if (dec->tp_world < 2 || dec->tp_world > kMaxTpRanks)
     return fail(ETC_UNSUPPORTED, "tensor parallel: the peer-memory all-reduce serves 2 to " + std::to_string(kMaxTpRanks) + " ranks");
@@ -748,12 +750,42 @@ etc_status etc_decoder_tp_peer_export(etc_decoder* dec, uint8_t* out_handle) {
   ETC_TRY(activate(rt));
   if (!dec->tp_region) {
     const size_t floats = (size_t)dec->cfg.batch * dec->max_advance * dec->cfg.d_model;
-    dec->tp_partial_bytes = (floats * sizeof(float) + 255) & ~(size_t)255;
-    const size_t bytes = kTpHeaderBytes + 2 * dec->tp_partial_bytes;
+    dec->tp_partial_bytes = tp_slot_bytes(floats);
+    const size_t bytes = tp_region_bytes(floats, dec->tp_world);
     ETC_TRY(rt->device_alloc(bytes, (void**)&dec->tp_region));
     ETC_CUDA(cudaMemsetAsync(dec->tp_region, 0, bytes, rt->stream));
     ETC_CUDA(cudaStreamSynchronize(rt->stream));  // peers may write flags as soon as they hold the handle
   }
+  return ETC_OK;
+}
+
+// regions[r]: rank r's region as mapped in this process (own slot: the decoder's own region)
+etc_status bind_peers(etc_decoder* dec, unsigned char* const* regions) {
+  PeerView view{};
+  view.rank = dec->tp_rank;
+  view.world = dec->tp_world;
+  for (int r = 0; r < dec->tp_world; ++r) tp_view_bind(view, r, regions[r], dec->tp_partial_bytes, dec->tp_world);
+  dec->tp_view = view;
+  dec->tp_peer = true;
+  dec->tp_two_shot = dec->tp_world >= 4;
+  if (const char* forced = std::getenv("ETC_TP_TWO_SHOT")) dec->tp_two_shot = std::atoi(forced) != 0;
+  if (dec->step_graph) {  // captured with the NCCL all-reduces
+    cudaGraphExecDestroy(dec->step_graph);
+    dec->step_graph = nullptr;
+  }
+  if (dec->exec_graph) {
+    cudaGraphExecDestroy(dec->exec_graph);
+    dec->exec_graph = nullptr;
+  }
+  return ETC_OK;
+}
+
+}  // namespace
+
+etc_status etc_decoder_tp_peer_export(etc_decoder* dec, uint8_t* out_handle) {
+  if (!valid_decoder(dec)) return fail(ETC_INVALID_HANDLE, "decoder handle is invalid or destroyed");
+  if (!out_handle) return fail(ETC_INVALID_ARGUMENT, "tensor parallel: the handle buffer is null");
+  ETC_TRY(ensure_tp_region(dec));
   cudaIpcMemHandle_t handle;
   ETC_CUDA(cudaIpcGetMemHandle(&handle, dec->tp_region));
   static_assert(sizeof(handle) == 64, "CUDA IPC handles are 64 bytes");
@@ -768,26 +800,46 @@ etc_status etc_decoder_tp_peer_import(etc_decoder* dec, const uint8_t* handles) 
   if (dec->tp_peer) return fail(ETC_COMPILATION, "tensor parallel: the peers are already mapped");
   etc_runtime* rt = dec->rt;
   ETC_TRY(activate(rt));
-  PeerView view{};
-  view.rank = dec->tp_rank;
-  view.world = dec->tp_world;
+  unsigned char* regions[kMaxTpRanks] = {};
   for (int r = 0; r < dec->tp_world; ++r) {
-    unsigned char* base = dec->tp_region;
+    regions[r] = dec->tp_region;
     if (r != dec->tp_rank) {
       cudaIpcMemHandle_t handle;
       std::memcpy(&handle, handles + (size_t)r * 64, sizeof(handle));
       void* mapped = nullptr;
       ETC_CUDA(cudaIpcOpenMemHandle(&mapped, handle, cudaIpcMemLazyEnablePeerAccess));
       dec->tp_peer_base[r] = mapped;
-      base = static_cast<unsigned char*>(mapped);
+      regions[r] = static_cast<unsigned char*>(mapped);
     }
-    tp_view_bind(view, r, base, dec->tp_partial_bytes);
   }
-  dec->tp_view = view;
-  dec->tp_peer = true;
-  dec->tp_two_shot = dec->tp_world >= 4;
-  if (const char* forced = std::getenv("ETC_TP_TWO_SHOT")) dec->tp_two_shot = std::atoi(forced) != 0;
-  if (dec->step_graph) {  // captured with the NCCL all-reduces
+  return bind_peers(dec, regions);
+}
+
+etc_status etc_decoder_tp_region(etc_decoder* dec, void** out_region, size_t* out_bytes) {
+  if (!valid_decoder(dec)) return fail(ETC_INVALID_HANDLE, "decoder handle is invalid or destroyed");
+  ETC_TRY(ensure_tp_region(dec));
+  if (out_region) *out_region = dec->tp_region;
+  if (out_bytes) *out_bytes = tp_region_bytes((size_t)dec->cfg.batch * dec->max_advance * dec->cfg.d_model, dec->tp_world);
+  return ETC_OK;
+}
+
+etc_status etc_decoder_tp_peer_attach(etc_decoder* dec, void* const* peer_regions) {
+  if (!valid_decoder(dec)) return fail(ETC_INVALID_HANDLE, "decoder handle is invalid or destroyed");
+  if (!peer_regions) return fail(ETC_INVALID_ARGUMENT, "tensor parallel: the region table is null");
+  if (dec->tp_peer) return fail(ETC_COMPILATION, "tensor parallel: the peers are already mapped");
+  ETC_TRY(ensure_tp_region(dec));
+  unsigned char* regions[kMaxTpRanks] = {};
+  for (int r = 0; r < dec->tp_world; ++r) {
+    regions[r] = r == dec->tp_rank ? dec->tp_region : static_cast<unsigned char*>(peer_regions[r]);
+    if (!regions[r]) return fail(ETC_INVALID_ARGUMENT, "tensor parallel: the region of rank " + std::to_string(r) + " is null");
+  }
+  return bind_peers(dec, regions);
+}
+
+etc_status etc_decoder_set_wait_limit(etc_decoder* dec, int64_t cycles) {
+  if (!valid_decoder(dec)) return fail(ETC_INVALID_HANDLE, "decoder handle is invalid or destroyed");
+  dec->tp_wait_cycles = cycles > 0 ? cycles : kTpWaitCycles;
+  if (dec->step_graph) {  // the limit is a kernel argument of the captured all-reduces
     cudaGraphExecDestroy(dec->step_graph);
     dec->step_graph = nullptr;
   }

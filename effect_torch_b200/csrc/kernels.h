@@ -106,29 +106,39 @@ cudaError_t launch_sum_rmsnorm_xh8(float* x, const DeferredSum& sum, const float
 
 // ---- tensor-parallel all-reduce over peer memory (tp_kernels.cu) -----------------------------
 constexpr int kMaxTpRanks = 8;
-// One rank's exchange region: [0, 96) three flag arrays of kTpFlagStride words (partial ready, slice total ready, picks
-// ready), [256, 288) counters private to the owner, [1024, 1024 + 8 * kTpMaxPicks) (best logit, token) pairs, then two
-// partial-sum buffers of `partial_bytes` each from kTpHeaderBytes on.
+// One rank's exchange region: [0, 96) three flag arrays of kTpFlagStride words (partial sums stored, slice totals stored,
+// picks stored), [256, 288) counters private to the owner, [1024, 1024 + 8 * kTpMaxPicks) (best logit, token) pairs, then
+// from kTpHeaderBytes on two exchange buffers of (world + 1) slots of `slot_bytes` each: an inbox with one slot per
+// sender, and the table of totals.
 constexpr int kTpFlagStride = 8;
 constexpr size_t kTpCounterOffset = 256, kTpPickOffset = 1024, kTpHeaderBytes = 4096;
 constexpr int kTpMaxPicks = 256;
 constexpr long long kTpWaitCycles = 1ll << 31;  // about a second
 struct PeerView {
-  float* partial[kMaxTpRanks][2];  // every rank's two partial-sum buffers (own: local memory, others: peer mappings)
-  uint32_t* flags[kMaxTpRanks];    // every rank's flag arrays; entry r of each is written by rank r
-  uint2* picks[kMaxTpRanks];       // every rank's (best logit bits, token) per lane
+  float* inbox[kMaxTpRanks][2];   // every rank's inboxes [world][slot] (own: local memory, others: peer mappings)
+  float* totals[kMaxTpRanks][2];  // every rank's tables of slice totals [slot]
+  uint32_t* flags[kMaxTpRanks];   // every rank's flag arrays; entry r of each is written by rank r
+  uint2* picks[kMaxTpRanks];      // every rank's (best logit bits, token) per lane
   int rank, world;
 };
-inline void tp_view_bind(PeerView& view, int r, unsigned char* base, size_t partial_bytes) {
+inline size_t tp_slot_bytes(size_t capacity_floats) { return (capacity_floats * sizeof(float) + 255) & ~(size_t)255; }
+inline size_t tp_region_bytes(size_t capacity_floats, int world) {
+  return kTpHeaderBytes + 2 * (size_t)(world + 1) * tp_slot_bytes(capacity_floats);
+}
+inline void tp_view_bind(PeerView& view, int r, unsigned char* base, size_t slot_bytes, int world) {
   view.flags[r] = reinterpret_cast<uint32_t*>(base);
   view.picks[r] = reinterpret_cast<uint2*>(base + kTpPickOffset);
-  view.partial[r][0] = reinterpret_cast<float*>(base + kTpHeaderBytes);
-  view.partial[r][1] = reinterpret_cast<float*>(base + kTpHeaderBytes + partial_bytes);
+  for (int b = 0; b < 2; ++b) {
+    unsigned char* buffer = base + kTpHeaderBytes + (size_t)b * (world + 1) * slot_bytes;
+    view.inbox[r][b] = reinterpret_cast<float*>(buffer);
+    view.totals[r][b] = reinterpret_cast<float*>(buffer + (size_t)world * slot_bytes);
+  }
 }
-// hidden[0, count) += sum over ranks of partial[rank][buffer][0, count); count is a multiple of 4. sum.splits > 0: this
-// rank's partial is first added up from split-K partials of a [count / columns, columns] projection result.
+// hidden[0, count) += sum over ranks of their partial sums; count is a multiple of 4. This rank's partial sum is
+// `partial`, or with sum.splits > 0 the sum of the split-K partials of a [count / columns, columns] projection result.
 cudaError_t launch_tp_allreduce(const PeerView& view, int buffer, float* hidden, size_t count, int columns, const DeferredSum& sum,
-                                bool two_shot, uint32_t* counters, long long wait_cycles, DeviceStatus* status, cudaStream_t stream);
+                                const float* partial, bool two_shot, uint32_t* counters, long long wait_cycles, int sm_count,
+                                DeviceStatus* status, cudaStream_t stream);
 // tokens[b] = the token of the largest logit over all ranks' picks (lowest token on ties), b < batch <= kTpMaxPicks.
 cudaError_t launch_tp_pick(const PeerView& view, int batch, uint32_t* tokens, uint32_t* counters, long long wait_cycles,
                            DeviceStatus* status, cudaStream_t stream);

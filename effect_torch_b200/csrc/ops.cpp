@@ -399,9 +399,8 @@ etc_status etc_argmax_into(etc_runtime* rt, const float* d_logits, int64_t rows,
   return ETC_OK;
 }
 
-size_t etc_peer_region_bytes(int64_t capacity) {
-  const size_t partial = ((size_t)std::max<int64_t>(capacity, 0) * sizeof(float) + 255) & ~(size_t)255;
-  return kTpHeaderBytes + 2 * partial;
+size_t etc_peer_region_bytes(int64_t capacity, int world) {
+  return tp_region_bytes((size_t)std::max<int64_t>(capacity, 0), std::min(std::max(world, 1), kMaxTpRanks));
 }
 
 etc_status etc_peer_allreduce_into(etc_runtime* rt, int rank, int world, void* const* regions, int64_t capacity, int buffer,
@@ -410,23 +409,20 @@ etc_status etc_peer_allreduce_into(etc_runtime* rt, int rank, int world, void* c
   if (world < 1 || world > kMaxTpRanks || rank < 0 || rank >= world)
     return fail(ETC_INVALID_ARGUMENT, "peer all-reduce: rank " + std::to_string(rank) + " of " + std::to_string(world) + " is out of range (at most " +
                                           std::to_string(kMaxTpRanks) + " ranks)");
-  if (!regions || !d_hidden || buffer < 0 || buffer > 1 || count < 0 || count % 4 != 0 || count > capacity)
+  if (!regions || !d_hidden || !d_partial || buffer < 0 || buffer > 1 || count < 0 || count % 4 != 0 || count > capacity)
     return fail(ETC_INVALID_ARGUMENT, "peer all-reduce: count must be a multiple of 4 within the regions' capacity, buffer 0 or 1");
-  const size_t partial_bytes = ((size_t)capacity * sizeof(float) + 255) & ~(size_t)255;
   PeerView view{};
   view.rank = rank;
   view.world = world;
   for (int r = 0; r < world; ++r) {
     if (!regions[r]) return fail(ETC_INVALID_ARGUMENT, "peer all-reduce: region " + std::to_string(r) + " is null");
-    tp_view_bind(view, r, static_cast<unsigned char*>(regions[r]), partial_bytes);
+    tp_view_bind(view, r, static_cast<unsigned char*>(regions[r]), tp_slot_bytes((size_t)capacity), world);
   }
   if (count == 0) return ETC_OK;
-  if (d_partial)
-    ETC_CUDA(cudaMemcpyAsync(view.partial[rank][buffer], d_partial, (size_t)count * sizeof(float), cudaMemcpyDeviceToDevice, rt->stream));
   unsigned char* own = static_cast<unsigned char*>(regions[rank]);
-  ETC_CUDA(launch_tp_allreduce(view, buffer, d_hidden, (size_t)count, (int)count, DeferredSum(), two_shot != 0,
+  ETC_CUDA(launch_tp_allreduce(view, buffer, d_hidden, (size_t)count, (int)count, DeferredSum(), d_partial, two_shot != 0,
                                reinterpret_cast<uint32_t*>(own + kTpCounterOffset), wait_cycles > 0 ? wait_cycles : kTpWaitCycles,
-                               rt->d_status, rt->stream));
+                               rt->sm_count, rt->d_status, rt->stream));
   rt->launches++;
   return ETC_OK;
 }

@@ -1,26 +1,29 @@
-// All-reduce over peer memory for the tensor-parallel decoder: hidden += sum over ranks of partial[rank], and the exchange
-// of every rank's best logit for a vocabulary-parallel head.
+// All-reduce over peer memory for the tensor-parallel decoder: hidden += sum over ranks of every rank's partial sum, and
+// the exchange of every rank's best logit for a vocabulary-parallel head.
 //
-// Every rank owns one exported region (layout: tp_region_* in kernels.h): three flag arrays (one 32-bit epoch per peer,
-// written BY that peer), a table of (best logit, token) pairs, and two partial-sum buffers that the o and down
-// projections alternate between. Ranks read their peers' buffers with plain loads over NVLink; nothing here uses
-// multicast. Two buffers suffice: a rank can only reach the second next projection after every peer entered the next
-// all-reduce, i.e. finished reading in this one.
+// Every rank owns one exported region (layout: kTp* in kernels.h): three flag arrays (one 32-bit epoch per peer,
+// written BY that peer), a table of (best logit, token) pairs, and two exchange buffers that the o and down projections
+// alternate between, each an inbox with one slot per sender and a table of totals. Data moves by plain STORES into the
+// peers' regions over NVLink (posted writes: no round trip is waited for), followed by a system-wide fence and a release
+// store of the epoch into the peer's flag array; all reads are local. Nothing here uses multicast.
 //
-//   one shot (2 ranks, or small messages): publish "my partial of epoch e is complete" into every peer's flags, wait
-//     until all peers have published e, then every CTA adds the partial sums of all ranks in rank order on top of its
-//     local hidden state: (world - 1) x message bytes cross NVLink into every rank.
-//   two shot (4-8 ranks): rank r first reduces slice r of the message over all ranks (in rank order) and writes the
-//     total back into slice r of its own buffer (reduce-scatter); after a second flag exchange every rank adds every
-//     slice's total, read from its owner, onto its hidden state (all-gather): 2 (world - 1) / world x message bytes.
-//   Both give bit-identical hidden states on all ranks (the same additions in the same order).
+//   one shot (2 ranks, or forced): every rank stores its whole partial sum into slot `rank` of every rank's inbox; after
+//     one flag exchange every rank adds the slots in rank order onto its hidden state. (world - 1) x message bytes leave
+//     every rank.
+//   two shot (4-8 ranks): rank r stores slice q of its partial sum into slot r of rank q's inbox (reduce-scatter); after
+//     the first flag exchange rank q adds the slots of its slice in rank order, adds the total onto its own hidden state
+//     and stores it into every peer's table of totals (all-gather); after the second exchange every rank adds the other
+//     slices' totals onto its hidden state. 2 (world - 1) / world x message bytes leave every rank.
+//   Both give bit-identical hidden states on all ranks: the sum over ranks first, in rank order, then onto hidden.
 //
-// With `sum.splits > 0` the kernel first adds up the row-parallel projection's split-K partials into this rank's buffer,
-// so that projection needs no sum launch of its own and its result never passes through the hidden state.
+// The partial sum is either read from a buffer or, with `sum.splits > 0`, added up from the row-parallel projection's
+// split-K partials on the way out, so that projection needs no sum launch of its own. Two buffers suffice: a rank can
+// only store for the second next all-reduce after every peer entered the next one, i.e. finished reading this one.
 //
-// CTAs of one launch wait for one another at the phase boundaries; the grid is at most 64 CTAs of 256 threads without
-// shared memory, launched after the previous kernel of the stream has ended, so all of them are resident. Every wait is
-// bounded by `wait_cycles`: on expiry the kernel records status code 4 and returns.
+// CTAs of one launch wait for one another at the phase boundaries (a slice's slots are filled by all CTAs); the grid is
+// at most one CTA of 256 threads per SM without shared memory, launched after the previous kernel of the stream has
+// ended, so all of them are resident. Every wait is bounded by `wait_cycles`: on expiry the kernel records status code 4
+// and returns.
 #include <algorithm>
 
 #include "kernels.h"
@@ -42,10 +45,14 @@ __device__ __forceinline__ uint32_t load_acquire_gpu(const uint32_t* p) {
   asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ float4 load_peer4(const float4* p) {
+// data a peer stored into this rank's region: never from a stale L1 line
+__device__ __forceinline__ float4 load_inbox4(const float4* p) {
   float4 v;
   asm volatile("ld.volatile.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
   return v;
+}
+__device__ __forceinline__ void store_peer4(float4* p, const float4& v) {
+  asm volatile("st.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
 
 // Thread 0 of a CTA: waits until every peer has published `epoch` into flag array `which` of this rank's region.
@@ -63,8 +70,8 @@ __device__ void publish_to_peers(const PeerView& pv, int which, uint32_t epoch) 
   for (int r = 0; r < pv.world; ++r)
     if (r != pv.rank) store_release_sys(pv.flags[r] + which * kTpFlagStride + pv.rank, epoch);
 }
-// Thread 0 of a CTA: arrives at phase counter `bar`; the last CTA of the grid to arrive publishes flag array `which`.
-// The CTA's earlier global writes (made visible by the __syncthreads before this call) are fenced system-wide first.
+// Thread 0 of a CTA, after a __syncthreads that follows the CTA's stores: fences them system-wide and arrives at phase
+// counter `bar`; the last CTA of the grid to arrive publishes flag array `which` to the peers.
 __device__ void arrive_and_publish(const PeerView& pv, uint32_t* bar, int which, uint32_t epoch) {
   __threadfence_system();
   if (atomicAdd(bar, 1u) == gridDim.x - 1) {
@@ -80,15 +87,14 @@ __device__ bool wait_for_grid(const uint32_t* bar, long long start, long long wa
   return true;
 }
 
-// ctr: [0] epoch of the last completed all-reduce, [1] CTAs done, [2] / [3] phase arrivals
+// ctr: [0] epoch of the last completed all-reduce, [1] CTAs done, [2] / [3] phase arrivals, [4] epoch of the last pick exchange
 template <bool TWO_SHOT>
 __global__ void __launch_bounds__(256) tp_allreduce_kernel(PeerView pv, int buffer, float* __restrict__ hidden, size_t count4,
-                                                           DeferredSum sum, int columns, uint32_t* ctr, long long wait_cycles,
-                                                           unsigned long long* status) {
+                                                           DeferredSum sum, int columns, const float* __restrict__ partial,
+                                                           uint32_t* ctr, long long wait_cycles, unsigned long long* status) {
   __shared__ uint32_t epoch_s;
   __shared__ int ok_s;
   const size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x, stride = (size_t)gridDim.x * blockDim.x;
-  float4* mine = reinterpret_cast<float4*>(pv.partial[pv.rank][buffer]);
   const long long start = clock64();
   if (threadIdx.x == 0) {
     epoch_s = *reinterpret_cast<volatile uint32_t*>(ctr) + 1;
@@ -96,73 +102,75 @@ __global__ void __launch_bounds__(256) tp_allreduce_kernel(PeerView pv, int buff
   }
   __syncthreads();
   const uint32_t epoch = epoch_s;
-  // ---- phase 0: this rank's partial sum is complete in its buffer, tell the peers
-  if (sum.splits > 0) {
-    const int columns4 = columns / 4;
-    for (size_t i = tid; i < count4; i += stride) {
+  const int world = pv.world, rank = pv.rank;
+  const size_t slice = TWO_SHOT ? (count4 + world - 1) / world : count4;  // float4 elements per inbox slot
+  float4* h4 = reinterpret_cast<float4*>(hidden);
+  const int columns4 = columns / 4;
+  // ---- phase A: this rank's partial sum goes out, slice q (two shot) or all of it (one shot) into slot `rank` of rank q
+  for (size_t i = tid; i < count4; i += stride) {
+    float4 val;
+    if (sum.splits > 0) {
       const size_t v = i / columns4, c4 = i - v * columns4;
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      val = make_float4(0.f, 0.f, 0.f, 0.f);
       for (int s = 0; s < sum.splits; ++s) {
         const float4 p = *reinterpret_cast<const float4*>(sum.partials + ((size_t)s * sum.vpad + v) * sum.rows_padded + 4 * c4);
+        val.x += p.x; val.y += p.y; val.z += p.z; val.w += p.w;
+      }
+    } else {
+      val = reinterpret_cast<const float4*>(partial)[i];
+    }
+    if (TWO_SHOT) {
+      const int q = (int)(i / slice);
+      store_peer4(reinterpret_cast<float4*>(pv.inbox[q][buffer]) + (size_t)rank * slice + (i - (size_t)q * slice), val);
+    } else {
+      for (int q = 0; q < world; ++q) store_peer4(reinterpret_cast<float4*>(pv.inbox[q][buffer]) + (size_t)rank * slice + i, val);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    arrive_and_publish(pv, ctr + 2, 0, epoch);
+    // the slots of this rank's inbox are filled by the peers and by every CTA of this grid
+    if (!wait_for_grid(ctr + 2, start, wait_cycles) || !wait_for_peers(pv, 0, epoch, start, wait_cycles)) ok_s = 0;
+  }
+  __syncthreads();
+  const float4* inbox = reinterpret_cast<const float4*>(pv.inbox[rank][buffer]);
+  if (!TWO_SHOT) {
+    for (size_t i = tid; i < count4 && ok_s; i += stride) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int r = 0; r < world; ++r) {
+        const float4 p = load_inbox4(inbox + (size_t)r * slice + i);
         acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
       }
-      mine[i] = acc;
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      arrive_and_publish(pv, ctr + 2, 0, epoch);
-      if (TWO_SHOT && !wait_for_grid(ctr + 2, start, wait_cycles)) ok_s = 0;  // slice `rank` below spans other CTAs' sums
-    }
-  } else if (threadIdx.x == 0 && blockIdx.x == 0) {
-    __threadfence_system();  // the projection that filled this rank's buffer finished before this kernel started
-    publish_to_peers(pv, 0, epoch);
-  }
-  if (threadIdx.x == 0 && ok_s && !wait_for_peers(pv, 0, epoch, start, wait_cycles)) ok_s = 0;
-  __syncthreads();
-  float4* h4 = reinterpret_cast<float4*>(hidden);
-  if (!TWO_SHOT) {
-    if (ok_s) {
-      if (sum.splits > 0 && threadIdx.x == 0 && !wait_for_grid(ctr + 2, start, wait_cycles)) ok_s = 0;
-      __syncthreads();
-      for (size_t i = tid; i < count4 && ok_s; i += stride) {
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);  // the ranks' sum first, then onto hidden: what the two-shot form computes
-        for (int r = 0; r < pv.world; ++r) {
-          const float4 p = load_peer4(reinterpret_cast<const float4*>(pv.partial[r][buffer]) + i);
-          acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
-        }
-        const float4 h = h4[i];
-        h4[i] = make_float4(h.x + acc.x, h.y + acc.y, h.z + acc.z, h.w + acc.w);
-      }
+      const float4 h = h4[i];
+      h4[i] = make_float4(h.x + acc.x, h.y + acc.y, h.z + acc.z, h.w + acc.w);
     }
   } else {
-    const size_t slice = (count4 + pv.world - 1) / pv.world;
-    if (ok_s) {
-      // ---- phase 1: total of this rank's slice over all ranks, written back into this rank's buffer
-      const size_t lo = slice * pv.rank < count4 ? slice * pv.rank : count4, hi = lo + slice < count4 ? lo + slice : count4;
-      for (size_t i = lo + tid; i < hi; i += stride) {
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int r = 0; r < pv.world; ++r) {
-          const float4 p = load_peer4(reinterpret_cast<const float4*>(pv.partial[r][buffer]) + i);
-          acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
-        }
-        mine[i] = acc;
+    const size_t lo = slice * rank < count4 ? slice * rank : count4, hi = lo + slice < count4 ? lo + slice : count4;
+    // ---- phase B: total of this rank's slice, onto its own hidden state and out to every peer's table of totals
+    for (size_t j = tid; lo + j < hi && ok_s; j += stride) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int r = 0; r < world; ++r) {
+        const float4 p = load_inbox4(inbox + (size_t)r * slice + j);
+        acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
       }
+      const float4 h = h4[lo + j];
+      h4[lo + j] = make_float4(h.x + acc.x, h.y + acc.y, h.z + acc.z, h.w + acc.w);
+      for (int q = 0; q < world; ++q)
+        if (q != rank) store_peer4(reinterpret_cast<float4*>(pv.totals[q][buffer]) + lo + j, acc);
     }
     __syncthreads();
     if (threadIdx.x == 0 && ok_s) {
       arrive_and_publish(pv, ctr + 3, 1, epoch);
-      if (!wait_for_grid(ctr + 3, start, wait_cycles) || !wait_for_peers(pv, 1, epoch, start, wait_cycles)) ok_s = 0;
+      if (!wait_for_peers(pv, 1, epoch, start, wait_cycles)) ok_s = 0;
     }
     __syncthreads();
-    if (ok_s) {
-      // ---- phase 2: every slice's total, read from its owner, onto the hidden state
-      for (size_t i = tid; i < count4; i += stride) {
-        const int owner = (int)(i / slice);
-        const float4 p = load_peer4(reinterpret_cast<const float4*>(pv.partial[owner][buffer]) + i);
-        float4 acc = h4[i];
-        acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
-        h4[i] = acc;
-      }
+    // ---- phase C: the other slices' totals onto the hidden state
+    const float4* totals = reinterpret_cast<const float4*>(pv.totals[rank][buffer]);
+    for (size_t i = tid; i < count4 && ok_s; i += stride) {
+      if (i >= lo && i < hi) continue;
+      const float4 p = load_inbox4(totals + i);
+      const float4 h = h4[i];
+      h4[i] = make_float4(h.x + p.x, h.y + p.y, h.z + p.z, h.w + p.w);
     }
   }
   __syncthreads();
@@ -217,13 +225,15 @@ __global__ void __launch_bounds__(256) tp_pick_kernel(PeerView pv, int batch, ui
 }  // namespace
 
 cudaError_t launch_tp_allreduce(const PeerView& view, int buffer, float* hidden, size_t count, int columns, const DeferredSum& sum,
-                                bool two_shot, uint32_t* counters, long long wait_cycles, DeviceStatus* status, cudaStream_t stream) {
+                                const float* partial, bool two_shot, uint32_t* counters, long long wait_cycles, int sm_count,
+                                DeviceStatus* status, cudaStream_t stream) {
   const size_t count4 = count / 4;
-  const unsigned grid = (unsigned)std::min<size_t>(64, std::max<size_t>(1, (count4 + 255) / 256));
+  // every thread has a few 16-byte stores in flight; no more CTAs than SMs, so that all of them are resident
+  const unsigned grid = (unsigned)std::min<size_t>((size_t)std::max(1, sm_count), std::max<size_t>(1, (count4 + 1023) / 1024));
   if (two_shot)
-    tp_allreduce_kernel<true><<<grid, 256, 0, stream>>>(view, buffer, hidden, count4, sum, columns, counters, wait_cycles, &status->code);
+    tp_allreduce_kernel<true><<<grid, 256, 0, stream>>>(view, buffer, hidden, count4, sum, columns, partial, counters, wait_cycles, &status->code);
   else
-    tp_allreduce_kernel<false><<<grid, 256, 0, stream>>>(view, buffer, hidden, count4, sum, columns, counters, wait_cycles, &status->code);
+    tp_allreduce_kernel<false><<<grid, 256, 0, stream>>>(view, buffer, hidden, count4, sum, columns, partial, counters, wait_cycles, &status->code);
   return cudaGetLastError();
 }
 

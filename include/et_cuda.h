@@ -356,9 +356,9 @@ ETC_API etc_status etc_gguf_load_tensor_device(etc_runtime* rt, const etc_gguf* 
 ETC_API etc_status etc_tp_unique_id(uint8_t* out_id_128_bytes);
 ETC_API etc_status etc_decoder_set_tensor_parallel(etc_decoder* dec, int rank, int world, const uint8_t* id_128_bytes);
 /* Optional, after etc_decoder_set_tensor_parallel and etc_decoder_finalize: replace the NCCL all-reduce by the
- * library's kernel over peer memory (CUDA IPC, plain peer loads over NVLink, 2..8 ranks on one node): one shot at
- * 2 ranks (every rank adds all ranks' partial sums), reduce-scatter + all-gather from 4 ranks on; the row-parallel
- * projection's split-K partials are summed inside the same kernel. Every rank exports a
+ * library's kernel over peer memory (CUDA IPC, plain stores into the peers' regions over NVLink, 2..8 ranks on one
+ * node): one shot at 2 ranks (every rank receives all ranks' partial sums), reduce-scatter + all-gather from 4 ranks
+ * on; the row-parallel projection's split-K partials are summed inside the same kernel. Every rank exports a
  * 64-byte handle of its exchange region, the host gathers the handles of all ranks into a table [world][64] (own slot
  * ignored) and every rank imports it. The kernel's wait for its peers is bounded: a rank that never arrives turns
  * into ETC_EXECUTION at the next synchronising call, not into a hang.
@@ -369,6 +369,16 @@ ETC_API etc_status etc_decoder_set_tensor_parallel(etc_decoder* dec, int rank, i
  * barrier: a peer may still be reading this rank's exchange region until its own step has been synchronised. */
 ETC_API etc_status etc_decoder_tp_peer_export(etc_decoder* dec, uint8_t* out_handle_64_bytes);
 ETC_API etc_status etc_decoder_tp_peer_import(etc_decoder* dec, const uint8_t* handles_world_x_64_bytes);
+/* The same without CUDA IPC, for hosts that map the peers' regions themselves (a virtual-memory mapping, or one process
+ * that drives several devices): etc_decoder_tp_region returns this rank's region (allocated on first use, zeroed) and
+ * its size; etc_decoder_tp_peer_attach takes every rank's region as a device pointer valid in this process (own slot
+ * ignored). With these, etc_decoder_set_tensor_parallel may be called with a null id: no NCCL communicator is made and
+ * the decoder steps only once the regions are attached. */
+ETC_API etc_status etc_decoder_tp_region(etc_decoder* dec, void** out_region, size_t* out_bytes);
+ETC_API etc_status etc_decoder_tp_peer_attach(etc_decoder* dec, void* const* regions_world);
+/* Bound of every wait for a peer inside the decoder's kernels, in SM clock cycles (<= 0: the default, about a second).
+ * A step whose wait runs out returns ETC_EXECUTION and is rolled back like any other failed step. */
+ETC_API etc_status etc_decoder_set_wait_limit(etc_decoder* dec, int64_t cycles);
 /* Vocabulary-parallel head, before any weight is bound: the decoder's config.vocab is the number of head rows this rank
  * holds, rows [first_row, first_row + config.vocab) of a head with `vocab_global` rows; the token embedding keeps
  * vocab_global rows on every rank. Greedy steps then exchange every rank's (best logit, token) pair over the peer
@@ -376,13 +386,14 @@ ETC_API etc_status etc_decoder_tp_peer_import(etc_decoder* dec, const uint8_t* h
  * an ascending scan with a strict comparison finds on one device (crates/runtime/src/sampling.rs:88-105).
  * etc_decoder_execute returns this rank's [active, config.vocab] slice of the logits. */
 ETC_API etc_status etc_decoder_set_head_shard(etc_decoder* dec, int64_t vocab_global, int64_t first_row);
-/* The peer-memory all-reduce as an operator of its own. A region is etc_peer_region_bytes(capacity) bytes of device
- * memory, zeroed once before its first use; regions[r] is rank r's region as mapped in this process (own rank: local
- * memory). hidden[0, count) += sum over ranks of the partial sums in buffer `buffer` (0 or 1) of every region; with
- * d_partial the call first copies this rank's partial sum into its region. count is a multiple of 4, at most
+/* The peer-memory all-reduce as an operator of its own. A region is etc_peer_region_bytes(capacity, world) bytes of
+ * device memory, zeroed once before its first use; regions[r] is rank r's region as mapped in this process (own rank:
+ * local memory). hidden[0, count) += sum over ranks of their partial sums (d_partial is this rank's): every rank stores
+ * its partial sum (two_shot: slice q of it to rank q) into the peers' regions, buffer `buffer` (0 or 1, alternating
+ * between consecutive calls), and adds up what the peers stored into its own. count is a multiple of 4, at most
  * `capacity`. wait_cycles bounds the wait for the peers in SM clock cycles (<= 0: about one second); when it runs out
  * the launch gives up and the next synchronising call returns ETC_EXECUTION, the runtime stays usable. */
-ETC_API size_t etc_peer_region_bytes(int64_t capacity);
+ETC_API size_t etc_peer_region_bytes(int64_t capacity, int world);
 ETC_API etc_status etc_peer_allreduce_into(etc_runtime* rt, int rank, int world, void* const* regions, int64_t capacity,
                                            int buffer, const float* d_partial, float* d_hidden, int64_t count, int two_shot,
                                            int64_t wait_cycles);
