@@ -185,6 +185,12 @@ class Runtime:
                                      C.byref(out)))
         return out.value
 
+    def sample_rows_into(self, logits, rows, vocab, tokens, temperature=1.0, top_k=None, top_p=1.0, seed=0, counter=0, seeds=None,
+                         counters=None):
+        """One token per row into the device tensor `tokens` (uint32); per-row (seed, counter) as device u64 tensors, or the scalars."""
+        _check(self.L.etc_sample_rows_into(self.h, _ptr(logits), rows, vocab, temperature, 0 if top_k is None else top_k, top_p, seed,
+                                           counter, _ptr(seeds), _ptr(counters), _ptr(tokens)))
+
     def kv_attention_into(self, pool, layer, seqs, batch, active, advance, q, k, v, q_heads, tokens, scale, op_window=None,
                           pool_window=None, out=None):
         arr = (C.c_void_p * max(len(seqs), 1))(*[s.h for s in seqs])

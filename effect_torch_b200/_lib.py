@@ -70,6 +70,7 @@ SIGNATURES = {
     "etc_add_into": (None, [P, P, P, I64, P]),
     "etc_argmax_into": (None, [P, P, I64, I64, P]),
     "etc_sample_row": (None, [P, P, I64, D, I64, D, U64, U64, P]),
+    "etc_sample_rows_into": (None, [P, P, I64, I64, D, I64, D, U64, U64, P, P, P]),
     "etc_pool_create": (None, [P, I, I, I, I, I, I, P]),
     "etc_pool_destroy": (None, [P]),
     "etc_pool_stats": (None, [P, P, P, P]),

@@ -61,6 +61,8 @@ struct etc_runtime {
   cudaStream_t stream = nullptr;
   etc::DeviceStatus* d_status = nullptr;
   etc::DeviceStatus* h_status = nullptr;  // pinned
+  uint32_t* d_sampled = nullptr;          // one token: etc_sample_row's device output and its pinned copy
+  uint32_t* h_sampled = nullptr;
   void* d_workspace = nullptr;
   size_t workspace_bytes = 0;
   std::atomic<uint64_t> launches{0};

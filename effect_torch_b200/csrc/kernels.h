@@ -155,6 +155,11 @@ cudaError_t launch_add(const float* a, const float* b, int64_t n, float* out, cu
 cudaError_t launch_argmax(const float* logits, int64_t rows, int64_t vocab, uint32_t* tokens, DeviceStatus* status,
                           cudaStream_t stream,
                           uint2* picks = nullptr, uint32_t index_base = 0);
+// One token per logits row by temperature / top-k / top-p sampling with the splitmix64 draw (sampling.cu); temperature
+// must be positive here (zero is the argmax kernel's case). seeds / counters: optional per-row device arrays.
+cudaError_t launch_sample_rows(const float* logits, int64_t rows, int64_t vocab, double temperature, int64_t top_k, double top_p,
+                               uint64_t seed, uint64_t counter, const uint64_t* seeds, const uint64_t* counters, uint32_t* tokens,
+                               DeviceStatus* status, cudaStream_t stream);
 cudaError_t launch_embedding_f32(const void* indexes, int index_is_i64, int64_t count, const float* table, int64_t rows,
                                  int64_t columns, float* out, DeviceStatus* status, cudaStream_t stream);
 // [B,T,H*D] <-> [B,H,T,D] (the reshape/transpose pairs around attention)

@@ -28,87 +28,16 @@ static etc_status check_codec_geometry(const char* operation, int codec, int64_t
   return ETC_OK;
 }
 
-// sample_logits on the host (crates/runtime/src/sampling.rs:80-206) over a row already read back.
-etc_status sample_logits_host(const float* logits, int64_t length, double temperature, int64_t top_k, double top_p,
-                              uint64_t seed, uint64_t counter, uint32_t* out_token) {
-  if (length == 0) return fail(ETC_EXECUTION, "sample: logits must be non-empty");
+// The argument checks of sample_logits (crates/runtime/src/sampling.rs:44-78), same messages.
+etc_status validate_sampling(int64_t length, double temperature, int64_t top_k, double top_p) {
+  if (length <= 0) return fail(ETC_EXECUTION, "sample: logits must be non-empty");
   if (length > 1048576) return fail(ETC_EXECUTION, "sample: vocabulary " + std::to_string(length) + " exceeds limit 1048576");
   if (!std::isfinite(temperature) || temperature < 0.0)
     return fail(ETC_EXECUTION, "sample: temperature must be finite and non-negative, got " + std::to_string(temperature));
   if (!std::isfinite(top_p) || top_p <= 0.0 || top_p > 1.0)
     return fail(ETC_EXECUTION, "sample: topP must be finite and in (0, 1], got " + std::to_string(top_p));
-  if (top_k > 0 && top_k > length)
+  if (top_k < 0 || top_k > length)
     return fail(ETC_EXECUTION, "sample: topK must be in [1, " + std::to_string(length) + "], got " + std::to_string(top_k));
-  auto non_finite = [&](int64_t t) { return fail(ETC_EXECUTION, "sample: logit " + std::to_string(t) + " is not finite"); };
-  auto random_unit = [&]() {
-    uint64_t value = seed ^ (counter * 0x9e3779b97f4a7c15ull);
-    value += 0x9e3779b97f4a7c15ull;
-    value = (value ^ (value >> 30)) * 0xbf58476d1ce4e5b9ull;
-    value = (value ^ (value >> 27)) * 0x94d049bb133111ebull;
-    value ^= value >> 31;
-    return (double)(value >> 11) * (1.0 / 9007199254740992.0);
-  };
-  if (temperature == 0.0) {
-    int64_t selected = 0;
-    double best = -INFINITY;
-    for (int64_t t = 0; t < length; ++t) {
-      const double v = (double)logits[t];
-      if (!std::isfinite(v)) return non_finite(t);
-      if (v > best) { best = v; selected = t; }
-    }
-    *out_token = (uint32_t)selected;
-    return ETC_OK;
-  }
-  const bool has_top_k = top_k > 0 && top_k < length;
-  if (!has_top_k && top_p >= 1.0) {
-    double max = -INFINITY;
-    for (int64_t t = 0; t < length; ++t) {
-      const double v = (double)logits[t];
-      if (!std::isfinite(v)) return non_finite(t);
-      max = std::fmax(max, v);
-    }
-    double total = 0.0;
-    for (int64_t t = 0; t < length; ++t) total += std::exp(((double)logits[t] - max) / temperature);
-    double draw = random_unit() * total;
-    for (int64_t t = 0; t < length; ++t) {
-      draw -= std::exp(((double)logits[t] - max) / temperature);
-      if (draw < 0.0) { *out_token = (uint32_t)t; return ETC_OK; }
-    }
-    *out_token = (uint32_t)(length - 1);
-    return ETC_OK;
-  }
-  struct Candidate { int64_t token; double value; };
-  std::vector<Candidate> candidates((size_t)length);
-  for (int64_t t = 0; t < length; ++t) {
-    const double v = (double)logits[t];
-    if (!std::isfinite(v)) return non_finite(t);
-    candidates[(size_t)t] = {t, v};
-  }
-  std::sort(candidates.begin(), candidates.end(), [](const Candidate& l, const Candidate& r) {
-    return l.value != r.value ? l.value > r.value : l.token < r.token;
-  });
-  if (has_top_k) candidates.resize((size_t)top_k);
-  const double max = candidates[0].value;
-  double total = 0.0;
-  for (auto& c : candidates) {
-    c.value = std::exp((c.value - max) / temperature);
-    total += c.value;
-  }
-  size_t retained = candidates.size();
-  if (top_p < 1.0) {
-    const double threshold = top_p * total;
-    double cumulative = 0.0;
-    for (size_t i = 0; i < candidates.size(); ++i) {
-      cumulative += candidates[i].value;
-      if (cumulative >= threshold) { retained = i + 1; total = cumulative; break; }
-    }
-  }
-  double draw = random_unit() * total;
-  for (size_t i = 0; i < retained; ++i) {
-    draw -= candidates[i].value;
-    if (draw < 0.0) { *out_token = (uint32_t)candidates[i].token; return ETC_OK; }
-  }
-  *out_token = (uint32_t)candidates[retained - 1].token;
   return ETC_OK;
 }
 
@@ -427,15 +356,31 @@ etc_status etc_peer_allreduce_into(etc_runtime* rt, int rank, int world, void* c
   return ETC_OK;
 }
 
+etc_status etc_sample_rows_into(etc_runtime* rt, const float* d_logits, int64_t rows, int64_t vocab, double temperature,
+                                int64_t top_k, double top_p, uint64_t seed, uint64_t counter, const uint64_t* d_seeds,
+                                const uint64_t* d_counters, uint32_t* d_tokens) {
+  ETC_TRY(activate(rt));
+  ETC_TRY(validate_sampling(vocab, temperature, top_k, top_p));
+  if (rows < 0 || !d_logits || !d_tokens) return fail(ETC_INVALID_ARGUMENT, "sample: logits and tokens must be device buffers");
+  if (temperature == 0.0)
+    ETC_CUDA(launch_argmax(d_logits, rows, vocab, d_tokens, rt->d_status, rt->stream));
+  else
+    ETC_CUDA(launch_sample_rows(d_logits, rows, vocab, temperature, top_k, top_p, seed, counter, d_seeds, d_counters, d_tokens,
+                                rt->d_status, rt->stream));
+  rt->launches++;
+  return ETC_OK;
+}
+
 etc_status etc_sample_row(etc_runtime* rt, const float* d_logits, int64_t vocab, double temperature, int64_t top_k,
                           double top_p, uint64_t seed, uint64_t counter, uint32_t* out_token) {
   ETC_TRY(activate(rt));
-  if (vocab <= 0) return fail(ETC_EXECUTION, "sample: logits must be non-empty");
-  std::vector<float> row((size_t)vocab);
-  cudaError_t e = cudaMemcpyAsync(row.data(), d_logits, (size_t)vocab * sizeof(float), cudaMemcpyDeviceToHost, rt->stream);
-  if (e == cudaSuccess) e = cudaStreamSynchronize(rt->stream);
+  if (!out_token) return fail(ETC_INVALID_ARGUMENT, "sample: the token output is null");
+  ETC_TRY(etc_sample_rows_into(rt, d_logits, 1, vocab, temperature, top_k, top_p, seed, counter, nullptr, nullptr, rt->d_sampled));
+  cudaError_t e = cudaMemcpyAsync(rt->h_sampled, rt->d_sampled, sizeof(uint32_t), cudaMemcpyDeviceToHost, rt->stream);
   if (e != cudaSuccess) return fail(ETC_TRANSFER, std::string("readback failed: ") + cudaGetErrorString(e));
-  return sample_logits_host(row.data(), vocab, temperature, top_k, top_p, seed, counter, out_token);
+  ETC_TRY(rt->check_status());  // synchronises; a non-finite logit surfaces here
+  *out_token = *rt->h_sampled;
+  return ETC_OK;
 }
 
 }  // extern "C"

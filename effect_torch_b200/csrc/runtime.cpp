@@ -184,6 +184,8 @@ etc_status etc_runtime_create(int device_ordinal, etc_runtime** out) {
   if (e == cudaSuccess) e = cudaMalloc((void**)&rt->d_status, sizeof(DeviceStatus));
   if (e == cudaSuccess) e = cudaMemset(rt->d_status, 0, sizeof(DeviceStatus));
   if (e == cudaSuccess) e = cudaMallocHost((void**)&rt->h_status, sizeof(DeviceStatus));
+  if (e == cudaSuccess) e = cudaMalloc((void**)&rt->d_sampled, sizeof(uint32_t));
+  if (e == cudaSuccess) e = cudaMallocHost((void**)&rt->h_sampled, sizeof(uint32_t));
   // reserve the fixed scratch array of the allocation-free linear now, not inside its first call
   if (e == cudaSuccess) e = static_scratch_prepare(device_ordinal);
   if (e != cudaSuccess) {
@@ -222,6 +224,8 @@ etc_status etc_runtime_destroy(etc_runtime* rt) {
   rt->allocations.clear();
   cudaFree(rt->d_status);
   cudaFreeHost(rt->h_status);
+  cudaFree(rt->d_sampled);
+  cudaFreeHost(rt->h_sampled);
   cudaStreamDestroy(rt->stream);
   rt->magic = 0;
   delete rt;

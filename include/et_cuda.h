@@ -227,8 +227,18 @@ ETC_API etc_status etc_add_into(etc_runtime* rt, const float* d_a, const float* 
  * "sample: logit {i} is not finite". d_tokens u32 [rows]. */
 ETC_API etc_status etc_argmax_into(etc_runtime* rt, const float* d_logits, int64_t rows, int64_t vocab,
                                    uint32_t* d_tokens);
-/* sample_logits (sampling.rs:80-206) for one row already on the host side of the boundary: reads the
- * row back and draws with the reference's splitmix64 stream (temperature 0 = greedy; top_k <= 0 off). */
+/* sample_logits (crates/runtime/src/sampling.rs:80-206) on the device, one CTA per logits row: temperature 0 = greedy;
+ * otherwise candidates in (value descending, token ascending) order, the first top_k of them (0 = all), weights
+ * exp((value - max) / temperature), the smallest prefix holding top_p of the weight, and the candidate at which the
+ * splitmix64 unit of (seed, counter) x total is used up; without top-k and top-p the walk is in token order. Row r draws
+ * with (d_seeds[r], d_counters[r]) when those device arrays are given, else with the scalars. Asynchronous; argument
+ * errors carry the reference's messages, a non-finite logit surfaces at the next synchronising call. The sums are f64 as
+ * in the reference but associated differently, so a token can differ only when the draw (or the top-p threshold) lies
+ * within about vocab x 2^-52 (relative) of a candidate's boundary. */
+ETC_API etc_status etc_sample_rows_into(etc_runtime* rt, const float* d_logits, int64_t rows, int64_t vocab, double temperature,
+                                        int64_t top_k, double top_p, uint64_t seed, uint64_t counter, const uint64_t* d_seeds,
+                                        const uint64_t* d_counters, uint32_t* d_tokens);
+/* One row, synchronous, token returned to the host. */
 ETC_API etc_status etc_sample_row(etc_runtime* rt, const float* d_logits, int64_t vocab, double temperature,
                                   int64_t top_k, double top_p, uint64_t seed, uint64_t counter, uint32_t* out_token);
 

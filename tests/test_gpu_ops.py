@@ -97,3 +97,44 @@ def test_sample_row_replays_the_reference_stream():
         assert rt.sample_row(d, 512, **kwargs) == orc.sample_logits(logits, **kwargs)
     with pytest.raises(et.BackendError, match="topK"):
         rt.sample_row(d, 512, top_k=513)
+
+
+@pytest.mark.parametrize("vocab", [1, 33, 4096, 128256])
+def test_device_sampling_agrees_with_the_reference_rule_on_many_draws(vocab):
+    """Every mode of sample_logits over batches of rows with per-row (seed, counter) keys: unfiltered (token-order walk),
+    top-k, top-p, both; peaked and flat rows; ties (repeated values must be ordered by token)."""
+    rt = runtime()
+    rng = np.random.default_rng(vocab)
+    rows = 24
+    logits = (rng.normal(size=(rows, vocab)) * rng.uniform(0.2, 6.0, size=(rows, 1))).astype(np.float32)
+    logits[3] = np.round(logits[3])  # many exact ties
+    logits[4] = 0.25                 # one value everywhere: order is by token alone
+    d = dev(logits)
+    seeds = rng.integers(0, 2**63, size=rows, dtype=np.uint64)
+    counters = rng.integers(0, 1000, size=rows, dtype=np.uint64)
+    d_seeds, d_counters = dev(seeds), dev(counters)
+    tokens = empty(rows, dtype=torch.int32)
+    modes = [dict(temperature=1.0), dict(temperature=0.6), dict(temperature=0.0)]
+    if vocab > 1:
+        k = min(vocab - 1, 50)
+        modes += [dict(temperature=0.8, top_k=k), dict(temperature=1.0, top_p=0.9), dict(temperature=1.5, top_p=0.3),
+                  dict(temperature=0.9, top_k=k, top_p=0.7), dict(temperature=1.0, top_k=1), dict(temperature=2.0, top_k=vocab)]
+    for mode in modes:
+        rt.sample_rows_into(d, rows, vocab, tokens, seeds=d_seeds, counters=d_counters, **mode)
+        got = host(tokens)
+        want = [orc.sample_logits(logits[r], seed=int(seeds[r]), counter=int(counters[r]), **mode) for r in range(rows)]
+        np.testing.assert_array_equal(got, want, err_msg=str(mode))
+
+
+def test_device_sampling_reports_bad_arguments_and_non_finite_logits_like_the_reference():
+    rt = runtime()
+    logits = np.zeros((2, 64), dtype=np.float32)
+    d, tokens = dev(logits), empty(2, dtype=torch.int32)
+    for kwargs, message in ((dict(temperature=-1.0), "temperature must be finite and non-negative"), (dict(top_p=0.0), "topP"),
+                            (dict(top_p=1.5), "topP"), (dict(top_k=65), "topK"), (dict(temperature=float("nan")), "temperature")):
+        with pytest.raises(et.BackendError, match=message):
+            rt.sample_rows_into(d, 2, 64, tokens, **kwargs)
+    logits[1, 9] = np.inf
+    rt.sample_rows_into(dev(logits), 2, 64, tokens, temperature=1.0, top_p=0.9)
+    with pytest.raises(et.BackendError, match="sample: logit 9 is not finite"):
+        rt.synchronize()
