@@ -723,8 +723,8 @@ def run_gpu_arm(args, rank, world):
         if prefill_seconds:
             line["prefill"] = {"tokens_per_s": jobs * BATCH * PROMPT / float(np.mean(prefill_seconds)), "chunk": chunk,
                                "seconds": float(np.mean(prefill_seconds)),
-                               "path": "chunks through Executable.executeSampled: tcgen05 linears at batch x chunk rows, attention by the "
-                                       "reference-order kernel"}
+                               "path": "chunks through Executable.executeSampled: tcgen05 linears at batch x chunk rows, RoPE + KV append "
+                                       "for the whole chunk in one launch, tensor-core chunked-prefill attention"}
         if not args.no_kernel_timing:
             us, algorithmic = time_linear(rt, et, torch, Q4_0, 2 * model["ffn"], model["d_model"], BATCH, True, et.EPILOGUE_SWIGLU, False, 264e6)
             # DRAM bytes per launch of this very kernel and shape, from the committed ncu summary

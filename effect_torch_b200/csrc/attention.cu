@@ -275,6 +275,7 @@ struct AttnArgs {
   float* partial;          // [B, Hq, splits, D + 2] f32: O unnormalised, then m (log2 domain), l
   int q_heads, kv_heads;
   int pages_per_split;
+  int tokens;              // query tokens per lane (1: decode; > 1: a prefill chunk, q and out are [B, tokens, Hq, D])
   float scale_log2;        // scale * log2(e)
   long long op_window;
 };
@@ -286,7 +287,11 @@ __device__ __forceinline__ int swizzled_offset(int row, int chunk) {  // in byte
   return row * (D * 2) + ((chunk & ~7) | ((chunk ^ row) & 7)) * 16;
 }
 
-template <int D, bool BF16>
+// CHUNK = false: one query token per lane; the 16 MMA rows are the query heads of one KV head and grid.x splits the pages.
+// CHUNK = true: a chunk of a.tokens query tokens per lane (chunked prefill, napi/mod.rs:3420-3477 semantics: token t of
+// the chunk attends positions up to cursor + t); the 16 MMA rows are (token, query head) pairs, 16 / G tokens per CTA,
+// grid.x counts row tiles and every row carries its own causal bound.
+template <int D, bool BF16, bool CHUNK>
 __global__ void __launch_bounds__(kAttnWarps * 32) attention_mma_kernel(AttnArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
   constexpr int PAGE_BYTES = kPageTokens * D * 2;
@@ -298,20 +303,36 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attention_mma_kernel(AttnArgs
   const int g = lane >> 2, t = lane & 3;
   chain_release();  // the next kernel of the step may be scheduled; it waits for this one before touching memory
   chain_wait();
-  const int split = blockIdx.x, kv_head = blockIdx.y, lane_id = blockIdx.z;
+  const int split = CHUNK ? 0 : blockIdx.x, kv_head = blockIdx.y, lane_id = blockIdx.z;
   const LaneInfo info = a.lanes[lane_id];
   const int G = a.q_heads / a.kv_heads;
-  const int nsplits = gridDim.x;
-
-  const int end = info.cursor + info.advance;  // one query token: attends positions [begin, end)
+  const int nsplits = CHUNK ? 1 : gridDim.x;
+  // rows g and g + 8 of the MMA tile: which query token and head they are, and the positions [begin, end) they attend
+  const int T = CHUNK ? a.tokens : 1;
+  const int tokens_per_tile = CHUNK ? max(1, 16 / G) : 1;
+  const int tile_token0 = CHUNK ? blockIdx.x * tokens_per_tile : 0;
+  auto row_token = [&](int row) { return CHUNK ? tile_token0 + row / G : 0; };
+  auto row_head = [&](int row) { return CHUNK ? row % G : row; };
+  auto row_valid = [&](int row) { return CHUNK ? (row / G < tokens_per_tile && row_token(row) < T) : row < G; };
+  auto row_end = [&](int row) { return CHUNK ? (row_valid(row) && info.advance > 0 ? info.cursor + row_token(row) + 1 : 0) : info.cursor + info.advance; };
+  auto row_begin = [&](int row, int row_end_) {
+    int b = info.start;
+    if (a.op_window >= 0) b = max((int)max((long long)row_end_ - a.op_window, 0ll), info.start);
+    return b;
+  };
+  const int end_lo = row_end(g), end_hi = row_end(g + 8);
+  const int begin_lo = row_begin(g, end_lo), begin_hi = row_begin(g + 8, end_hi);
+  // the tile as a whole: pages from the earliest begin to the latest end of its rows
+  const int last_token = CHUNK ? min(T, tile_token0 + tokens_per_tile) - 1 : 0;
+  const int end = CHUNK ? (info.advance > 0 && last_token >= tile_token0 ? info.cursor + last_token + 1 : 0) : info.cursor + info.advance;
   int begin = info.start;
-  if (a.op_window >= 0) begin = max((int)max((long long)end - a.op_window, 0ll), info.start);
+  if (a.op_window >= 0) begin = max((int)max((long long)(CHUNK ? info.cursor + tile_token0 + 1 : end) - a.op_window, 0ll), info.start);
   const bool idle_lane = info.advance == 0 || end <= begin;
   // page range of this split (pages are indexed from the table start, i.e. position 0)
   const int first_page = begin / kPageTokens;
   const int last_page = idle_lane ? first_page : (end - 1) / kPageTokens + 1;  // exclusive
   const int p0 = first_page + split * a.pages_per_split;
-  const int p1 = min(last_page, p0 + a.pages_per_split);
+  const int p1 = CHUNK ? last_page : min(last_page, p0 + a.pages_per_split);
 
   unsigned char* my_smem = smem + (size_t)warp * kAttnStages * STAGE_BYTES;
   const int* table = a.tables + info.table_offset;
@@ -339,9 +360,9 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attention_mma_kernel(AttnArgs
   // Q fragments: rows 0..G-1 = query heads of this KV head, scaled into the exp2 domain
   uint32_t qf[KSTEPS][4];
   {
-    const float* qrow_lo = a.q + ((size_t)lane_id * a.q_heads + kv_head * G + g) * D;
-    const float* qrow_hi = qrow_lo + 8 * D;
-    const bool lo_ok = g < G, hi_ok = g + 8 < G;
+    const bool lo_ok = row_valid(g), hi_ok = row_valid(g + 8);
+    const float* qrow_lo = a.q + (((size_t)lane_id * T + (lo_ok ? row_token(g) : 0)) * a.q_heads + kv_head * G + (lo_ok ? row_head(g) : 0)) * D;
+    const float* qrow_hi = a.q + (((size_t)lane_id * T + (hi_ok ? row_token(g + 8) : 0)) * a.q_heads + kv_head * G + (hi_ok ? row_head(g + 8) : 0)) * D;
 #pragma unroll
     for (int ks = 0; ks < KSTEPS; ++ks) {
       const int c0 = ks * 16 + 2 * t;
@@ -395,8 +416,10 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attention_mma_kernel(AttnArgs
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
       const int pa = base_pos + 2 * t + j, pb = pa + 8;
-      if (pa < begin || pa >= end) { s0[j] = -INFINITY; s0[2 + j] = -INFINITY; }
-      if (pb < begin || pb >= end) { s1[j] = -INFINITY; s1[2 + j] = -INFINITY; }
+      if (pa < begin_lo || pa >= end_lo) s0[j] = -INFINITY;
+      if (pa < begin_hi || pa >= end_hi) s0[2 + j] = -INFINITY;
+      if (pb < begin_lo || pb >= end_lo) s1[j] = -INFINITY;
+      if (pb < begin_hi || pb >= end_hi) s1[2 + j] = -INFINITY;
     }
     // online softmax for rows g (index 0,1) and g+8 (index 2,3)
     float mx_lo = fmaxf(fmaxf(s0[0], s0[1]), fmaxf(s1[0], s1[1]));
@@ -464,8 +487,9 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attention_mma_kernel(AttnArgs
     ml[warp * 16 + g] = l_lo; ml[warp * 16 + g + 8] = l_hi;
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
+  for (int idx = threadIdx.x; idx < (CHUNK ? 16 : G) * D; idx += blockDim.x) {
     const int row = idx / D, d = idx - row * D;
+    if (CHUNK && !row_valid(row)) continue;
     float m = -INFINITY;
 #pragma unroll
     for (int w = 0; w < kAttnWarps; ++w) m = fmaxf(m, mm[w * 16 + row]);
@@ -477,11 +501,11 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attention_mma_kernel(AttnArgs
       acc += f * mo[((size_t)w * 16 + row) * D + d];
       l += f * ml[w * 16 + row];
     }
-    const int head = kv_head * G + row;
+    const int head = kv_head * G + row_head(row);
     if (nsplits == 1) {
       const float val = l > 0.0f ? acc / l : 0.0f;
-      a.out[((size_t)lane_id * a.q_heads + head) * D + d] = val;
-      if (a.out_xh) {
+      a.out[(((size_t)lane_id * T + row_token(row)) * a.q_heads + head) * D + d] = val;
+      if (!CHUNK && a.out_xh) {
         const int k = head * D + d;
         a.out_xh[((size_t)(k >> 3) * a.out_xh_nv + lane_id) * 8 + (k & 7)] = __float2half_rn(fminf(fmaxf(val, -65504.f), 65504.f));
       }
@@ -521,7 +545,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ partial, int q_
 
 bool attention_mma_supported(const PoolView& pool, int q_heads, int tokens) {
   const int G = pool.kv_heads > 0 ? q_heads / pool.kv_heads : 0;
-  return tokens == 1 && pool.block_size == kPageTokens && (pool.head_dim == 64 || pool.head_dim == 128) &&
+  return tokens >= 1 && pool.block_size == kPageTokens && (pool.head_dim == 64 || pool.head_dim == 128) &&
          (pool.dtype == kKvF16 || pool.dtype == kKvBF16) && G >= 1 && G <= 16 && q_heads % pool.kv_heads == 0;
 }
 
@@ -545,24 +569,25 @@ size_t plan_attention_max_scratch(int batch, int q_heads, int kv_heads, int head
   return need;
 }
 
-template <int D, bool BF16>
-static cudaError_t launch_attention_mma_t(const PoolView& pool, const AttnArgs& args, int batch, int splits,
+template <int D, bool BF16, bool CHUNK>
+static cudaError_t launch_attention_mma_t(const PoolView& pool, const AttnArgs& args, int batch, int grid_x,
                                           cudaStream_t stream) {
   constexpr size_t ring = (size_t)kAttnWarps * kAttnStages * 2 * kPageTokens * D * 2;
   constexpr size_t merge = (size_t)kAttnWarps * 16 * (D + 2) * sizeof(float);
   constexpr size_t smem = ring > merge ? ring : merge;
-  auto kernel = attention_mma_kernel<D, BF16>;
+  auto kernel = attention_mma_kernel<D, BF16, CHUNK>;
   const cudaError_t attr = opt_in_shared_memory(kernel, smem);
   if (attr != cudaSuccess) return attr;
-  dim3 grid((unsigned)splits, (unsigned)pool.kv_heads, (unsigned)batch);
+  dim3 grid((unsigned)grid_x, (unsigned)pool.kv_heads, (unsigned)batch);
   return launch_chained(kernel, grid, dim3(kAttnWarps * 32), smem, stream, args);
 }
 
 cudaError_t launch_attention_mma(const PoolView& pool, const float* q, const LaneInfo* lanes, const int* tables,
                                  int batch, int q_heads, double scale, long long op_window, float* out,
-                                 const AttnPlan& plan, float* scratch, cudaStream_t stream, int* launches, __half* out_xh, int xh_nv) {
+                                 const AttnPlan& plan, float* scratch, cudaStream_t stream, int* launches, __half* out_xh, int xh_nv,
+                                 int tokens) {
   if (batch == 0) return cudaSuccess;
-  if (batch > xh_nv) out_xh = nullptr;
+  if (batch > xh_nv || tokens > 1) out_xh = nullptr;
   AttnArgs args;
   args.out_xh = out_xh;
   args.out_xh_nv = xh_nv;
@@ -571,12 +596,26 @@ cudaError_t launch_attention_mma(const PoolView& pool, const float* q, const Lan
   args.pages_per_split = plan.pages_per_split;
   args.scale_log2 = (float)(scale * 1.4426950408889634);
   args.op_window = op_window;
+  args.tokens = tokens;
   cudaError_t e;
   const bool bf = pool.dtype == kKvBF16;
-  if (pool.head_dim == 128) e = bf ? launch_attention_mma_t<128, true>(pool, args, batch, plan.splits, stream)
-                                   : launch_attention_mma_t<128, false>(pool, args, batch, plan.splits, stream);
-  else e = bf ? launch_attention_mma_t<64, true>(pool, args, batch, plan.splits, stream)
-              : launch_attention_mma_t<64, false>(pool, args, batch, plan.splits, stream);
+  if (tokens > 1) {
+    // a prefill chunk: one CTA per tile of 16 / G tokens, no split over the pages
+    const int G = q_heads / pool.kv_heads;
+    const int per_tile = std::max(1, 16 / G);
+    const int tiles = (tokens + per_tile - 1) / per_tile;
+    if (pool.head_dim == 128) e = bf ? launch_attention_mma_t<128, true, true>(pool, args, batch, tiles, stream)
+                                     : launch_attention_mma_t<128, false, true>(pool, args, batch, tiles, stream);
+    else e = bf ? launch_attention_mma_t<64, true, true>(pool, args, batch, tiles, stream)
+                : launch_attention_mma_t<64, false, true>(pool, args, batch, tiles, stream);
+    if (e != cudaSuccess) return e;
+    if (launches) ++*launches;
+    return cudaSuccess;
+  }
+  if (pool.head_dim == 128) e = bf ? launch_attention_mma_t<128, true, false>(pool, args, batch, plan.splits, stream)
+                                   : launch_attention_mma_t<128, false, false>(pool, args, batch, plan.splits, stream);
+  else e = bf ? launch_attention_mma_t<64, true, false>(pool, args, batch, plan.splits, stream)
+              : launch_attention_mma_t<64, false, false>(pool, args, batch, plan.splits, stream);
   if (e != cudaSuccess) return e;
   if (launches) ++*launches;
   if (plan.splits > 1) {
@@ -590,7 +629,8 @@ cudaError_t launch_attention_mma(const PoolView& pool, const float* q, const Lan
 }
 
 // --------------------------------------------------------------------------------------------
-// Fused RoPE + KV append for one-token steps. grid (q_heads + 2*kv_heads, batch), D/2 threads.
+// Fused RoPE + KV append. grid (q_heads + 2*kv_heads, batch, tokens), D/2 threads: token t of lane b is row b*tokens + t
+// of qkv, sits at position cursor + t, and its rotated query goes to q_out[b, t, head, :].
 // qkv row layout: [q heads | k heads | v heads] x D. Query heads are rotated into q_out, key heads
 // are rotated and stored into the pool, value heads are stored. Angles in f64 like rope_kernel.
 // --------------------------------------------------------------------------------------------
@@ -605,20 +645,21 @@ __global__ void rope_append_kernel(PoolView pool, const float* __restrict__ qkv,
                                    int q_heads, float* __restrict__ q_out, DeferredSum sum) {
   chain_release();  // the next kernel of the step may be scheduled; it waits for this one before touching memory
   chain_wait();
-  const int head = blockIdx.x, lane_id = blockIdx.y;
+  const int head = blockIdx.x, lane_id = blockIdx.y, tok = blockIdx.z, tokens = gridDim.z;
   const LaneInfo info = lanes[lane_id];
   const int D = pool.head_dim, half = D / 2;
   const int j = threadIdx.x;
   if (j >= half) return;
   const size_t row_width = (size_t)(q_heads + 2 * pool.kv_heads) * D;
-  const float* src = qkv + lane_id * row_width + (size_t)head * D;
+  const size_t row = (size_t)lane_id * tokens + tok;
+  const float* src = qkv + row * row_width + (size_t)head * D;
   const int i0 = layout == 0 ? j : 2 * j, i1 = layout == 0 ? half + j : 2 * j + 1;
   const bool is_q = head < q_heads, is_k = !is_q && head < q_heads + pool.kv_heads;
   float r0, r1;
   if (sum.splits > 0) {  // the projection left its split-K partials unsummed: add them up here, in split order
     r0 = r1 = 0.f;
     for (int s = 0; s < sum.splits; ++s) {
-      const float* p = sum.partials + ((size_t)s * sum.vpad + lane_id) * sum.rows_padded + (size_t)head * D;
+      const float* p = sum.partials + ((size_t)s * sum.vpad + row) * sum.rows_padded + (size_t)head * D;
       r0 += p[i0];
       r1 += p[i1];
     }
@@ -627,7 +668,7 @@ __global__ void rope_append_kernel(PoolView pool, const float* __restrict__ qkv,
     r1 = src[i1];
   }
   if (is_q || is_k) {
-    const double angle = (double)info.cursor * inv_freq[j];
+    const double angle = (double)(info.cursor + tok) * inv_freq[j];
     double s, c;
     sincos(angle, &s, &c);
     const double first = (double)r0, second = (double)r1;
@@ -635,14 +676,14 @@ __global__ void rope_append_kernel(PoolView pool, const float* __restrict__ qkv,
     r1 = (float)__dadd_rn(__dmul_rn(second, c), __dmul_rn(first, s));
   }
   if (is_q) {
-    float* dst = q_out + ((size_t)lane_id * q_heads + head) * D;
+    float* dst = q_out + (row * q_heads + head) * D;
     dst[i0] = r0;
     dst[i1] = r1;
     return;
   }
   if (info.advance == 0) return;  // padded lane: nothing is cached
   const int kv_head = is_k ? head - q_heads : head - q_heads - pool.kv_heads;
-  const int pos = info.cursor;
+  const int pos = info.cursor + tok;
   const int page = tables[info.table_offset + pos / pool.block_size], slot = pos % pool.block_size;
   const size_t dst = pool_elem(pool, page, kv_head, slot);
   void* slab = is_k ? pool.k : pool.v;
@@ -652,9 +693,9 @@ __global__ void rope_append_kernel(PoolView pool, const float* __restrict__ qkv,
 
 cudaError_t launch_rope_append(const PoolView& pool, const float* qkv, const LaneInfo* lanes, const int* tables,
                                const double* inv_freq, int layout, int batch, int q_heads, float* q_out,
-                               cudaStream_t stream, const DeferredSum* sum) {
+                               cudaStream_t stream, const DeferredSum* sum, int tokens) {
   if (batch == 0) return cudaSuccess;
-  dim3 grid((unsigned)(q_heads + 2 * pool.kv_heads), (unsigned)batch);
+  dim3 grid((unsigned)(q_heads + 2 * pool.kv_heads), (unsigned)batch, (unsigned)tokens);
   return launch_chained(rope_append_kernel, grid, dim3((unsigned)std::max(32, pool.head_dim / 2)), 0, stream, pool, qkv, lanes, tables, inv_freq, layout, q_heads,
                         q_out, sum ? *sum : DeferredSum());
 }

@@ -188,6 +188,7 @@ etc_status set_weight(etc_decoder* dec, int slot, int layer, int codec, const vo
 }
 
 bool tileable(const BoundWeight& w) {
+  if (w.codec == ETC_CODEC_Q4_K || w.codec == ETC_CODEC_Q6_K) return w.columns % 256 == 0;
   return (w.codec == ETC_CODEC_Q4_0 || w.codec == ETC_CODEC_Q8_0) && w.columns % 64 == 0;
 }
 
@@ -336,7 +337,7 @@ etc_status enqueue_step(StepContext& s) {
       stride_q = qw; stride_kv = kvw;
     }
     if (fast_attention) {
-      ETC_CUDA(launch_rope_append(view, d->qkv, d->d_lanes, d->d_tables, d->d_inv_freq, c.rope_layout, B, Hq, d->qr, stream, &qkv_sum));
+      ETC_CUDA(launch_rope_append(view, d->qkv, d->d_lanes, d->d_tables, d->d_inv_freq, c.rope_layout, B, Hq, d->qr, stream, &qkv_sum, T));
       ++s.launches;
       const AttnPlan plan = plan_attention(B, Hq, Hkv, D, std::max(1, s.max_pages), d->rt->sm_count);
       if (plan.scratch_bytes > d->attn_scratch_bytes)
@@ -344,7 +345,7 @@ etc_status enqueue_step(StepContext& s) {
                                        std::to_string(plan.scratch_bytes) + " bytes of partials, the decoder holds " +
                                        std::to_string(d->attn_scratch_bytes));
       ETC_CUDA(launch_attention_mma(view, d->qr, d->d_lanes, d->d_tables, B, Hq, scale, c.window, d->attl, plan,
-                                    d->attn_scratch, stream, &s.launches, xh ? d->xh_att : nullptr, d->xh_nv));
+                                    d->attn_scratch, stream, &s.launches, xh ? d->xh_att : nullptr, d->xh_nv, T));
     } else {
       ETC_CUDA(launch_heads_first(qp, d->qh, B, T, Hq, D, stride_q, stream));
       ETC_CUDA(launch_heads_first(kp, d->kh, B, T, Hkv, D, stride_kv, stream));

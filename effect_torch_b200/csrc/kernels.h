@@ -210,12 +210,12 @@ bool attention_mma_supported(const PoolView& pool, int q_heads, int tokens);
 cudaError_t launch_attention_mma(const PoolView& pool, const float* q, const LaneInfo* lanes, const int* tables,
                                  int batch, int q_heads, double scale, long long op_window, float* out,
                                  const AttnPlan& plan, float* scratch, cudaStream_t stream, int* launches,
-                                 __half* out_xh = nullptr, int xh_nv = 32);
-// Fused RoPE(q), RoPE(k) and KV append for one-token steps: qkv [B, (Hq+2*Hkv)*D] f32 (the fused
-// projection output) -> q_out [B,Hq,D] f32 rotated, K/V rows written to the pool.
+                                 __half* out_xh = nullptr, int xh_nv = 32, int tokens = 1);
+// Fused RoPE(q), RoPE(k) and KV append: qkv [B * tokens, (Hq+2*Hkv)*D] f32 (the fused projection output) ->
+// q_out [B, tokens, Hq, D] f32 rotated, K/V rows written to the pool at positions cursor .. cursor + tokens - 1.
 cudaError_t launch_rope_append(const PoolView& pool, const float* qkv, const LaneInfo* lanes, const int* tables,
                                const double* inv_freq, int layout, int batch, int q_heads, float* q_out,
-                               cudaStream_t stream, const DeferredSum* sum = nullptr);
+                               cudaStream_t stream, const DeferredSum* sum = nullptr, int tokens = 1);
 // Tail of a device-resident greedy step: feeds the sampled tokens back as the next ids, appends
 // them to the history, and advances every live lane's cursor (and window start) by one.
 cudaError_t launch_record_step(const uint32_t* tokens, uint32_t* ids, uint32_t* history, int* step_counter, LaneInfo* lanes,

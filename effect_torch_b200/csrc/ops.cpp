@@ -60,11 +60,12 @@ etc_status make_inv_freq(etc_runtime* rt, double theta, int head_dim, double** o
 
 etc_status build_qweight(etc_runtime* rt, int codec, const void* const* parts, const int64_t* part_rows, int n_parts,
                          int64_t columns, int interleave8, int on_device, etc_qweight** out) {
-  if (codec != ETC_CODEC_Q4_0 && codec != ETC_CODEC_Q8_0)
-    return fail(ETC_UNSUPPORTED, std::string("tiled weights support Q4_0 and Q8_0, got ") + codec_name(codec));
+  const bool kquant = codec == ETC_CODEC_Q4_K || codec == ETC_CODEC_Q6_K;
+  if (codec != ETC_CODEC_Q4_0 && codec != ETC_CODEC_Q8_0 && !kquant)
+    return fail(ETC_UNSUPPORTED, std::string("tiled weights support Q4_0, Q8_0, Q4_K and Q6_K, got ") + codec_name(codec));
   if (n_parts < 1 || n_parts > 4) return fail(ETC_INVALID_ARGUMENT, "qweight: between 1 and 4 parts are supported");
-  if (columns <= 0 || columns % 64 != 0)
-    return fail(ETC_COMPILATION, "qweight: logical row width " + std::to_string(columns) + " must be a multiple of 64");
+  if (columns <= 0 || columns % 64 != 0 || (kquant && columns % 256 != 0))
+    return fail(ETC_COMPILATION, "qweight: logical row width " + std::to_string(columns) + " must be a multiple of " + (kquant ? "256" : "64"));
   if (interleave8 && (n_parts != 2 || part_rows[0] != part_rows[1] || part_rows[0] % 8 != 0))
     return fail(ETC_COMPILATION, "qweight: interleave8 needs two parts of equal row count divisible by 8");
   int64_t rows = 0;
@@ -82,9 +83,12 @@ etc_status build_qweight(etc_runtime* rt, int codec, const void* const* parts, c
   w->tiled.columns = columns;
   w->tiled.interleave8 = interleave8;
   const int64_t kblocks = columns / 32;
-  w->tiled.quant_bytes = (size_t)w->tiled.rows_padded * kblocks * (codec == ETC_CODEC_Q4_0 ? 16 : 32);
-  w->tiled.scale_bytes = (size_t)w->tiled.rows_padded * kblocks * 2;
-  const size_t counter_bytes = (size_t)(w->tiled.rows_padded / 128) * sizeof(int);
+  // K-quants are re-cut into 32-value blocks at load: Q4_K -> nibbles + (scale, min) per block, Q6_K -> int8 codes + one
+  // scale per 16 values; the small-batch matvec kernel (and its arrival tickets) serves the 32-value codecs only
+  const bool nibbles = codec == ETC_CODEC_Q4_0 || codec == ETC_CODEC_Q4_K;
+  w->tiled.quant_bytes = (size_t)w->tiled.rows_padded * kblocks * (nibbles ? 16 : 32);
+  w->tiled.scale_bytes = (size_t)w->tiled.rows_padded * kblocks * (kquant ? 4 : 2);
+  const size_t counter_bytes = kquant ? 0 : (size_t)(w->tiled.rows_padded / 128) * sizeof(int);
   etc_status st = rt->device_alloc(w->tiled.quant_bytes, (void**)&w->tiled.quants);
   if (st == ETC_OK && w->tiled.scale_bytes) st = rt->device_alloc(w->tiled.scale_bytes, (void**)&w->tiled.scales);
   if (st == ETC_OK && counter_bytes) {

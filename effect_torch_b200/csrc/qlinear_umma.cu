@@ -28,8 +28,10 @@
 #include <cuda_fp16.h>
 
 #include <algorithm>
+#include <type_traits>
 
 #include "chain.cuh"
+#include "codecs.cuh"
 #include "kernels.h"
 #include "tc05.cuh"
 
@@ -75,7 +77,9 @@ __global__ void __launch_bounds__(UmmaCfg<NV>::kThreads) qlinear_umma_kernel(Umm
   using Cfg = UmmaCfg<NV>;
   constexpr int kGroups = Cfg::kGroups, kStageBlocks = Cfg::kStageBlocks, kStages = Cfg::kStages;
   constexpr int kAColsPerStage = Cfg::kAColsPerStage;
-  constexpr int QW = CODEC == 2 ? 1 : 2;                    // uint4 words per (row, block)
+  constexpr bool kNibbles = CODEC == 2 || CODEC == 12;      // 4-bit codes (Q4_0, re-cut Q4_K) or 8-bit (Q8_0, re-cut Q6_K)
+  constexpr bool kPair = CODEC == 12 || CODEC == 14;        // two f16 per (row, block): (scale, min) or the two half-block scales
+  constexpr int QW = kNibbles ? 1 : 2;                      // uint4 words per (row, block)
   constexpr uint32_t kStageBBytes = Cfg::kStageBBytes;      // one stage of activations
   constexpr uint32_t kTmemCols = Cfg::kTmemCols;
   constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(NV >> 3) << 17) | ((uint32_t)(kUmmaRows >> 4) << 24);  // f16 x f16 -> f32
@@ -121,17 +125,19 @@ __global__ void __launch_bounds__(UmmaCfg<NV>::kThreads) qlinear_umma_kernel(Umm
     const int row = (warp & 3) * 32 + lane;  // TMEM lane == row inside the tile
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const uint4* qrow = a.quants + ((size_t)tile * a.kblocks) * (kUmmaRows * QW) + (size_t)row * QW;
-    const __half* srow = a.scales + ((size_t)tile * a.kblocks) * kUmmaRows + row;
+    constexpr int SW = kPair ? 2 : 1;  // halves per (row, block) in the scale array
+    const __half* srow = a.scales + (((size_t)tile * a.kblocks) * kUmmaRows + row) * SW;
     constexpr int PF = 2;  // of this group's stages, held packed in registers ahead of use
     uint4 qbuf[PF][kStageBlocks][QW];
-    __half sbuf[PF][kStageBlocks];
+    uint32_t sbuf[PF][kStageBlocks];  // one f16 (low half) or a pair
     auto load_stage = [&](int stage_index, int slot) {
 #pragma unroll
       for (int b = 0; b < kStageBlocks; ++b) {
         const int kb = min(kb0 + stage_index * kStageBlocks + b, kb1 - 1);  // clamped: masked at use
 #pragma unroll
         for (int w = 0; w < QW; ++w) qbuf[slot][b][w] = __ldg(qrow + (size_t)kb * (kUmmaRows * QW) + w);
-        sbuf[slot][b] = __ldg(srow + (size_t)kb * kUmmaRows);
+        if (kPair) sbuf[slot][b] = __ldg(reinterpret_cast<const uint32_t*>(srow + (size_t)kb * kUmmaRows * 2));
+        else sbuf[slot][b] = (uint32_t)__ldg(reinterpret_cast<const unsigned short*>(srow + (size_t)kb * kUmmaRows));
       }
     };
     const int my_stages = nstages > group ? (nstages - group + kGroups - 1) / kGroups : 0;
@@ -154,17 +160,29 @@ __global__ void __launch_bounds__(UmmaCfg<NV>::kThreads) qlinear_umma_kernel(Umm
         uint32_t regs[kStageBlocks][16];
 #pragma unroll
         for (int b = 0; b < kStageBlocks; ++b) {
-          const __half2 sc = __half2half2(b < valid ? sbuf[p][b] : __float2half_rn(0.0f));
+          const uint32_t sraw = b < valid ? sbuf[p][b] : 0u;
+          const __half2 pair = u2h(sraw);
+          // first f16 of the entry: the block scale (Q6_K: of values 0-15); second: Q4_K's min, Q6_K's scale of values 16-31
+          const __half2 sc = __half2half2(__low2half(pair));
+          const __half2 second = __half2half2(__high2half(pair));
           if (CODEC == 2) {
             const uint4 q = qbuf[p][b][0];
             expand_q4(q.x, sc, regs[b] + 0);
             expand_q4(q.y, sc, regs[b] + 4);
             expand_q4(q.z, sc, regs[b] + 8);
             expand_q4(q.w, sc, regs[b] + 12);
+          } else if (CODEC == 12) {
+            const uint4 q = qbuf[p][b][0];
+            const __half2 neg_min = __hneg2(second);
+            expand_q4k(q.x, sc, neg_min, regs[b] + 0);
+            expand_q4k(q.y, sc, neg_min, regs[b] + 4);
+            expand_q4k(q.z, sc, neg_min, regs[b] + 8);
+            expand_q4k(q.w, sc, neg_min, regs[b] + 12);
           } else {
+            const __half2 sc_hi = CODEC == 14 ? second : sc;
             const uint4 q0 = qbuf[p][b][0], q1 = qbuf[p][b][QW - 1];
             expand_q8(q0.x, sc, regs[b] + 0); expand_q8(q0.y, sc, regs[b] + 2); expand_q8(q0.z, sc, regs[b] + 4); expand_q8(q0.w, sc, regs[b] + 6);
-            expand_q8(q1.x, sc, regs[b] + 8); expand_q8(q1.y, sc, regs[b] + 10); expand_q8(q1.z, sc, regs[b] + 12); expand_q8(q1.w, sc, regs[b] + 14);
+            expand_q8(q1.x, sc_hi, regs[b] + 8); expand_q8(q1.y, sc_hi, regs[b] + 10); expand_q8(q1.z, sc_hi, regs[b] + 12); expand_q8(q1.w, sc_hi, regs[b] + 14);
           }
         }
         if (j + PF < my_stages) load_stage(group + (j + PF) * kGroups, p);  // refill this register slot
@@ -313,28 +331,70 @@ __global__ void convert_xh8_kernel(const float* __restrict__ x, int vectors, int
 __global__ void repack_umma_kernel(RepackParts parts, int codec, int64_t rows, int64_t rows_padded, int64_t kblocks,
                                    int interleave8, uint32_t* __restrict__ quants, __half* __restrict__ scales) {
   const int64_t total = rows_padded * kblocks;
-  const int bb = codec == 2 ? 18 : 34;
-  const int words = codec == 2 ? 4 : 8;
+  const bool kquant = codec == 12 || codec == 14;
+  const int bb = codec == 2 ? 18 : (codec == 8 ? 34 : (codec == 12 ? 144 : 210));  // bytes per source block
+  const int per_block = kquant ? 8 : 1;                                              // 32-value blocks per source block
+  const int words = (codec == 2 || codec == 12) ? 4 : 8;
+  const int64_t row_bytes = kblocks / per_block * bb;
   for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
     const int64_t r = idx / kblocks, kb = idx - r * kblocks;
     const uint8_t* src_row = nullptr;
     if (r < rows) {
       if (interleave8) {
         const int64_t grp = r >> 4, within = r & 15;
-        src_row = parts.ptr[within >= 8 ? 1 : 0] + (grp * 8 + (within & 7)) * kblocks * bb;
+        src_row = parts.ptr[within >= 8 ? 1 : 0] + (grp * 8 + (within & 7)) * row_bytes;
       } else {
         int64_t rr = r;
         for (int p = 0; p < parts.n_parts; ++p) {
-          if (rr < parts.rows[p]) { src_row = parts.ptr[p] + rr * kblocks * bb; break; }
+          if (rr < parts.rows[p]) { src_row = parts.ptr[p] + rr * row_bytes; break; }
           rr -= parts.rows[p];
         }
       }
     }
     const int64_t tile = r / kUmmaRows, row = r % kUmmaRows;
     uint32_t* dst = quants + ((tile * kblocks + kb) * kUmmaRows + row) * words;
-    __half scale = __float2half_rn(0.0f);
+    __half scale = __float2half_rn(0.0f), second = __float2half_rn(0.0f);
     if (!src_row) {
       for (int w = 0; w < words; ++w) dst[w] = codec == 2 ? 0x88888888u : 0u;
+    } else if (codec == 12) {
+      // Q4_K (crates/runtime-cpu/src/quantized.rs:180-199): sub-block `sub` of the 256-value block, value = d*sc*code - dmin*m
+      const uint8_t* blk = src_row + (kb >> 3) * bb;
+      const int sub = (int)(kb & 7);
+      int sc, mn;
+      scale_min_k4(sub, blk + 4, sc, mn);
+      scale = __float2half_rn(__fmul_rn(fp16_at(blk, 0), (float)sc));
+      second = __float2half_rn(__fmul_rn(fp16_at(blk, 2), (float)mn));
+      const int pos[8] = {0, 16, 8, 24, 4, 20, 12, 28};
+      for (int w = 0; w < 4; ++w) {
+        uint32_t word = 0;
+        for (int j = 0; j < 8; ++j) {
+          const int raw = blk[16 + (sub >> 1) * 32 + 8 * w + j];
+          word |= (uint32_t)((sub & 1) ? (raw >> 4) : (raw & 0x0f)) << pos[j];
+        }
+        dst[w] = word;
+      }
+    } else if (codec == 14) {
+      // Q6_K (quantized.rs:238-261): values 32*sub .. 32*sub+31 of the 256-value block, value = d*scale*(code - 32) with one
+      // int8 scale per 16 values
+      const uint8_t* blk = src_row + (kb >> 3) * bb;
+      const int first = (int)(kb & 7) * 32;
+      const int half = first >> 7, quarter = (first & 127) >> 5;
+      const uint8_t* ql = blk + half * 64;
+      const uint8_t* qh = blk + 128 + half * 32;
+      const float d = fp16_at(blk, 208);
+      scale = __float2half_rn(__fmul_rn(d, (float)(int)(signed char)blk[192 + half * 8 + quarter * 2]));
+      second = __float2half_rn(__fmul_rn(d, (float)(int)(signed char)blk[192 + half * 8 + quarter * 2 + 1]));
+      for (int w = 0; w < 8; ++w) {
+        uint32_t word = 0;
+        for (int j = 0; j < 4; ++j) {
+          const int index = 4 * w + j;
+          const int low = (quarter & 1) ? ql[index + 32] : ql[index];
+          const int low4 = (quarter & 2) ? (low >> 4) : (low & 0x0f);
+          const int code = (low4 | (((qh[index] >> (2 * quarter)) & 3) << 4)) - 32;
+          word |= (uint32_t)(code & 0xff) << (8 * j);
+        }
+        dst[w] = word;
+      }
     } else {
       const uint8_t* blk = src_row + kb * bb;
       scale = __ushort_as_half((unsigned short)(blk[0] | (blk[1] << 8)));
@@ -357,7 +417,12 @@ __global__ void repack_umma_kernel(RepackParts parts, int codec, int64_t rows, i
         }
       }
     }
-    scales[(tile * kblocks + kb) * kUmmaRows + row] = scale;
+    if (kquant) {
+      scales[((tile * kblocks + kb) * kUmmaRows + row) * 2] = scale;
+      scales[((tile * kblocks + kb) * kUmmaRows + row) * 2 + 1] = second;
+    } else {
+      scales[(tile * kblocks + kb) * kUmmaRows + row] = scale;
+    }
   }
 }
 
@@ -444,12 +509,20 @@ cudaError_t launch_qlinear_umma(const TiledWeight& w, const float* x, const __ha
     args.kblocks = K / 32;
     args.blocks_per_split = plan.blocks_per_split;
     args.epilogue = epilogue;
-    const bool q4 = w.codec == 2;
+    auto pass = [&](auto nv_tag) {
+      constexpr int NV = decltype(nv_tag)::value;
+      switch (w.codec) {
+        case 2: return launch_umma_pass<2, NV>(args, plan.tiles, plan.splits, stream);
+        case 8: return launch_umma_pass<8, NV>(args, plan.tiles, plan.splits, stream);
+        case 12: return launch_umma_pass<12, NV>(args, plan.tiles, plan.splits, stream);
+        default: return launch_umma_pass<14, NV>(args, plan.tiles, plan.splits, stream);
+      }
+    };
     switch (plan.nv) {
-      case 32: e = q4 ? launch_umma_pass<2, 32>(args, plan.tiles, plan.splits, stream) : launch_umma_pass<8, 32>(args, plan.tiles, plan.splits, stream); break;
-      case 64: e = q4 ? launch_umma_pass<2, 64>(args, plan.tiles, plan.splits, stream) : launch_umma_pass<8, 64>(args, plan.tiles, plan.splits, stream); break;
-      case 128: e = q4 ? launch_umma_pass<2, 128>(args, plan.tiles, plan.splits, stream) : launch_umma_pass<8, 128>(args, plan.tiles, plan.splits, stream); break;
-      default: e = q4 ? launch_umma_pass<2, 256>(args, plan.tiles, plan.splits, stream) : launch_umma_pass<8, 256>(args, plan.tiles, plan.splits, stream); break;
+      case 32: e = pass(std::integral_constant<int, 32>()); break;
+      case 64: e = pass(std::integral_constant<int, 64>()); break;
+      case 128: e = pass(std::integral_constant<int, 128>()); break;
+      default: e = pass(std::integral_constant<int, 256>()); break;
     }
     if (e != cudaSuccess) return e;
     if (launches) ++*launches;

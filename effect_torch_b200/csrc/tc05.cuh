@@ -165,6 +165,19 @@ __device__ __forceinline__ void expand_q8(uint32_t w, __half2 scale, uint32_t* o
   out2[1] = h2u(__hmul2(__hsub2(u2h(__byte_perm(x, 0x64646464u, 0x4342)), bias), scale));
 }
 
+// Q4_K block re-cut to 32 values: code * scale - min (scale = d * sc, min = dmin * m, both rounded to f16 at load).
+__device__ __forceinline__ void expand_q4k(uint32_t q, __half2 scale, __half2 neg_min, uint32_t* out4) {
+  const uint32_t magic = 0x64006400u;
+  const uint32_t qs = q >> 8;
+  const __half2 bias_lo = __floats2half2_rn(1024.0f, 1024.0f);
+  const __half2 sixteenth = __floats2half2_rn(0.0625f, 0.0625f);
+  const __half2 bias_hi = __floats2half2_rn(-64.0f, -64.0f);
+  out4[0] = h2u(__hfma2(__hsub2(u2h((q & 0x000F000Fu) | magic), bias_lo), scale, neg_min));
+  out4[1] = h2u(__hfma2(__hsub2(u2h((qs & 0x000F000Fu) | magic), bias_lo), scale, neg_min));
+  out4[2] = h2u(__hfma2(__hfma2(u2h((q & 0x00F000F0u) | magic), sixteenth, bias_hi), scale, neg_min));
+  out4[3] = h2u(__hfma2(__hfma2(u2h((qs & 0x00F000F0u) | magic), sixteenth, bias_hi), scale, neg_min));
+}
+
 __device__ __forceinline__ float silu_tanh(float x) { return x * (tanhf(x * 0.5f) * 0.5f + 0.5f); }
 
 // D[tmem] (+)= A[smem desc] * B[smem desc].

@@ -264,3 +264,91 @@ def test_a_recreated_pool_never_replays_the_old_pools_graph():
     second = run(pool_b)
     np.testing.assert_array_equal(second, first)
     del filler
+
+
+def test_the_operator_by_operator_route_agrees_with_the_fused_decoder():
+    """A backend that lowers the specialised decode graph node by node (QuantizedEmbedding, RmsNorm, QuantizedLinear,
+    RotaryEmbedding{Cursor}, KvAttention, SwiGLU, Add, LastTokenRow: crates/compiler/src/decode.rs:105-481) calls one C-ABI
+    operator per node. That route, the fused decoder and the CPU oracle must tell the same story for a prefill chunk and two
+    decode steps of a small quantized model (tensors only change layout between operators here, through torch views)."""
+    import torch
+    from tests.gpu_util import dev, empty, host
+
+    rt = runtime()
+    cfg = helpers.TINY_Q
+    codec = orc.Q4_0
+    weights = helpers.make_weights(cfg, seed=4, codec=codec)
+    weights["tok_embd"] = (orc.quantize(codec, weights["tok_embd"]),) + weights["tok_embd"].shape  # QuantizedEmbedding
+    B, max_tokens = 2, 128
+    L, d, Hq, Hkv, D, ffn, V = (cfg[k] for k in ("layers", "d_model", "q_heads", "kv_heads", "head_dim", "ffn", "vocab"))
+    fused = gpu_decoder(cfg, weights, B, max_tokens, kv_dtype=et.KV_F16, exact=False, max_advance=8)
+    odec = helpers.oracle_decoder(cfg, weights, batch=B)
+    pool_fused = et.NativeKvPool(rt, L, Hkv, D, max_tokens, 16, et.KV_F16)
+    pool_ops = et.NativeKvPool(rt, L, Hkv, D, max_tokens, 16, et.KV_F16)
+    opool = orc.Pool(L, Hkv, D, max_tokens, 16, orc.F16)
+    seqs_fused = [pool_fused.makeSequence() for _ in range(B)]
+    seqs_ops = [pool_ops.makeSequence() for _ in range(B)]
+    oseqs = [opool.make_sequence() for _ in range(B)]
+    w = {name: [dev(layer[name][0]) if isinstance(layer[name], tuple) else dev(layer[name]) for layer in weights["layers"]]
+         for name in helpers.SLOTS}
+    embd, head, out_norm = dev(weights["tok_embd"][0]), dev(weights["head"][0]), dev(weights["out_norm"])
+
+    def linear(x, rows_in, weight, n, k):
+        out = empty((rows_in, n))
+        rt.qlinear_into(codec, x, rows_in, k, weight, n, None, out)
+        return out
+
+    def step_by_operators(tokens):
+        T = tokens.shape[1]
+        R = B * T
+        cursors = dev(np.array([s.cursor for s in seqs_ops], dtype=np.int64))
+        hidden = empty((R, d))
+        rt.qembedding_into(codec, dev(tokens.reshape(-1).astype(np.uint32)), False, R, embd, V, d, hidden)
+        for l in range(L):
+            normed = empty((R, d))
+            rt.rmsnorm_into(hidden, w["attn_norm"][l], cfg["rms_eps"], R, d, normed)
+            q, k, v = (linear(normed, R, w[n][l], width, d) for n, width in (("wq", Hq * D), ("wk", Hkv * D), ("wv", Hkv * D)))
+            rt.synchronize()
+            heads_first = lambda x, h: x.view(B, T, h, D).permute(0, 2, 1, 3).contiguous()  # [B, H, T, D]
+            qh, kh, vh = heads_first(q, Hq), heads_first(k, Hkv), heads_first(v, Hkv)
+            torch.cuda.synchronize()
+            qr, kr = empty((B, Hq, T, D)), empty((B, Hkv, T, D))
+            rt.rope_into(qh, cursors, B, cfg["rope_theta"], et.HALF_SPLIT, B, Hq, T, D, qr)
+            rt.rope_into(kh, cursors, B, cfg["rope_theta"], et.HALF_SPLIT, B, Hkv, T, D, kr)
+            att = empty((B, Hq, T, D))
+            rt.kv_attention_into(pool_ops, l, seqs_ops, B, B, T, qr, kr, vh, Hq, T, 1.0 / np.sqrt(D), out=att)
+            rt.synchronize()
+            att_rows = att.permute(0, 2, 1, 3).contiguous().view(R, Hq * D)
+            torch.cuda.synchronize()
+            o = linear(att_rows, R, w["wo"][l], d, Hq * D)
+            rt.add_into(hidden, o, R * d, hidden)
+            rt.rmsnorm_into(hidden, w["ffn_norm"][l], cfg["rms_eps"], R, d, normed)
+            gate, up = linear(normed, R, w["gate"][l], ffn, d), linear(normed, R, w["up"][l], ffn, d)
+            act = empty((R, ffn))
+            rt.swiglu_into(gate, up, R * ffn, act)
+            down = linear(act, R, w["down"][l], d, ffn)
+            rt.add_into(hidden, down, R * d, hidden)
+        normed = empty((R, d))
+        rt.rmsnorm_into(hidden, out_norm, cfg["rms_eps"], R, d, normed)
+        rt.synchronize()
+        last = normed.view(B, T, d)[:, T - 1, :].contiguous()  # LastTokenRow
+        torch.cuda.synchronize()
+        logits = linear(last, B, head, V, d)
+        picked = empty(B, dtype=torch.int32)
+        rt.argmax_into(logits, B, V, picked)
+        result = host(logits)
+        for s, row in zip(seqs_ops, tokens):
+            s.commit(row)
+        return result, host(picked)
+
+    rng = np.random.default_rng(8)
+    for advance in (8, 1, 1):
+        tokens = rng.integers(0, V, size=(B, advance)).astype(np.uint32)
+        by_ops, picked = step_by_operators(tokens)
+        by_decoder = fused.execute(pool_fused, seqs_fused, tokens)
+        by_oracle, _ = odec.execute(opool, oseqs, tokens)
+        assert helpers.rel_err(by_ops, by_oracle) <= LOGIT_TOL, f"operators vs oracle, advance {advance}"
+        assert helpers.rel_err(by_decoder, by_oracle) <= LOGIT_TOL, f"decoder vs oracle, advance {advance}"
+        assert helpers.rel_err(by_ops, by_decoder) <= LOGIT_TOL, f"operators vs decoder, advance {advance}"
+        np.testing.assert_array_equal(picked, by_ops.argmax(axis=1))
+        assert [s.cursor for s in seqs_ops] == [s.cursor for s in seqs_fused]

@@ -182,10 +182,61 @@ def test_tiled_linear_epilogues(codec, vectors):
     assert helpers.rel_err(host(both), expected_both) <= REL_TOL
 
 
+@pytest.mark.parametrize("codec", [gv.Q4_K, gv.Q6_K])
+def test_k_quant_tiling_preserves_every_weight(codec):
+    """The 256-value K-quant blocks are re-cut into 32-value blocks at load (effective scales rounded to f16): x = identity
+    picks out single weights, which must equal the reference decode to the f16 precision of the MMA operands."""
+    rows, columns = 40, 512
+    packed = random_packed(codec, rows, columns, seed=11)
+    deq = orc.dequantize(codec, packed, rows, columns)
+    qw = et.QWeight(runtime(), codec, [dev(packed)], [rows], columns)
+    out = empty((columns, rows))
+    qw.linear_into(dev(np.eye(columns, dtype=np.float32)), columns, out)
+    scale = np.abs(deq).max()
+    np.testing.assert_allclose(host(out).T, deq, rtol=2.0 ** -9, atol=scale * 2.0 ** -10)
+
+
+@pytest.mark.parametrize("codec", [gv.Q4_K, gv.Q6_K])
+@pytest.mark.parametrize("rows,columns", [(256, 512), (200, 1024), (1024, 4096)])
+@pytest.mark.parametrize("vectors", [1, 8, 17, 32, 64, 300])
+def test_k_quant_tiled_linear_matches_the_oracle(codec, rows, columns, vectors):
+    rng = np.random.default_rng(rows + columns + vectors)
+    packed = random_packed(codec, rows, columns, seed=rows + vectors)
+    x = rng.normal(size=(vectors, columns)).astype(np.float32)
+    qw = et.QWeight(runtime(), codec, [dev(packed)], [rows], columns)
+    out = empty((vectors, rows))
+    qw.linear_into(dev(x), vectors, out)
+    expected = orc.qlinear(codec, x, packed, rows, columns, threads=8)
+    assert helpers.rel_err(host(out), expected) <= REL_TOL
+
+
+@pytest.mark.parametrize("codec", [gv.Q4_K, gv.Q6_K])
+def test_k_quant_fused_gate_up_and_residual_epilogues(codec):
+    rng = np.random.default_rng(21)
+    d, ffn, vectors = 512, 256, 20
+    pg, pu, pd = random_packed(codec, ffn, d, 1), random_packed(codec, ffn, d, 2), random_packed(codec, d, ffn, 3)
+    x = rng.normal(size=(vectors, d)).astype(np.float32)
+    residual = rng.normal(size=(vectors, d)).astype(np.float32)
+    rt = runtime()
+    qgu = et.QWeight(rt, codec, [dev(pg), dev(pu)], [ffn, ffn], d, interleave8=True)
+    act = empty((vectors, ffn))
+    qgu.linear_into(dev(x), vectors, act, epilogue=et.EPILOGUE_SWIGLU)
+    expected_act = orc.silu_mul(orc.qlinear(codec, x, pg, ffn, d, threads=4), orc.qlinear(codec, x, pu, ffn, d, threads=4))
+    assert helpers.rel_err(host(act), expected_act) <= REL_TOL
+    qd = et.QWeight(rt, codec, [dev(pd)], [d], ffn)
+    out = empty((vectors, d))
+    unit_act = (expected_act / np.abs(expected_act).max()).astype(np.float32)  # random code bytes make huge activations: keep f16 range
+    qd.linear_into(dev(unit_act), vectors, out, residual=dev(residual), epilogue=et.EPILOGUE_RESIDUAL)
+    expected = residual + orc.qlinear(codec, unit_act, pd, d, ffn, threads=4)
+    assert helpers.rel_err(host(out), expected) <= REL_TOL
+
+
 def test_tiled_weight_rejects_unsupported_geometry():
     rt = runtime()
     raw = empty((16, 18 * 3), dtype=torch.uint8)
     with pytest.raises(et.BackendError, match="multiple of 64"):
         et.QWeight(rt, gv.Q4_0, [raw], [16], 96)
-    with pytest.raises(et.BackendError, match="Q4_0 and Q8_0"):
-        et.QWeight(rt, gv.Q4_K, [raw], [16], 256)
+    with pytest.raises(et.BackendError, match="Q4_0, Q8_0, Q4_K and Q6_K"):
+        et.QWeight(rt, gv.Q5_K, [empty((16, 176), dtype=torch.uint8)], [16], 256)
+    with pytest.raises(et.BackendError, match="multiple of 256"):
+        et.QWeight(rt, gv.Q4_K, [raw], [16], 128)
