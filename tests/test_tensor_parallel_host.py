@@ -125,3 +125,32 @@ def test_two_rank_projection_block_over_gloo_matches_the_unsharded_oracle():
     assert sorted(numeric.keys()) == [0, 1, 2, 3]
     assert all(err <= 1e-6 for err in numeric.values()), dict(results)
     assert results[("agree", 0)] == (False, True) and results[("agree", 1)] == (False, True)
+
+
+def test_a_sharded_head_cuts_the_vocabulary_by_rows_and_the_picks_recombine_to_the_full_argmax():
+    """Vocabulary-parallel head on the host side: local geometry, the head shard, and the rule the ranks' (best logit, token)
+    picks are merged by (largest logit, lowest token on ties) against the full-row argmax of the oracle."""
+    cfg = helpers.TINY_Q
+    world = 4
+    locals_ = [tp.local_config(dict(cfg, kv_heads=4, q_heads=8), world, shard_head=True, rank=r) for r in range(world)]
+    assert [c["vocab"] for c in locals_] == [512] * 4 and all(c["vocab_global"] == 2048 for c in locals_)
+    assert [c["head_first_row"] for c in locals_] == [0, 512, 1024, 1536]
+    assert "vocab_global" not in tp.local_config(cfg, 2)  # replicated head: nothing changes
+    with pytest.raises(ValueError, match="vocab"):
+        tp.local_config(dict(cfg, vocab=2049), 2, shard_head=True)
+    weights = helpers.make_weights(cfg, seed=1, codec=gv.Q4_0)
+    shards = [tp.shard_weights(weights, cfg, r, 2, shard_head=True) for r in range(2)]
+    packed, n, k = weights["head"]
+    for r, shard in enumerate(shards):
+        got, rows, cols = shard["head"]
+        assert (rows, cols) == (n // 2, k)
+        np.testing.assert_array_equal(got, packed[r * n // 2:(r + 1) * n // 2])
+    assert tp.shard_weights(weights, cfg, 0, 2)["head"][0] is packed
+    # merging picks: ties across ranks go to the lower token
+    rng = np.random.default_rng(3)
+    logits = rng.normal(size=(5, 2048)).astype(np.float32)
+    logits[1, 1700] = logits[1, 40] = logits[1].max() + 1  # the same maximum on rank 0 and rank 3
+    per = 2048 // world
+    picks = [[(float(row[r * per:(r + 1) * per].max()), r * per + int(row[r * per:(r + 1) * per].argmax())) for r in range(world)] for row in logits]
+    merged = [min(p, key=lambda vt: (-vt[0], vt[1]))[1] for p in picks]
+    assert merged == [orc.argmax(row) for row in logits] and merged[1] == 40
