@@ -493,9 +493,16 @@ def run_tp_70b(args, rank, world, rt, et, torch, dist, steps, warmup):
         full["layers"] = args.layers
     shard_head = world > 1 and args.tp_head == "sharded"
     model = tensor_parallel.local_config(full, world, shard_head=shard_head, rank=rank)
+    if world == 1 and args.rank_of > 1:
+        # one rank's share of the work of a tensor-parallel group of that size, alone on one GPU and without the exchange:
+        # what is left of a real rank's step time after this is communication and waiting for peers
+        model = tensor_parallel.local_config(full, args.rank_of, shard_head=args.tp_head == "sharded", rank=0)
+        model.pop("vocab_global", None)
+        model.pop("head_first_row", None)
     B, K, W, chunk = 64, steps, warmup, 256
     rng = np.random.default_rng(4)  # the same contexts and tokens on every rank
-    lo, hi = (1024, 8192) if world > 1 else (256, 1024)  # one GPU: 138 GB of weights leave room for an eighth of the KV
+    whole_model_on_one_gpu = world == 1 and args.rank_of <= 1
+    lo, hi = (256, 1024) if whole_model_on_one_gpu else (1024, 8192)  # one GPU: 138 GB of weights leave room for an eighth of the KV
     ctx = np.sort((rng.integers(lo, hi + 1, size=B) // chunk) * chunk)[::-1].copy()
     max_tokens = ((int(ctx.sum()) + B * (W + K + 2 * BLOCK)) // BLOCK + B) * BLOCK
     dec = build_decoder(rt, et, torch, model, B, max_tokens, seed=40 + rank, shared_seed=4)
@@ -527,7 +534,7 @@ def run_tp_70b(args, rank, world, rt, et, torch, dist, steps, warmup):
         for s in seqs[:active]:
             s.commit(filler)
     del kv
-    tok = rng.integers(0, full["vocab"], size=B).astype(np.uint32)
+    tok = rng.integers(0, model.get("vocab_global", model["vocab"]), size=B).astype(np.uint32)
     sampler = ClockSampler(local)
     if W:
         out, _ = dec.generate_greedy(pool, seqs, tok, W)
@@ -565,13 +572,15 @@ def run_tp_70b(args, rank, world, rt, et, torch, dist, steps, warmup):
         "tp": world, "steps": K, "warmup": W, "ms_per_step": 1000.0 * seconds / K, "scaling": "strong",
         "config": {"workload": f"llama3-70b-shape Q4_0 paged decode: {full['layers']} layers, batch {B}, contexts {int(ctx.min())}.."
                                f"{int(ctx.max())} (mean {ctx.mean():.0f}) written directly into the pages, {K} greedy steps",
-                   "parallelism": "one GPU holds the whole model" if world == 1 else
+                   "parallelism": (f"one rank's share of a tp{args.rank_of} group, alone and without the exchange" if args.rank_of > 1 else
+                                   "one GPU holds the whole model") if world == 1 else
                                   f"tp{world}: rows of q/k/v/gate/up and columns of o/down cut over the ranks, {allreduce} all-reduce of "
                                   "[batch, d_model] f32 after o and down (split-K partials summed in the same kernel), head "
                                   + ("cut by rows, (logit, token) picks exchanged" if shard_head else "replicated")},
         "launches_per_step": launches, "all_reduce": allreduce, "ranks_agree_on_tokens": agree,
-        "step_roofline": {"algorithmic_bytes_per_step_all_ranks": step_bytes, "achieved_gbs_per_rank": step_bytes / world * K / seconds / 1e9,
-                          "frac_of_" + peak_kind + "_per_rank": step_bytes / world * K / seconds / 1e9 / peaks["hbm_gbs"]},
+        "step_roofline": {"algorithmic_bytes_per_step_all_ranks": step_bytes,
+                          "achieved_gbs_per_rank": step_bytes / max(world, args.rank_of, 1) * K / seconds / 1e9,
+                          "frac_of_" + peak_kind + "_per_rank": step_bytes / max(world, args.rank_of, 1) * K / seconds / 1e9 / peaks["hbm_gbs"]},
         "clocks": clocks}
 
 
@@ -803,13 +812,18 @@ def main():
     ap.add_argument("--tp-head", default="sharded", choices=["sharded", "replicated"],
                     help="tensor parallel: the head cut by rows over the ranks (every rank scores vocab / N tokens) or whole on every rank")
     ap.add_argument("--layers", type=int, default=0, help="debug: fewer layers than the named shape (the result is then not a bench value)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "decode-70b"],
-                    help="decode: the headline 8B-shape decode step (the bench contract) with the kernel rooflines, microbenchmarks and, at "
-                         "N > 1, the 70B tensor-parallel run in the same line; decode-70b: only the 70B shape over --gpus ranks")
+    ap.add_argument("--workload", default="decode", choices=["decode", "decode-70b", "kernels"],
+                    help="decode: the headline 8B-shape decode step (the bench contract) with the kernel rooflines, microbenchmarks and the "
+                         "70B tensor-parallel run in the same line; decode-70b: only the 70B shape over --gpus ranks; kernels: only the "
+                         "stand-alone kernel timings (the linears at --vectors rows, the attention launches), e.g. under a profiler")
+    ap.add_argument("--vectors", type=int, default=BATCH, help="--workload kernels: input rows of the linears")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-microbench", action="store_true", help="skip the quantized-matmul and paged-attention microbenchmark tables")
     ap.add_argument("--no-tp70b", action="store_true", help="skip the 70B-shape run (tensor parallel over the N ranks) that fills the line's tp object")
     ap.add_argument("--tp-steps", type=int, default=32, help="decode steps of the 70B run")
+    ap.add_argument("--rank-of", type=int, default=0,
+                    help="--workload decode-70b on one GPU: run one rank's share of a tensor-parallel group of this size without the "
+                         "exchange (a per-rank compute baseline, e.g. under a profiler)")
     ap.add_argument("--parallelism", default="replicas", choices=["replicas", "tp"],
                     help="N > 1: N independent replicas, each decoding its own batch (weak scaling; the 8B shape fits one GPU), or "
                          "one tensor-parallel model over the ranks (strong scaling)")
@@ -823,6 +837,22 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
         run_reference_arm(args, rank)
+        return
+    if args.workload == "kernels":
+        import torch
+        import effect_torch_b200 as et
+        torch.cuda.set_device(0)
+        rt = et.Runtime(0)
+        peaks, peak_kind = measured_peaks()
+        line = {"metric": "kernel HBM GB/s vs peak", "unit": "GB/s", "n_gpus": 1, "data": "synthetic",
+                "config": {"workload": f"stand-alone kernel timings at {args.vectors} vectors (graph replays over more than L2 of weights / KV)"},
+                "roofline_by_projection": projection_rooflines(rt, et, torch, MODEL, args.vectors, peaks, peak_kind)}
+        if not args.no_microbench:
+            ctx_step = np.full(BATCH, PROMPT + 19)
+            line["roofline_attention"] = time_attention(rt, et, torch, BATCH, MODEL["q_heads"], MODEL["kv_heads"], MODEL["head_dim"], ctx_step,
+                                                        int(np.ceil((ctx_step + 1) / BLOCK).sum()) * 6 + 256, peaks, peak_kind,
+                                                        f"the decode step's launch: {BATCH} sequences at context {PROMPT + 19}")
+        emit(line)
         return
     if args.workload == "decode-70b":
         import torch

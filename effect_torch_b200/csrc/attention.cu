@@ -14,6 +14,7 @@
 #include <cuda_fp16.h>
 
 #include <algorithm>
+#include <type_traits>
 
 #include "chain.cuh"
 #include "kernels.h"
@@ -266,6 +267,8 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 struct AttnArgs {
   const void* k;
   const void* v;
+  const float* k_scale;    // u8 tier: one f32 per (page, head, slot)
+  const float* v_scale;
   const float* q;          // [B, Hq, D] f32
   const LaneInfo* lanes;
   const int* tables;
@@ -291,11 +294,17 @@ __device__ __forceinline__ int swizzled_offset(int row, int chunk) {  // in byte
 // CHUNK = true: a chunk of a.tokens query tokens per lane (chunked prefill, napi/mod.rs:3420-3477 semantics: token t of
 // the chunk attends positions up to cursor + t); the 16 MMA rows are (token, query head) pairs, 16 / G tokens per CTA,
 // grid.x counts row tiles and every row carries its own causal bound.
-template <int D, bool BF16, bool CHUNK>
+// U8: the int8 tier (code - 128) * scale with one scale per cached row (napi/mod.rs:3474-3476): pages travel as bytes, a warp
+// widens the page it is about to use to f16 integers in a staging page of its own, and the row scales multiply the score
+// columns (K) and the probabilities before P V (V), so the tensor core only ever sees exact small integers.
+template <int D, bool BF16, bool CHUNK, bool U8>
 __global__ void __launch_bounds__(kAttnWarps * 32) attention_mma_kernel(AttnArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
-  constexpr int PAGE_BYTES = kPageTokens * D * 2;
-  constexpr int STAGE_BYTES = 2 * PAGE_BYTES;
+  constexpr int PAGE_BYTES = kPageTokens * D * 2;               // one page as MMA operands (f16 / bf16)
+  constexpr int RAW_PAGE = U8 ? kPageTokens * D : PAGE_BYTES;   // one page as cached
+  constexpr int SCALE_BYTES = U8 ? kPageTokens * 4 : 0;         // its row scales
+  constexpr int STAGE_BYTES = 2 * (RAW_PAGE + SCALE_BYTES);
+  constexpr int WARP_BYTES = kAttnStages * STAGE_BYTES + (U8 ? 2 * PAGE_BYTES : 0);  // ring (+ the widened K and V page)
   constexpr int CHUNKS = D / 8;    // 16-byte chunks per row
   constexpr int KSTEPS = D / 16;   // k16 steps of the QK^T product
   constexpr int DTILES = D / 8;    // n-tiles of the PV product
@@ -334,27 +343,66 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attention_mma_kernel(AttnArgs
   const int p0 = first_page + split * a.pages_per_split;
   const int p1 = CHUNK ? last_page : min(last_page, p0 + a.pages_per_split);
 
-  unsigned char* my_smem = smem + (size_t)warp * kAttnStages * STAGE_BYTES;
+  unsigned char* my_smem = smem + (size_t)warp * WARP_BYTES;
+  unsigned char* wide = my_smem + kAttnStages * STAGE_BYTES;  // U8: this warp's widened K page, then V page
   const int* table = a.tables + info.table_offset;
-  const size_t page_stride = (size_t)a.kv_heads * PAGE_BYTES;  // bytes between consecutive pages
-  const unsigned char* kbase = reinterpret_cast<const unsigned char*>(a.k) + (size_t)kv_head * PAGE_BYTES;
-  const unsigned char* vbase = reinterpret_cast<const unsigned char*>(a.v) + (size_t)kv_head * PAGE_BYTES;
+  const size_t page_stride = (size_t)a.kv_heads * RAW_PAGE;  // bytes between consecutive pages
+  const unsigned char* kbase = reinterpret_cast<const unsigned char*>(a.k) + (size_t)kv_head * RAW_PAGE;
+  const unsigned char* vbase = reinterpret_cast<const unsigned char*>(a.v) + (size_t)kv_head * RAW_PAGE;
 
   auto issue = [&](int page_index, int stage) {
     if (page_index < p1) {
       const size_t off = (size_t)table[page_index] * page_stride;
       unsigned char* ks = my_smem + stage * STAGE_BYTES;
-      unsigned char* vs = ks + PAGE_BYTES;
+      unsigned char* vs = ks + RAW_PAGE;
+      if (U8) {
+        // bytes as they are (row-major), then the 16 row scales of K and of V
 #pragma unroll
-      for (int i = 0; i < (kPageTokens * CHUNKS) / 32; ++i) {
-        const int c = lane + 32 * i;  // chunk index within the page
-        const int row = c / CHUNKS, chunk = c % CHUNKS;
-        const int so = swizzled_offset<D>(row, chunk);
-        cp_async16(ks + so, kbase + off + (size_t)c * 16);
-        cp_async16(vs + so, vbase + off + (size_t)c * 16);
+        for (int i = 0; i < RAW_PAGE / 16 / 32; ++i) {
+          const int c = lane + 32 * i;
+          cp_async16(ks + c * 16, kbase + off + (size_t)c * 16);
+          cp_async16(vs + c * 16, vbase + off + (size_t)c * 16);
+        }
+        if (lane < 8) {
+          const size_t si = ((size_t)table[page_index] * a.kv_heads + kv_head) * kPageTokens;  // 16 floats = 4 chunks each
+          const float* src = (lane < 4 ? a.k_scale : a.v_scale) + si + (lane & 3) * 4;
+          cp_async16(my_smem + stage * STAGE_BYTES + 2 * RAW_PAGE + lane * 16, src);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < (kPageTokens * CHUNKS) / 32; ++i) {
+          const int c = lane + 32 * i;  // chunk index within the page
+          const int row = c / CHUNKS, chunk = c % CHUNKS;
+          const int so = swizzled_offset<D>(row, chunk);
+          cp_async16(ks + so, kbase + off + (size_t)c * 16);
+          cp_async16(vs + so, vbase + off + (size_t)c * 16);
+        }
       }
     }
     cp_async_commit();  // always commit so group counting stays uniform
+  };
+  // U8: bytes of one cached page -> f16 integers (code - 128) in the swizzled operand layout
+  auto widen = [&](const unsigned char* raw, unsigned char* dst) {
+#pragma unroll
+    for (int i = 0; i < RAW_PAGE / 16 / 32; ++i) {
+      const int c = lane + 32 * i;  // 16 codes: row c / (D/16), columns 16 * (c % (D/16)) ...
+      const int row = c / (D / 16), chunk = 2 * (c % (D / 16));
+      const uint4 codes = *reinterpret_cast<const uint4*>(raw + c * 16);
+      const uint32_t w[4] = {codes.x, codes.y, codes.z, codes.w};
+      uint32_t h[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        // bytes b0..b3 -> halves 1024 + b, minus 1152 = b - 128 (exact)
+        const __half2 bias = __floats2half2_rn(1152.0f, 1152.0f);
+        uint32_t lo_bits = __byte_perm(w[j], 0x64646464u, 0x4140), hi_bits = __byte_perm(w[j], 0x64646464u, 0x4342);
+        const __half2 lo = __hsub2(*reinterpret_cast<__half2*>(&lo_bits), bias);
+        const __half2 hi = __hsub2(*reinterpret_cast<__half2*>(&hi_bits), bias);
+        h[2 * j] = *reinterpret_cast<const uint32_t*>(&lo);
+        h[2 * j + 1] = *reinterpret_cast<const uint32_t*>(&hi);
+      }
+      *reinterpret_cast<uint4*>(dst + swizzled_offset<D>(row, chunk)) = make_uint4(h[0], h[1], h[2], h[3]);
+      *reinterpret_cast<uint4*>(dst + swizzled_offset<D>(row, chunk + 1)) = make_uint4(h[4], h[5], h[6], h[7]);
+    }
   };
 
   // Q fragments: rows 0..G-1 = query heads of this KV head, scaled into the exp2 domain
@@ -398,7 +446,15 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attention_mma_kernel(AttnArgs
     cp_async_wait<kAttnStages - 1>();
     __syncwarp();
     const unsigned char* ks_page = my_smem + stage * STAGE_BYTES;
-    const unsigned char* vs_page = ks_page + PAGE_BYTES;
+    const unsigned char* vs_page = ks_page + RAW_PAGE;
+    const float* page_scales = reinterpret_cast<const float*>(my_smem + stage * STAGE_BYTES + 2 * RAW_PAGE);  // U8: K rows, then V rows
+    if (U8) {
+      widen(ks_page, wide);
+      widen(vs_page, wide + PAGE_BYTES);
+      __syncwarp();
+      ks_page = wide;
+      vs_page = wide + PAGE_BYTES;
+    }
 
     // S = Q K^T : two n-tiles of 8 tokens
     float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
@@ -410,6 +466,11 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attention_mma_kernel(AttnArgs
       ldmatrix_x4(kf, ks_page + swizzled_offset<D>(row, chunk));
       mma_16816<BF16>(s0, qf[ks], kf[0], kf[1]);
       mma_16816<BF16>(s1, qf[ks], kf[2], kf[3]);
+    }
+    if (U8) {  // score of token column c carries that cached row's K scale
+      const float ka0 = page_scales[2 * t], ka1 = page_scales[2 * t + 1], kb0 = page_scales[2 * t + 8], kb1 = page_scales[2 * t + 9];
+      s0[0] *= ka0; s0[1] *= ka1; s0[2] *= ka0; s0[3] *= ka1;
+      s1[0] *= kb0; s1[1] *= kb1; s1[2] *= kb0; s1[3] *= kb1;
     }
     // mask positions outside [begin, end)
     const int base_pos = page_index * kPageTokens;
@@ -441,6 +502,12 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attention_mma_kernel(AttnArgs
     l_lo = l_lo * alpha_lo + (p0v[0] + p0v[1] + p1v[0] + p1v[1]);
     l_hi = l_hi * alpha_hi + (p0v[2] + p0v[3] + p1v[2] + p1v[3]);
     m_lo = mn_lo; m_hi = mn_hi;
+    if (U8) {  // V row scales ride on the probabilities; the denominators above stay unscaled
+      const float* vsc = page_scales + kPageTokens;
+      const float va0 = vsc[2 * t], va1 = vsc[2 * t + 1], vb0 = vsc[2 * t + 8], vb1 = vsc[2 * t + 9];
+      p0v[0] *= va0; p0v[1] *= va1; p0v[2] *= va0; p0v[3] *= va1;
+      p1v[0] *= vb0; p1v[1] *= vb1; p1v[2] *= vb0; p1v[3] *= vb1;
+    }
     uint32_t pf[4];
     pf[0] = pack2<BF16>(p0v[0], p0v[1]);  // row g,   tokens 2t, 2t+1
     pf[1] = pack2<BF16>(p0v[2], p0v[3]);  // row g+8
@@ -546,7 +613,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ partial, int q_
 bool attention_mma_supported(const PoolView& pool, int q_heads, int tokens) {
   const int G = pool.kv_heads > 0 ? q_heads / pool.kv_heads : 0;
   return tokens >= 1 && pool.block_size == kPageTokens && (pool.head_dim == 64 || pool.head_dim == 128) &&
-         (pool.dtype == kKvF16 || pool.dtype == kKvBF16) && G >= 1 && G <= 16 && q_heads % pool.kv_heads == 0;
+         (pool.dtype == kKvF16 || pool.dtype == kKvBF16 || pool.dtype == kKvU8) && G >= 1 && G <= 16 && q_heads % pool.kv_heads == 0;
 }
 
 AttnPlan plan_attention(int batch, int q_heads, int kv_heads, int head_dim, int max_pages, int sm_count) {
@@ -569,13 +636,15 @@ size_t plan_attention_max_scratch(int batch, int q_heads, int kv_heads, int head
   return need;
 }
 
-template <int D, bool BF16, bool CHUNK>
+template <int D, bool BF16, bool CHUNK, bool U8>
 static cudaError_t launch_attention_mma_t(const PoolView& pool, const AttnArgs& args, int batch, int grid_x,
                                           cudaStream_t stream) {
-  constexpr size_t ring = (size_t)kAttnWarps * kAttnStages * 2 * kPageTokens * D * 2;
+  constexpr size_t page = (size_t)kPageTokens * D * 2;
+  constexpr size_t ring = U8 ? (size_t)kAttnWarps * (kAttnStages * 2 * (kPageTokens * D + kPageTokens * 4) + 2 * page)
+                             : (size_t)kAttnWarps * kAttnStages * 2 * page;
   constexpr size_t merge = (size_t)kAttnWarps * 16 * (D + 2) * sizeof(float);
   constexpr size_t smem = ring > merge ? ring : merge;
-  auto kernel = attention_mma_kernel<D, BF16, CHUNK>;
+  auto kernel = attention_mma_kernel<D, BF16, CHUNK, U8>;
   const cudaError_t attr = opt_in_shared_memory(kernel, smem);
   if (attr != cudaSuccess) return attr;
   dim3 grid((unsigned)grid_x, (unsigned)pool.kv_heads, (unsigned)batch);
@@ -597,25 +666,32 @@ cudaError_t launch_attention_mma(const PoolView& pool, const float* q, const Lan
   args.scale_log2 = (float)(scale * 1.4426950408889634);
   args.op_window = op_window;
   args.tokens = tokens;
+  args.k_scale = pool.k_scale;
+  args.v_scale = pool.v_scale;
   cudaError_t e;
-  const bool bf = pool.dtype == kKvBF16;
+  // the tier and the head width pick the instantiation; `chunk` the row mapping
+  auto dispatch = [&](auto chunk_tag, int grid_x) {
+    constexpr bool CHUNK = decltype(chunk_tag)::value;
+    const bool wide = pool.head_dim == 128;
+    if (pool.dtype == kKvU8)
+      return wide ? launch_attention_mma_t<128, false, CHUNK, true>(pool, args, batch, grid_x, stream)
+                  : launch_attention_mma_t<64, false, CHUNK, true>(pool, args, batch, grid_x, stream);
+    if (pool.dtype == kKvBF16)
+      return wide ? launch_attention_mma_t<128, true, CHUNK, false>(pool, args, batch, grid_x, stream)
+                  : launch_attention_mma_t<64, true, CHUNK, false>(pool, args, batch, grid_x, stream);
+    return wide ? launch_attention_mma_t<128, false, CHUNK, false>(pool, args, batch, grid_x, stream)
+                : launch_attention_mma_t<64, false, CHUNK, false>(pool, args, batch, grid_x, stream);
+  };
   if (tokens > 1) {
     // a prefill chunk: one CTA per tile of 16 / G tokens, no split over the pages
     const int G = q_heads / pool.kv_heads;
     const int per_tile = std::max(1, 16 / G);
-    const int tiles = (tokens + per_tile - 1) / per_tile;
-    if (pool.head_dim == 128) e = bf ? launch_attention_mma_t<128, true, true>(pool, args, batch, tiles, stream)
-                                     : launch_attention_mma_t<128, false, true>(pool, args, batch, tiles, stream);
-    else e = bf ? launch_attention_mma_t<64, true, true>(pool, args, batch, tiles, stream)
-                : launch_attention_mma_t<64, false, true>(pool, args, batch, tiles, stream);
+    e = dispatch(std::true_type(), (tokens + per_tile - 1) / per_tile);
     if (e != cudaSuccess) return e;
     if (launches) ++*launches;
     return cudaSuccess;
   }
-  if (pool.head_dim == 128) e = bf ? launch_attention_mma_t<128, true, false>(pool, args, batch, plan.splits, stream)
-                                   : launch_attention_mma_t<128, false, false>(pool, args, batch, plan.splits, stream);
-  else e = bf ? launch_attention_mma_t<64, true, false>(pool, args, batch, plan.splits, stream)
-              : launch_attention_mma_t<64, false, false>(pool, args, batch, plan.splits, stream);
+  e = dispatch(std::false_type(), plan.splits);
   if (e != cudaSuccess) return e;
   if (launches) ++*launches;
   if (plan.splits > 1) {
@@ -687,6 +763,24 @@ __global__ void rope_append_kernel(PoolView pool, const float* __restrict__ qkv,
   const int page = tables[info.table_offset + pos / pool.block_size], slot = pos % pool.block_size;
   const size_t dst = pool_elem(pool, page, kv_head, slot);
   void* slab = is_k ? pool.k : pool.v;
+  if (pool.dtype == kKvU8) {
+    // the int8 tier: one scale per cached row, as kv_append_kernel (pool.rs:224-240)
+    __shared__ float red[32];
+    float amax = fmaxf(fabsf(r0), fabsf(r1));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = 0.0f;
+    for (int w = 0; w < (int)((blockDim.x + 31) >> 5); ++w) amax = fmaxf(amax, red[w]);
+    const float scale = __fadd_rn(__fdiv_rn(amax, 127.0f), 1e-12f);
+    if (threadIdx.x == 0) (is_k ? pool.k_scale : pool.v_scale)[pool_scale_index(pool, page, kv_head, slot)] = scale;
+    const float c0 = fminf(fmaxf(roundf(__fdiv_rn(r0, scale)), -127.0f), 127.0f) + 128.0f;
+    const float c1 = fminf(fmaxf(roundf(__fdiv_rn(r1, scale)), -127.0f), 127.0f) + 128.0f;
+    reinterpret_cast<uint8_t*>(slab)[dst + i0] = (uint8_t)c0;
+    reinterpret_cast<uint8_t*>(slab)[dst + i1] = (uint8_t)c1;
+    return;
+  }
   pool_store(pool, slab, dst + i0, r0);
   pool_store(pool, slab, dst + i1, r1);
 }

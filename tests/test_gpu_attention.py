@@ -156,7 +156,7 @@ def test_prefix_cache_and_prefill_match():
     assert g3.prefillMatch([1, 2, 3]) == 0
 
 
-@pytest.mark.parametrize("tier,otier,tol", [(et.KV_F16, orc.F16, REL_TOL), (et.KV_BF16, orc.BF16, 2e-2)])
+@pytest.mark.parametrize("tier,otier,tol", [(et.KV_F16, orc.F16, REL_TOL), (et.KV_BF16, orc.BF16, 2e-2), (et.KV_U8, orc.U8, REL_TOL)])
 @pytest.mark.parametrize("Hq,Hkv,D", [(32, 8, 128), (8, 1, 128), (4, 2, 64)])
 def test_tensor_core_decode_attention_matches_the_oracle(tier, otier, tol, Hq, Hkv, D):
     """Flash-decoding kernel vs the f64 oracle on ragged contexts (one lane crosses several splits, one is a single

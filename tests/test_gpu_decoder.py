@@ -81,10 +81,13 @@ def test_tiny_model_teacher_forced_logits(tiny):
 
 
 @pytest.mark.parametrize("codec", [orc.Q4_0, orc.Q8_0])
-@pytest.mark.parametrize("kv_dtype,okv,tol", [(et.KV_F16, orc.F16, LOGIT_TOL), (et.KV_F32, orc.F32, LOGIT_TOL)])
+@pytest.mark.parametrize("kv_dtype,okv,tol", [(et.KV_F16, orc.F16, LOGIT_TOL), (et.KV_F32, orc.F32, LOGIT_TOL), (et.KV_U8, orc.U8, 1e-2)])
 def test_quantized_model_on_the_tensor_core_path(codec, kv_dtype, okv, tol):
-    """Block-quantized projections on the tiled MMA kernels (and, with an f16 pool, the flash-decoding kernel)
-    against the oracle running the same packed bytes: teacher-forced logits within 2e-3."""
+    """Block-quantized projections on the tiled MMA kernels (and, with an f16 or int8 pool, the flash-decoding kernel)
+    against the oracle running the same packed bytes: teacher-forced logits within 2e-3. The int8 tier gets 1e-2: the f16
+    linears move a K / V row by about 1e-3, which flips codes of its int8 image by one step (1/127 of the row's maximum),
+    so the two sides attend over slightly different caches; on identical cache contents the int8 attention itself holds
+    2e-3 (tests/test_gpu_attention.py)."""
     cfg = helpers.TINY_Q
     w = helpers.make_weights(cfg, seed=3, codec=codec)
     rng = np.random.default_rng(2)
