@@ -521,7 +521,9 @@ def run_tp_70b(args, rank, world, rt, et, torch, dist, steps, warmup):
             table = [torch.empty_like(mine) for _ in range(world)]
             dist.all_gather(table, mine)
             dec.use_peer_allreduce([bytes(t.cpu().tolist()) for t in table])
-            allreduce = "peer memory, one shot" if world < 4 else "peer memory, reduce-scatter + all-gather"
+            forced = os.environ.get("ETC_TP_TWO_SHOT")
+            two_shot = world >= 8 if forced is None else forced != "0"
+            allreduce = "peer memory, reduce-scatter + all-gather" if two_shot else "peer memory, one shot"
     pool = et.NativeKvPool(rt, model["layers"], model["kv_heads"], model["head_dim"], max_tokens, BLOCK, et.KV_F16)
     seqs = [pool.makeSequence() for _ in range(B)]
     kv = torch.randn((B, model["kv_heads"], chunk, model["head_dim"]), device="cuda", dtype=torch.float32)
@@ -852,6 +854,9 @@ def main():
             line["roofline_attention"] = time_attention(rt, et, torch, BATCH, MODEL["q_heads"], MODEL["kv_heads"], MODEL["head_dim"], ctx_step,
                                                         int(np.ceil((ctx_step + 1) / BLOCK).sum()) * 6 + 256, peaks, peak_kind,
                                                         f"the decode step's launch: {BATCH} sequences at context {PROMPT + 19}")
+            ctx_c2 = np.random.default_rng(1).integers(128, 4097, size=64)
+            line["attention_microbench"] = time_attention(rt, et, torch, 64, 32, 8, 128, ctx_c2, 65536, peaks, peak_kind,
+                                                          "64 sequences, contexts ~U[128, 4096], pool of 65536 pages")
         emit(line)
         return
     if args.workload == "decode-70b":

@@ -405,6 +405,14 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attention_mma_kernel(AttnArgs
     }
   };
 
+  // this warp's pages: p0 + warp, p0 + warp + 4, ...; the first copies are in flight while the query rows are fetched
+  int next_issue = p0 + warp;
+#pragma unroll
+  for (int s = 0; s < kAttnStages - 1; ++s) {
+    issue(next_issue, s);
+    next_issue += kAttnWarps;
+  }
+
   // Q fragments: rows 0..G-1 = query heads of this KV head, scaled into the exp2 domain
   uint32_t qf[KSTEPS][4];
   {
@@ -432,13 +440,6 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attention_mma_kernel(AttnArgs
     for (int j = 0; j < 4; ++j) o[i][j] = 0.0f;
   float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.0f, l_hi = 0.0f;  // rows g and g+8
 
-  // this warp's pages: p0 + warp, p0 + warp + 4, ...
-  int next_issue = p0 + warp;
-#pragma unroll
-  for (int s = 0; s < kAttnStages - 1; ++s) {
-    issue(next_issue, s);
-    next_issue += kAttnWarps;
-  }
   int stage = 0;
   for (int page_index = p0 + warp; page_index < p1; page_index += kAttnWarps) {
     issue(next_issue, (stage + kAttnStages - 1) % kAttnStages);

@@ -94,27 +94,32 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const float* __restrict__ 
 // B-operand layout of the tcgen05 linear, instead of f32 row-major.
 // SUM = true first adds a projection's split-K partials (summed in split order) onto the row and stores it back: the
 // residual update the projection's own sum kernel would have done.
-template <bool XH, bool SUM>
-__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* x, const float* __restrict__ weight,
-                                                           double eps, int n, float* __restrict__ out, __half* __restrict__ out_xh,
-                                                           int xh_nv, DeferredSum sum_in, float* x_out) {
+template <bool XH, bool SUM, int THREADS>
+__global__ void __launch_bounds__(THREADS) rmsnorm_rows_kernel(const float* x, const float* __restrict__ weight,
+                                                               double eps, int n, float* __restrict__ out, __half* __restrict__ out_xh,
+                                                               int xh_nv, DeferredSum sum_in, float* x_out) {
   chain_release();  // the next kernel of the step may be scheduled; it waits for this one before touching memory
   chain_wait();
-  __shared__ double partial[8];
+  constexpr int ITEMS = 2048 / THREADS;  // float4 chunks per thread: rows of up to 8192 values
+  __shared__ double partial[THREADS / 32];
   __shared__ double scale_s;
   const int row = blockIdx.x;
   const float4* src = reinterpret_cast<const float4*>(x + (size_t)row * n);
   const int chunks = n / 4;
-  float4 v[8];
+  float4 v[ITEMS];
   double sum = 0.0;
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const int c = threadIdx.x + 256 * j;
+  for (int j = 0; j < ITEMS; ++j) {
+    const int c = threadIdx.x + THREADS * j;
     v[j] = c < chunks ? src[c] : make_float4(0.f, 0.f, 0.f, 0.f);
     if (SUM && c < chunks) {
+      // all splits' loads are independent: issued together, added in split order
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      const float* base = sum_in.partials + (size_t)row * sum_in.rows_padded + 4 * c;
+      const size_t split_stride = (size_t)sum_in.vpad * sum_in.rows_padded;
+#pragma unroll 4
       for (int s = 0; s < sum_in.splits; ++s) {
-        const float4 p = *reinterpret_cast<const float4*>(sum_in.partials + ((size_t)s * sum_in.vpad + row) * sum_in.rows_padded + 4 * c);
+        const float4 p = *reinterpret_cast<const float4*>(base + (size_t)s * split_stride);
         acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
       }
       v[j].x += acc.x; v[j].y += acc.y; v[j].z += acc.z; v[j].w += acc.w;
@@ -129,14 +134,14 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* x, const
   __syncthreads();
   if (threadIdx.x == 0) {
     double total = 0.0;
-    for (int i = 0; i < 8; ++i) total += partial[i];
+    for (int i = 0; i < THREADS / 32; ++i) total += partial[i];
     scale_s = 1.0 / sqrt(total / (double)n + eps);
   }
   __syncthreads();
   const double scale = scale_s;
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const int c = threadIdx.x + 256 * j;
+  for (int j = 0; j < ITEMS; ++j) {
+    const int c = threadIdx.x + THREADS * j;
     if (c >= chunks) continue;
     float4 w = weight ? reinterpret_cast<const float4*>(weight)[c] : make_float4(1.f, 1.f, 1.f, 1.f);
     const float r0 = (float)__dmul_rn(__dmul_rn((double)v[j].x, scale), (double)w.x);
@@ -163,7 +168,7 @@ cudaError_t launch_rmsnorm(const float* x, const float* weight, double eps, int6
                            cudaStream_t stream) {
   if (rows == 0) return cudaSuccess;
   if (rmsnorm_fast_ok(x, weight, n) && ((uintptr_t)out % 16) == 0)
-    return launch_chained(rmsnorm_rows_kernel<false, false>, dim3((unsigned)rows), dim3(256), 0, stream, x, weight, eps, (int)n, out, (__half*)nullptr, 32,
+    return launch_chained(rmsnorm_rows_kernel<false, false, 256>, dim3((unsigned)rows), dim3(256), 0, stream, x, weight, eps, (int)n, out, (__half*)nullptr, 32,
                           DeferredSum(), (float*)nullptr);
   else
     rmsnorm_kernel<<<(unsigned)rows, 256, 0, stream>>>(x, weight, eps, n, out);
@@ -174,7 +179,7 @@ cudaError_t launch_rmsnorm_xh8(const float* x, const float* weight, double eps, 
                                cudaStream_t stream, int xh_nv) {
   if (rows == 0) return cudaSuccess;
   if (rows > xh_nv || n % 8 != 0 || !rmsnorm_fast_ok(x, weight, n)) return cudaErrorInvalidValue;
-  return launch_chained(rmsnorm_rows_kernel<true, false>, dim3((unsigned)rows), dim3(256), 0, stream, x, weight, eps, (int)n, (float*)nullptr, out_xh, xh_nv,
+  return launch_chained(rmsnorm_rows_kernel<true, false, 256>, dim3((unsigned)rows), dim3(256), 0, stream, x, weight, eps, (int)n, (float*)nullptr, out_xh, xh_nv,
                         DeferredSum(), (float*)nullptr);
 }
 
@@ -183,7 +188,7 @@ cudaError_t launch_sum_rmsnorm_xh8(float* x, const DeferredSum& sum, const float
   if (rows == 0) return cudaSuccess;
   if (rows > xh_nv || n % 8 != 0 || !rmsnorm_fast_ok(x, weight, n) || sum.splits <= 0 || sum.rows_padded % 4 != 0 || rows > sum.vpad)
     return cudaErrorInvalidValue;
-  return launch_chained(rmsnorm_rows_kernel<true, true>, dim3((unsigned)rows), dim3(256), 0, stream, (const float*)x, weight, eps, (int)n,
+  return launch_chained(rmsnorm_rows_kernel<true, true, 1024>, dim3((unsigned)rows), dim3(1024), 0, stream, (const float*)x, weight, eps, (int)n,
                         (float*)nullptr, out_xh, xh_nv, sum, x);
 }
 

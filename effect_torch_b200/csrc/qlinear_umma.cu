@@ -100,6 +100,34 @@ __global__ void __launch_bounds__(UmmaCfg<NV>::kThreads) qlinear_umma_kernel(Umm
   const int kb1 = min(a.kblocks, kb0 + a.blocks_per_split);
   const int nstages = (kb1 - kb0 + kStageBlocks - 1) / kStageBlocks;
 
+  // ---- dequant warps: group g = warp / 4 expands stages g, g + kGroups, ...; inside a group warp w owns TMEM lanes 32*(w%4)...
+  const int group = warp >> 2;
+  const int row = (warp & 3) * 32 + lane;  // TMEM lane == row inside the tile
+  const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+  const uint4* qrow = a.quants + ((size_t)tile * a.kblocks) * (kUmmaRows * QW) + (size_t)row * QW;
+  constexpr int SW = kPair ? 2 : 1;  // halves per (row, block) in the scale array
+  const __half* srow = a.scales + (((size_t)tile * a.kblocks) * kUmmaRows + row) * SW;
+  constexpr int PF = 2;  // of this group's stages, held packed in registers ahead of use
+  uint4 qbuf[PF][kStageBlocks][QW];
+  uint32_t sbuf[PF][kStageBlocks];  // one f16 (low half) or a pair
+  auto load_stage = [&](int stage_index, int slot) {
+#pragma unroll
+    for (int b = 0; b < kStageBlocks; ++b) {
+      const int kb = min(kb0 + stage_index * kStageBlocks + b, kb1 - 1);  // clamped: masked at use
+#pragma unroll
+      for (int w = 0; w < QW; ++w) qbuf[slot][b][w] = __ldg(qrow + (size_t)kb * (kUmmaRows * QW) + w);
+      if (kPair) sbuf[slot][b] = __ldg(reinterpret_cast<const uint32_t*>(srow + (size_t)kb * kUmmaRows * 2));
+      else sbuf[slot][b] = (uint32_t)__ldg(reinterpret_cast<const unsigned short*>(srow + (size_t)kb * kUmmaRows));
+    }
+  };
+  const int my_stages = nstages > group ? (nstages - group + kGroups - 1) / kGroups : 0;
+  // the first packed stages are requested before tensor memory and the barriers are set up: weights depend on nothing
+  if (warp < 4 * kGroups) {
+#pragma unroll
+    for (int p = 0; p < PF; ++p)
+      if (p < my_stages) load_stage(group + p * kGroups, p);
+  }
+
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full_a[s], kDequantThreads);
@@ -120,30 +148,6 @@ __global__ void __launch_bounds__(UmmaCfg<NV>::kThreads) qlinear_umma_kernel(Umm
 
   if (warp < 4 * kGroups) {
     // ------------------------------------------------------------------ dequant warps
-    // group g = warp / 4 expands stages g, g + kGroups, ...; inside a group warp w owns TMEM lanes 32*(w%4)...
-    const int group = warp >> 2;
-    const int row = (warp & 3) * 32 + lane;  // TMEM lane == row inside the tile
-    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    const uint4* qrow = a.quants + ((size_t)tile * a.kblocks) * (kUmmaRows * QW) + (size_t)row * QW;
-    constexpr int SW = kPair ? 2 : 1;  // halves per (row, block) in the scale array
-    const __half* srow = a.scales + (((size_t)tile * a.kblocks) * kUmmaRows + row) * SW;
-    constexpr int PF = 2;  // of this group's stages, held packed in registers ahead of use
-    uint4 qbuf[PF][kStageBlocks][QW];
-    uint32_t sbuf[PF][kStageBlocks];  // one f16 (low half) or a pair
-    auto load_stage = [&](int stage_index, int slot) {
-#pragma unroll
-      for (int b = 0; b < kStageBlocks; ++b) {
-        const int kb = min(kb0 + stage_index * kStageBlocks + b, kb1 - 1);  // clamped: masked at use
-#pragma unroll
-        for (int w = 0; w < QW; ++w) qbuf[slot][b][w] = __ldg(qrow + (size_t)kb * (kUmmaRows * QW) + w);
-        if (kPair) sbuf[slot][b] = __ldg(reinterpret_cast<const uint32_t*>(srow + (size_t)kb * kUmmaRows * 2));
-        else sbuf[slot][b] = (uint32_t)__ldg(reinterpret_cast<const unsigned short*>(srow + (size_t)kb * kUmmaRows));
-      }
-    };
-    const int my_stages = nstages > group ? (nstages - group + kGroups - 1) / kGroups : 0;
-#pragma unroll
-    for (int p = 0; p < PF; ++p)
-      if (p < my_stages) load_stage(group + p * kGroups, p);
     bool ok = true;
     // Software pipeline: stage j is expanded in registers while the TMEM stores of stage j-1 are still in
     // flight; only then are those stores awaited and published, so the store latency hides behind ALU work.

@@ -367,8 +367,8 @@ ETC_API etc_status etc_tp_unique_id(uint8_t* out_id_128_bytes);
 ETC_API etc_status etc_decoder_set_tensor_parallel(etc_decoder* dec, int rank, int world, const uint8_t* id_128_bytes);
 /* Optional, after etc_decoder_set_tensor_parallel and etc_decoder_finalize: replace the NCCL all-reduce by the
  * library's kernel over peer memory (CUDA IPC, plain stores into the peers' regions over NVLink, 2..8 ranks on one
- * node): one shot at 2 ranks (every rank receives all ranks' partial sums), reduce-scatter + all-gather from 4 ranks
- * on; the row-parallel projection's split-K partials are summed inside the same kernel. Every rank exports a
+ * node): one shot up to 4 ranks (every rank receives all ranks' partial sums), reduce-scatter + all-gather at 8; the
+ * row-parallel projection's split-K partials are summed inside the same kernel. Every rank exports a
  * 64-byte handle of its exchange region, the host gathers the handles of all ranks into a table [world][64] (own slot
  * ignored) and every rank imports it. The kernel's wait for its peers is bounded: a rank that never arrives turns
  * into ETC_EXECUTION at the next synchronising call, not into a hang.

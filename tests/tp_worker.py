@@ -2,8 +2,7 @@
 with torch.distributed.run. Every rank builds its shard of a small Q4_0 model; rank 0 also runs the CPU oracle on the
 whole model. Checked: teacher-forced logits against the oracle (2e-3), identical tokens on all ranks, and the
 device-resident greedy loop (CUDA graph with the all-reduces captured) against step-by-step execution: with the NCCL
-all-reduce, with the peer-memory all-reduce (one shot at 2 ranks, reduce-scatter + all-gather from 4 on, and both
-forced), and with a vocabulary-parallel head whose ranks exchange their best logit."""
+all-reduce, with the peer-memory all-reduce (one shot by default at these sizes, reduce-scatter + all-gather forced), and with a vocabulary-parallel head whose ranks exchange their best logit."""
 import os
 import sys
 
@@ -131,7 +130,7 @@ def main():
         dec2.close()
         return tokens
 
-    tokens_other = second_decoder("the other peer all-reduce kind", False, two_shot=world < 4)
+    tokens_other = second_decoder("the other peer all-reduce kind", False, two_shot=True)
     tokens_vocab = second_decoder("vocabulary-parallel head", True, two_shot=world >= 4)
     for name, got in (("the other peer all-reduce kind", tokens_other), ("the vocabulary-parallel head", tokens_vocab)):
         if not np.array_equal(got, tokens_peer):  # one-shot and two-shot add in rank order: the same sums, the same tokens
