@@ -46,7 +46,7 @@ constexpr int kDequantThreads = 128;  // one TMEM lane (weight row) per thread o
 // the activations); for NV <= 64 two CTAs share an SM (256 TMEM columns each) and overlap each other's phases.
 template <int NV>
 struct UmmaCfg {
-  static constexpr int kGroups = 1;
+  static constexpr int kGroups = NV == 256 ? 2 : 1;  // at 256 vectors the MMAs of a stage take as long as one group needs to expand it
   static constexpr int kStageBlocks = 4;   // 32-value blocks per stage (K = 16 per MMA: 2 MMAs per block)
   static constexpr int kStages = 3;
   static constexpr int kAColsPerStage = kStageBlocks * 16;  // 32-bit TMEM columns holding the stage's f16 per lane
