@@ -58,10 +58,11 @@ cudaError_t launch_qlinear_reduce(const float* scratch, int splits, int vpad, in
 
 // tcgen05 path (qlinear_umma.cu)
 struct UmmaPlan {
-  int nv = 32;               // vectors per pass padded to the MMA N (32, 64, 128 or 256)
+  int nv = 32;               // vectors per chunk padded to the MMA N (32, 64, 128 or 256)
+  int chunks = 1;            // chunks of nv vectors the call is cut into (grid.z); more than one only at nv = 256
   int tiles = 1, splits = 1, blocks_per_split = 0;
-  size_t xh_bytes = 0;       // f16 activations in [K/8][nv][8] order
-  size_t scratch_bytes = 0;  // split-K partials
+  size_t xh_bytes = 0;       // f16 activations in [chunk][K/8][nv][8] order, all chunks
+  size_t scratch_bytes = 0;  // split-K partials [chunk][split][nv][rows_padded], all chunks
 };
 UmmaPlan plan_umma(const TiledWeight& w, int64_t vectors, int sm_count);
 cudaError_t launch_repack_umma(const TiledWeight& w, const RepackParts& parts, cudaStream_t stream);

@@ -96,6 +96,15 @@ __global__ void __launch_bounds__(UmmaCfg<NV>::kThreads) qlinear_umma_kernel(Umm
   chain_release();  // the next kernel (split-K sum or the step's next operator) may be scheduled already; it waits for this one
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile = blockIdx.x, split = blockIdx.y;
+  if (gridDim.z > 1) {  // this CTA's chunk of NV vectors: its activations, outputs and partials
+    const size_t chunk = blockIdx.z;
+    const size_t out_cols = a.epilogue == ETC_EPILOGUE_SWIGLU ? a.rows / 2 : a.rows;
+    a.xh += chunk * ((size_t)a.kblocks * 4 * NV * 8);
+    if (a.out) a.out += chunk * NV * out_cols;
+    if (a.residual) a.residual += chunk * NV * out_cols;
+    a.scratch += chunk * ((size_t)gridDim.y * NV * a.rows_padded);
+    a.vectors = max(0, min(NV, a.vectors - (int)chunk * NV));
+  }
   const int kb0 = split * a.blocks_per_split;
   const int kb1 = min(a.kblocks, kb0 + a.blocks_per_split);
   const int nstages = (kb1 - kb0 + kStageBlocks - 1) / kStageBlocks;
@@ -311,11 +320,14 @@ __global__ void __launch_bounds__(UmmaCfg<NV>::kThreads) qlinear_umma_kernel(Umm
 }
 
 // f32 [vectors, K] -> xh8 [K/8][NV][8] f16 (rows >= vectors are zero), saturating like the mma.sync path.
+// More than NV vectors: chunk c holds vectors c*NV ... in its own [K/8][NV][8] block.
 template <int NV>
 __global__ void convert_xh8_kernel(const float* __restrict__ x, int vectors, int K, __half* __restrict__ xh) {
-  const int total = (K / 8) * NV;
-  for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
-    const int kg = idx / NV, n = idx - kg * NV;
+  const int per_chunk = (K / 8) * NV;
+  const int64_t total = (int64_t)per_chunk * ((vectors + NV - 1) / NV);
+  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int chunk = (int)(idx / per_chunk), within = (int)(idx - (int64_t)chunk * per_chunk);
+    const int kg = within / NV, n = chunk * NV + (within - kg * NV);
     uint4 packed = make_uint4(0u, 0u, 0u, 0u);
     if (n < vectors) {
       const float4 lo = *reinterpret_cast<const float4*>(x + (size_t)n * K + kg * 8);
@@ -431,13 +443,13 @@ __global__ void repack_umma_kernel(RepackParts parts, int codec, int64_t rows, i
 }
 
 template <int CODEC, int NV>
-cudaError_t launch_umma_pass(const UmmaArgs& args, int tiles, int splits, cudaStream_t stream) {
+cudaError_t launch_umma_pass(const UmmaArgs& args, int tiles, int splits, int chunks, cudaStream_t stream) {
   constexpr size_t smem = UmmaCfg<NV>::kSmemBytes;
   auto kernel = qlinear_umma_kernel<CODEC, NV>;
   const cudaError_t attr = opt_in_shared_memory(kernel, smem);
   if (attr != cudaSuccess) return attr;
   // chained: set-up, weight loads and their expansion do not depend on the previous kernel and start under its tail
-  return launch_chained(kernel, dim3((unsigned)tiles, (unsigned)splits), dim3((unsigned)UmmaCfg<NV>::kThreads), smem, stream, args);
+  return launch_chained(kernel, dim3((unsigned)tiles, (unsigned)splits, (unsigned)chunks), dim3((unsigned)UmmaCfg<NV>::kThreads), smem, stream, args);
 }
 
 }  // namespace
@@ -455,21 +467,21 @@ int umma_vector_pad(int64_t vectors) { return vectors <= 32 ? 32 : (vectors <= 6
 
 UmmaPlan plan_umma(const TiledWeight& w, int64_t vectors, int sm_count) {
   UmmaPlan p;
-  const int64_t chunk = std::min<int64_t>(vectors, 256);
-  p.nv = umma_vector_pad(chunk);
+  p.nv = umma_vector_pad(std::min<int64_t>(vectors, 256));
+  p.chunks = (int)std::max<int64_t>(1, (vectors + p.nv - 1) / p.nv);
   p.tiles = (int)(w.rows_padded / kUmmaRows);
   const int kblocks = (int)(w.columns / 32);
   const int kStageBlocks = stage_blocks_for(p.nv);
   const int stages = (kblocks + kStageBlocks - 1) / kStageBlocks;
   const int ctas_per_sm = p.nv <= 64 ? 2 : 1;
   const int target = std::max(1, sm_count) * ctas_per_sm;
-  int splits = std::max(1, target / std::max(1, p.tiles));
+  int splits = std::max(1, target / std::max(1, p.tiles * p.chunks));
   splits = std::min(splits, std::max(1, stages / 2));  // at least two stages per split
   const int stages_per_split = (stages + splits - 1) / splits;
   p.blocks_per_split = stages_per_split * kStageBlocks;
   p.splits = (kblocks + p.blocks_per_split - 1) / p.blocks_per_split;
-  p.xh_bytes = (size_t)(w.columns / 8) * p.nv * 16;
-  p.scratch_bytes = p.splits > 1 ? (size_t)p.splits * p.nv * w.rows_padded * sizeof(float) : 0;
+  p.xh_bytes = (size_t)p.chunks * (w.columns / 8) * p.nv * 16;
+  p.scratch_bytes = p.splits > 1 ? (size_t)p.chunks * p.splits * p.nv * w.rows_padded * sizeof(float) : 0;
   return p;
 }
 
@@ -478,67 +490,69 @@ cudaError_t launch_qlinear_umma(const TiledWeight& w, const float* x, const __ha
                                 const float* residual, int epilogue, float* out, __half* out_xh, __half* xh, float* scratch,
                                 DeviceStatus* status, int sm_count, cudaStream_t stream, int* launches, int xh_nv, DeferredSum* defer) {
   if (defer) *defer = DeferredSum();
+  if (vectors <= 0) return cudaSuccess;
   const int out_cols = (int)(epilogue == ETC_EPILOGUE_SWIGLU ? w.rows / 2 : w.rows);
-  for (int64_t v0 = 0; v0 < vectors; v0 += 256) {
-    const int64_t chunk = std::min<int64_t>(256, vectors - v0);
-    const UmmaPlan plan = plan_umma(w, chunk, sm_count);
-    const int K = (int)w.columns;
-    const int total = (K / 8) * plan.nv;
-    const unsigned cgrid = (unsigned)std::min((total + 255) / 256, 148 * 4);
-    const float* xin = x ? x + v0 * w.columns : nullptr;
-    const bool ready = xh_ready != nullptr && vectors <= 128 && plan.nv == xh_nv;  // the producer stored the f16 layout with this row stride
-    if (!ready) switch (plan.nv) {
-      case 32: convert_xh8_kernel<32><<<cgrid, 256, 0, stream>>>(xin, (int)chunk, K, xh); break;
-      case 64: convert_xh8_kernel<64><<<cgrid, 256, 0, stream>>>(xin, (int)chunk, K, xh); break;
-      case 128: convert_xh8_kernel<128><<<cgrid, 256, 0, stream>>>(xin, (int)chunk, K, xh); break;
-      default: convert_xh8_kernel<256><<<cgrid, 256, 0, stream>>>(xin, (int)chunk, K, xh); break;
+  const UmmaPlan plan = plan_umma(w, vectors, sm_count);
+  const int K = (int)w.columns;
+  const int64_t total = (int64_t)(K / 8) * plan.nv * plan.chunks;
+  const unsigned cgrid = (unsigned)std::min<int64_t>((total + 255) / 256, 148 * 8);
+  const bool ready = xh_ready != nullptr && vectors <= 128 && plan.nv == xh_nv;  // the producer stored the f16 layout with this row stride
+  if (!ready) switch (plan.nv) {
+    case 32: convert_xh8_kernel<32><<<cgrid, 256, 0, stream>>>(x, (int)vectors, K, xh); break;
+    case 64: convert_xh8_kernel<64><<<cgrid, 256, 0, stream>>>(x, (int)vectors, K, xh); break;
+    case 128: convert_xh8_kernel<128><<<cgrid, 256, 0, stream>>>(x, (int)vectors, K, xh); break;
+    default: convert_xh8_kernel<256><<<cgrid, 256, 0, stream>>>(x, (int)vectors, K, xh); break;
+  }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  if (launches && !ready) ++*launches;
+  UmmaArgs args;
+  args.quants = reinterpret_cast<const uint4*>(w.quants);
+  args.scales = w.scales;
+  args.xh = ready ? xh_ready : xh;
+  args.out_xh = vectors <= xh_nv ? out_xh : nullptr;
+  args.out_xh_nv = xh_nv;
+  args.bias = bias;
+  args.residual = residual;
+  args.out = out;
+  args.scratch = scratch;
+  args.status = &status->code;
+  args.vectors = (int)vectors;
+  args.rows = (int)w.rows;
+  args.rows_padded = (int)w.rows_padded;
+  args.kblocks = K / 32;
+  args.blocks_per_split = plan.blocks_per_split;
+  args.epilogue = epilogue;
+  auto pass = [&](auto nv_tag) {
+    constexpr int NV = decltype(nv_tag)::value;
+    switch (w.codec) {
+      case 2: return launch_umma_pass<2, NV>(args, plan.tiles, plan.splits, plan.chunks, stream);
+      case 8: return launch_umma_pass<8, NV>(args, plan.tiles, plan.splits, plan.chunks, stream);
+      case 12: return launch_umma_pass<12, NV>(args, plan.tiles, plan.splits, plan.chunks, stream);
+      default: return launch_umma_pass<14, NV>(args, plan.tiles, plan.splits, plan.chunks, stream);
     }
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return e;
-    if (launches && !ready) ++*launches;
-    UmmaArgs args;
-    args.quants = reinterpret_cast<const uint4*>(w.quants);
-    args.scales = w.scales;
-    args.xh = ready ? xh_ready : xh;
-    args.out_xh = vectors <= xh_nv ? out_xh : nullptr;
-    args.out_xh_nv = xh_nv;
-    args.bias = bias;
-    args.residual = residual ? residual + v0 * out_cols : nullptr;
-    args.out = out + v0 * out_cols;
-    args.scratch = scratch;
-    args.status = &status->code;
-    args.vectors = (int)chunk;
-    args.rows = (int)w.rows;
-    args.rows_padded = (int)w.rows_padded;
-    args.kblocks = K / 32;
-    args.blocks_per_split = plan.blocks_per_split;
-    args.epilogue = epilogue;
-    auto pass = [&](auto nv_tag) {
-      constexpr int NV = decltype(nv_tag)::value;
-      switch (w.codec) {
-        case 2: return launch_umma_pass<2, NV>(args, plan.tiles, plan.splits, stream);
-        case 8: return launch_umma_pass<8, NV>(args, plan.tiles, plan.splits, stream);
-        case 12: return launch_umma_pass<12, NV>(args, plan.tiles, plan.splits, stream);
-        default: return launch_umma_pass<14, NV>(args, plan.tiles, plan.splits, stream);
-      }
-    };
-    switch (plan.nv) {
-      case 32: e = pass(std::integral_constant<int, 32>()); break;
-      case 64: e = pass(std::integral_constant<int, 64>()); break;
-      case 128: e = pass(std::integral_constant<int, 128>()); break;
-      default: e = pass(std::integral_constant<int, 256>()); break;
-    }
-    if (e != cudaSuccess) return e;
-    if (launches) ++*launches;
-    if (plan.splits > 1 && defer && vectors <= 256 && !bias && !out_xh && epilogue != ETC_EPILOGUE_SWIGLU) {
-      // the consumer sums the partials itself (and adds the residual stream where the epilogue asks for it)
-      defer->partials = scratch;
-      defer->splits = plan.splits;
-      defer->vpad = plan.nv;
-      defer->rows_padded = (int)w.rows_padded;
-    } else if (plan.splits > 1) {
-      e = launch_qlinear_reduce(scratch, plan.splits, plan.nv, (int)chunk, (int)w.rows, (int)w.rows_padded, bias, args.residual,
-                                epilogue, args.out, args.out_xh, stream, xh_nv);
+  };
+  switch (plan.nv) {
+    case 32: e = pass(std::integral_constant<int, 32>()); break;
+    case 64: e = pass(std::integral_constant<int, 64>()); break;
+    case 128: e = pass(std::integral_constant<int, 128>()); break;
+    default: e = pass(std::integral_constant<int, 256>()); break;
+  }
+  if (e != cudaSuccess) return e;
+  if (launches) ++*launches;
+  if (plan.splits > 1 && defer && plan.chunks == 1 && !bias && !out_xh && epilogue != ETC_EPILOGUE_SWIGLU) {
+    // the consumer sums the partials itself (and adds the residual stream where the epilogue asks for it)
+    defer->partials = scratch;
+    defer->splits = plan.splits;
+    defer->vpad = plan.nv;
+    defer->rows_padded = (int)w.rows_padded;
+  } else if (plan.splits > 1) {
+    for (int c = 0; c < plan.chunks; ++c) {  // one sum launch per chunk of vectors
+      const int64_t v0 = (int64_t)c * plan.nv;
+      const float* partials = scratch + (size_t)c * plan.splits * plan.nv * w.rows_padded;
+      e = launch_qlinear_reduce(partials, plan.splits, plan.nv, (int)std::min<int64_t>(plan.nv, vectors - v0), (int)w.rows, (int)w.rows_padded,
+                                bias, residual ? residual + v0 * out_cols : nullptr, epilogue, out + v0 * out_cols, c == 0 ? args.out_xh : nullptr,
+                                stream, xh_nv);
       if (e != cudaSuccess) return e;
       if (launches) ++*launches;
     }

@@ -292,12 +292,8 @@ size_t tiled_scratch_bytes(const TiledWeight& w, int64_t vectors, int sm_count) 
     const MvPlan p = plan_mv(w, vectors, sm_count);
     return p.xh_bytes + p.partial_bytes;
   }
-  size_t need = 0;
-  for (int64_t v0 = 0; v0 < vectors; v0 += 256) {
-    const UmmaPlan p = plan_umma(w, std::min<int64_t>(256, vectors - v0), sm_count);
-    need = std::max(need, umma_xh_region(p) + p.scratch_bytes);
-  }
-  return need;
+  const UmmaPlan p = plan_umma(w, vectors, sm_count);
+  return umma_xh_region(p) + p.scratch_bytes;
 }
 
 cudaError_t launch_qlinear_tiled(const TiledWeight& w, const float* x, int64_t vectors, const float* bias,
@@ -308,10 +304,7 @@ cudaError_t launch_qlinear_tiled(const TiledWeight& w, const float* x, int64_t v
   if (w.counters && vectors <= mv_max_vectors())
     return launch_qlinear_mv(w, x, xh_ready, vectors, bias, residual, epilogue, out, out_xh, scratch, status, sm_count, stream,
                              launches, xh_nv);
-  // the xh8 region is sized for the widest pass of this call
-  size_t xh_region = 0;
-  for (int64_t v0 = 0; v0 < vectors; v0 += 256)
-    xh_region = std::max(xh_region, umma_xh_region(plan_umma(w, std::min<int64_t>(256, vectors - v0), sm_count)));
+  const size_t xh_region = umma_xh_region(plan_umma(w, vectors, sm_count));  // f16 activations of every chunk, then the partials
   return launch_qlinear_umma(w, x, xh_ready, vectors, bias, residual, epilogue, out, out_xh, reinterpret_cast<__half*>(scratch),
                              reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + xh_region), status, sm_count, stream,
                              launches, xh_nv, defer);

@@ -14,6 +14,7 @@
 // pools, and can fail there with a clear error instead of inside the first allocation-free call.
 #include <mutex>
 
+#include <algorithm>
 #include "kernels.h"
 #include "weights.h"
 
@@ -72,16 +73,24 @@ etc_status etc_qlinear_tiled_static_into(etc_runtime* rt, const etc_qweight* w, 
   if (epilogue == ETC_EPILOGUE_RESIDUAL && !d_residual)
     return fail(ETC_INVALID_ARGUMENT, "quantized_linear: the residual epilogue needs a residual input");
   if (vectors <= 0) return ETC_OK;
-  const size_t need = tiled_scratch_bytes(w->tiled, vectors, rt->sm_count);
-  if (need > kStaticScratchBytes)
-    return fail(ETC_INVALID_ARGUMENT, "quantized_linear: this call needs " + std::to_string(need) +
-                                          " bytes of scratch, the static scratch holds " + std::to_string(kStaticScratchBytes) +
-                                          "; use etc_qlinear_tiled_into with caller scratch");
+  // the whole call in one pass when its scratch fits; otherwise 256 vectors at a time (a slice needs an eighth or so of
+  // what the one-pass plan of a long call needs), and only a slice that does not fit is refused
+  const int64_t slice = tiled_scratch_bytes(w->tiled, vectors, rt->sm_count) <= kStaticScratchBytes ? vectors : 256;
+  for (int64_t v0 = 0; v0 < vectors; v0 += slice) {
+    const size_t need = tiled_scratch_bytes(w->tiled, std::min(slice, vectors - v0), rt->sm_count);
+    if (need > kStaticScratchBytes)
+      return fail(ETC_INVALID_ARGUMENT, "quantized_linear: this call needs " + std::to_string(need) +
+                                            " bytes of scratch, the static scratch holds " + std::to_string(kStaticScratchBytes) +
+                                            "; use etc_qlinear_tiled_into with caller scratch");
+  }
   void* scratch = nullptr;
   ETC_CUDA(static_scratch_for_device(rt->device, &scratch));
   int launches = 0;
-  ETC_CUDA(launch_qlinear_tiled(w->tiled, d_x, vectors, d_bias, d_residual, epilogue, d_out, scratch, rt->d_status,
-                                rt->sm_count, rt->stream, &launches));
+  const int64_t out_cols = epilogue == ETC_EPILOGUE_SWIGLU ? w->tiled.rows / 2 : w->tiled.rows;
+  for (int64_t v0 = 0; v0 < vectors; v0 += slice)
+    ETC_CUDA(launch_qlinear_tiled(w->tiled, d_x + v0 * w->tiled.columns, std::min(slice, vectors - v0), d_bias,
+                                  d_residual ? d_residual + v0 * out_cols : nullptr, epilogue, d_out + v0 * out_cols, scratch, rt->d_status,
+                                  rt->sm_count, rt->stream, &launches));
   rt->launches += (uint64_t)launches;
   return ETC_OK;
 }

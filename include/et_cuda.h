@@ -185,9 +185,10 @@ ETC_API etc_status etc_qlinear_tiled_into(etc_runtime* rt, const etc_qweight* w,
 
 /* The same linear with its scratch in a fixed 16 MiB device array inside the library: the call allocates nothing,
  * neither device nor pinned memory, for callers that must not allocate while they run. No counterpart in the
- * reference, whose backends allocate per operation. Results equal etc_qlinear_tiled_into's. A call that needs more
- * than etc_qlinear_tiled_static_max_bytes of scratch is rejected with ETC_INVALID_ARGUMENT (the message gives both
- * sizes). The array's 16 MiB are reserved on a device when etc_runtime_create runs for it (that is when its device
+ * reference, whose backends allocate per operation. Results equal etc_qlinear_tiled_into's bit for bit when the call's
+ * scratch (etc_qlinear_tiled_scratch_bytes) fits etc_qlinear_tiled_static_max_bytes; a longer call runs 256 vectors at
+ * a time, whose split plans can differ from the one-pass plan (same values to the linear's tolerance), and is rejected
+ * with ETC_INVALID_ARGUMENT only when a 256-vector slice does not fit either (the message gives both sizes). The array's 16 MiB are reserved on a device when etc_runtime_create runs for it (that is when its device
  * address is looked up, which loads the module holding it), so create the runtime before dividing the remaining
  * device memory among your own pools; the entry point looks the address up again only if that step was skipped, and
  * that look-up should not happen during a stream capture. All calls on a device share the array: calls that overlap in
