@@ -365,7 +365,8 @@ def projection_rooflines(rt, et, torch, model, vectors, peaks, peak_kind):
     shapes = [("qkv", qw + 2 * kvw, d, False, et.EPILOGUE_NONE, False), ("o", d, qw, False, et.EPILOGUE_RESIDUAL, True),
               ("gate_up", 2 * ffn, d, True, et.EPILOGUE_SWIGLU, False), ("down", d, ffn, False, et.EPILOGUE_RESIDUAL, True),
               ("head", V, d, False, et.EPILOGUE_NONE, False)]
-    kernel = "qlinear_mv_kernel<Q4_0>" if vectors <= 16 else "qlinear_umma_kernel<Q4_0,32> (+ f16 conversion and split-K sum launches)"
+    nv = 32 if vectors <= 32 else 64 if vectors <= 64 else 128 if vectors <= 128 else 256
+    kernel = "qlinear_mv_kernel<Q4_0>" if vectors <= 16 else f"qlinear_umma_kernel<Q4_0,{nv}> (+ f16 conversion and split-K sum launches)"
     out = {}
     for name, rows, cols, interleave, epilogue, residual in shapes:
         us, algorithmic = time_linear(rt, et, torch, Q4_0, rows, cols, vectors, interleave, epilogue, residual)
