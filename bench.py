@@ -474,7 +474,8 @@ def time_attention(rt, et, torch, batch, q_heads, kv_heads, head_dim, ctx, pool_
     total_ctx = int((ctx + 1).sum())
     algorithmic = total_ctx * 2 * kv_heads * head_dim * 2 + batch * q_heads * head_dim * 8 + 4 * int(np.ceil((ctx + 1) / BLOCK).sum())
     entry = roofline_entry(us, algorithmic, peaks, peak_kind, f"attention_mma_kernel<{head_dim},f16> (+ merge when split): {label}")
-    entry.update({"splits": plan["splits"], "kv_sets_rotated": sets, "tables": "drawn from a shuffled page pool"})
+    entry.update({"splits": plan["splits"], "kv_sets_rotated": sets, "tables": "drawn from a shuffled page pool",
+                  "operands": "f32 queries (rounded to f16 for the MMA), f16 K / V pages"})
     del graph
     keep.clear()
     pool.close()
