@@ -21,6 +21,10 @@
  *     asynchronous unless stated; device-detected problems (index out of range, non-finite
  *     logit) are reported through a status word read at the next synchronising call.
  *   - There is no CPU fallback: a call that cannot run on the device fails.
+ *   - Threads: different runtimes may be driven from different threads freely. Calls on ONE runtime (and on the pools,
+ *     weights and decoders made from it) share its stream, status word and staging buffers: the host serialises them,
+ *     as the reference's addon does with one worker per executable invocation. Sequences carry their own run lock, so
+ *     two steps over disjoint sequences are ordered by the caller only through the runtime they share.
  */
 #ifndef ET_CUDA_H
 #define ET_CUDA_H
@@ -372,7 +376,8 @@ ETC_API etc_status etc_decoder_set_tensor_parallel(etc_decoder* dec, int rank, i
  * row-parallel projection's split-K partials are summed inside the same kernel. Every rank exports a
  * 64-byte handle of its exchange region, the host gathers the handles of all ranks into a table [world][64] (own slot
  * ignored) and every rank imports it. The kernel's wait for its peers is bounded: a rank that never arrives turns
- * into ETC_EXECUTION at the next synchronising call, not into a hang.
+ * into ETC_EXECUTION at the next synchronising call, not into a hang. ETC_TP_TWO_SHOT=0 or 1 in the environment of the
+ * importing call forces the one-shot or the reduce-scatter + all-gather form (every rank must use the same).
  * Two duties stay with the host, because a rank only sees its own status. (1) After every step the ranks exchange
  * their step status over the host transport; when any rank failed, every rank treats the step as failed (a rank whose
  * own call returned ETC_OK has committed already: it releases the affected sequences and re-creates them, as it would
