@@ -188,7 +188,7 @@ etc_status set_weight(etc_decoder* dec, int slot, int layer, int codec, const vo
 }
 
 bool tileable(const BoundWeight& w) {
-  if (w.codec == ETC_CODEC_Q4_K || w.codec == ETC_CODEC_Q6_K) return w.columns % 256 == 0;
+  if (w.codec == ETC_CODEC_Q3_K || w.codec == ETC_CODEC_Q4_K || w.codec == ETC_CODEC_Q5_K || w.codec == ETC_CODEC_Q6_K) return w.columns % 256 == 0;
   return (w.codec == ETC_CODEC_Q4_0 || w.codec == ETC_CODEC_Q8_0) && w.columns % 64 == 0;
 }
 
@@ -867,11 +867,20 @@ etc_status etc_decoder_finalize(etc_decoder* dec) {
           bound(dec->wo[l]) && bound(dec->gate[l]) && bound(dec->up[l]) && bound(dec->down[l]);
   if (!all) return fail(ETC_COMPILATION, "compile: every weight slot of every layer must be bound before finalize");
 
-  // Tensor-core tiling when every projection is Q4_0/Q8_0 and exact order was not requested.
+  // Tensor-core tiling when every projection has a tiled form (Q4_0, Q8_0, Q3_K - Q6_K) and exact order was not requested.
   bool tiled = !c.exact && tileable(dec->head) && c.ffn % 8 == 0;
+  // q, k and v may differ in codec (GGUF files keep v, and only v, at more bits in some layers): the fused weight then
+  // holds one segment per run of equal codecs, which must meet on a 128-row tile boundary
+  auto qkv_fusable = [&](size_t l) {
+    const BoundWeight &q = dec->wq[l], &k = dec->wk[l], &v = dec->wv[l];
+    if (!tileable(q) || !tileable(k) || !tileable(v)) return false;
+    if (k.codec != q.codec && q.rows % 128 != 0) return false;
+    if (v.codec != k.codec && (q.rows + k.rows) % 128 != 0) return false;
+    return true;
+  };
   for (size_t l = 0; l < L && tiled; ++l)
-    tiled = tileable(dec->wq[l]) && dec->wk[l].codec == dec->wq[l].codec && dec->wv[l].codec == dec->wq[l].codec &&
-            tileable(dec->wo[l]) && tileable(dec->gate[l]) && dec->up[l].codec == dec->gate[l].codec && tileable(dec->down[l]);
+    tiled = qkv_fusable(l) && tileable(dec->wo[l]) && tileable(dec->gate[l]) && dec->up[l].codec == dec->gate[l].codec &&
+            tileable(dec->down[l]);
   dec->tiled = tiled;
   auto release_raw = [&](BoundWeight& w) {
     if (w.d_raw) rt->device_free(w.d_raw);
@@ -882,7 +891,8 @@ etc_status etc_decoder_finalize(etc_decoder* dec) {
     for (size_t l = 0; l < L; ++l) {
       const void* qkv_parts[3] = {dec->wq[l].d_raw, dec->wk[l].d_raw, dec->wv[l].d_raw};
       const int64_t qkv_rows[3] = {dec->wq[l].rows, dec->wk[l].rows, dec->wv[l].rows};
-      ETC_TRY(build_qweight(rt, dec->wq[l].codec, qkv_parts, qkv_rows, 3, c.d_model, 0, 1, &dec->t_qkv[l]));
+      const int qkv_codecs[3] = {dec->wq[l].codec, dec->wk[l].codec, dec->wv[l].codec};
+      ETC_TRY(build_qweight(rt, dec->wq[l].codec, qkv_parts, qkv_rows, 3, c.d_model, 0, 1, &dec->t_qkv[l], qkv_codecs));
       const void* o_parts[1] = {dec->wo[l].d_raw};
       const int64_t o_rows[1] = {dec->wo[l].rows};
       ETC_TRY(build_qweight(rt, dec->wo[l].codec, o_parts, o_rows, 1, dec->wo[l].columns, 0, 1, &dec->t_o[l]));

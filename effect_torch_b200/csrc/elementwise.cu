@@ -99,13 +99,25 @@ __global__ void __launch_bounds__(THREADS) rmsnorm_rows_kernel(const float* x, c
                                                                double eps, int n, float* __restrict__ out, __half* __restrict__ out_xh,
                                                                int xh_nv, DeferredSum sum_in, float* x_out) {
   chain_release();  // the next kernel of the step may be scheduled; it waits for this one before touching memory
-  chain_wait();
   constexpr int ITEMS = 2048 / THREADS;  // float4 chunks per thread: rows of up to 8192 values
+  const int chunks = n / 4;
+  float4 w[ITEMS];
+  auto load_weight = [&]() {
+#pragma unroll
+    for (int j = 0; j < ITEMS; ++j) {
+      const int c = threadIdx.x + THREADS * j;
+      w[j] = weight && c < chunks ? reinterpret_cast<const float4*>(weight)[c] : make_float4(1.f, 1.f, 1.f, 1.f);
+    }
+  };
+  // The f16 hand-off forms are launched by the decoder alone, whose norm weights no kernel writes after the load: they
+  // are fetched while the kernel before this one is still running. The plain form may be given a weight that the
+  // previous kernel of the stream produced, and reads it after the wait.
+  if (XH) load_weight();
+  chain_wait();
+  if (!XH) load_weight();
   __shared__ double partial[THREADS / 32];
-  __shared__ double scale_s;
   const int row = blockIdx.x;
   const float4* src = reinterpret_cast<const float4*>(x + (size_t)row * n);
-  const int chunks = n / 4;
   float4 v[ITEMS];
   double sum = 0.0;
 #pragma unroll
@@ -132,22 +144,19 @@ __global__ void __launch_bounds__(THREADS) rmsnorm_rows_kernel(const float* x, c
   for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
   if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = sum;
   __syncthreads();
-  if (threadIdx.x == 0) {
-    double total = 0.0;
-    for (int i = 0; i < THREADS / 32; ++i) total += partial[i];
-    scale_s = 1.0 / sqrt(total / (double)n + eps);
-  }
-  __syncthreads();
-  const double scale = scale_s;
+  // every thread adds the warps' sums in the same order and takes the reciprocal root itself: one barrier, no hand-over
+  double total = 0.0;
+#pragma unroll
+  for (int i = 0; i < THREADS / 32; ++i) total += partial[i];
+  const double scale = 1.0 / sqrt(total / (double)n + eps);
 #pragma unroll
   for (int j = 0; j < ITEMS; ++j) {
     const int c = threadIdx.x + THREADS * j;
     if (c >= chunks) continue;
-    float4 w = weight ? reinterpret_cast<const float4*>(weight)[c] : make_float4(1.f, 1.f, 1.f, 1.f);
-    const float r0 = (float)__dmul_rn(__dmul_rn((double)v[j].x, scale), (double)w.x);
-    const float r1 = (float)__dmul_rn(__dmul_rn((double)v[j].y, scale), (double)w.y);
-    const float r2 = (float)__dmul_rn(__dmul_rn((double)v[j].z, scale), (double)w.z);
-    const float r3 = (float)__dmul_rn(__dmul_rn((double)v[j].w, scale), (double)w.w);
+    const float r0 = (float)__dmul_rn(__dmul_rn((double)v[j].x, scale), (double)w[j].x);
+    const float r1 = (float)__dmul_rn(__dmul_rn((double)v[j].y, scale), (double)w[j].y);
+    const float r2 = (float)__dmul_rn(__dmul_rn((double)v[j].z, scale), (double)w[j].z);
+    const float r3 = (float)__dmul_rn(__dmul_rn((double)v[j].w, scale), (double)w[j].w);
     if (XH) {
       auto sat = [](float f) { return fminf(fmaxf(f, -65504.f), 65504.f); };
       __half2 h01 = __floats2half2_rn(sat(r0), sat(r1)), h23 = __floats2half2_rn(sat(r2), sat(r3));

@@ -24,8 +24,18 @@ cudaError_t launch_qembedding(int codec, const void* indexes, int index_is_i64, 
 // (Q8_0) payload bytes are contiguous ([tile][block][row][bytes]; Q4_0 nibbles pre-ordered so that masks give f16 pairs
 // in column order), scales are [tile][block][row] f16. Same byte count as the GGUF encoding; rows padded to 128 with
 // zero scales. Both linear kernels (qlinear_mv.cu, qlinear_umma.cu) read this one layout.
-struct TiledWeight {
+// A run of 128-row tiles of one codec inside a tiled weight. A weight fused from parts of different codecs (q and k in
+// Q4_K, v in Q6_K, as GGUF files mix them) holds one segment per run of equal codecs, each repacked in its codec's layout
+// at byte offsets into the weight's arrays; the linear launches one kernel per segment into the same outputs.
+struct TiledSegment {
   int codec = 0;
+  int tile0 = 0, tiles = 0;
+  size_t quant_offset = 0, scale_offset = 0;  // bytes
+};
+constexpr int kMaxSegments = 4;
+
+struct TiledWeight {
+  int codec = 0;            // the first segment's codec
   int64_t rows = 0;         // logical rows (outputs) after concatenation / interleave
   int64_t rows_padded = 0;  // multiple of 128
   int64_t columns = 0;      // multiple of 64
@@ -36,6 +46,8 @@ struct TiledWeight {
   // [rows_padded/128] arrival tickets, zero between launches: taken by the matvec kernel's CTAs that hold part of a row
   // group's K; the last one to arrive finishes the group
   int* counters = nullptr;
+  int n_segments = 0;       // 0: one segment of `codec` over the whole weight
+  TiledSegment segments[kMaxSegments];
 };
 // Split-K partials a linear left unsummed for the kernel that consumes its result (the next RMSNorm, or the RoPE /
 // KV-append kernel): [splits][vpad][rows_padded] f32, summed in split order. splits == 0: the result is already in `out`.

@@ -58,75 +58,132 @@ etc_status make_inv_freq(etc_runtime* rt, double theta, int head_dim, double** o
   return ETC_OK;
 }
 
+namespace {
+bool tiled_k_quant(int codec) {
+  return codec == ETC_CODEC_Q3_K || codec == ETC_CODEC_Q4_K || codec == ETC_CODEC_Q5_K || codec == ETC_CODEC_Q6_K;
+}
+bool tiled_nibbles(int codec) { return codec == ETC_CODEC_Q4_0 || codec == ETC_CODEC_Q4_K; }
+}  // namespace
+
+// `part_codecs` (may be null: every part is `codec`) gives each part its own codec. Parts of different codecs become
+// segments: runs of 128-row tiles repacked in their own layouts, which requires every run to end on a tile boundary.
 etc_status build_qweight(etc_runtime* rt, int codec, const void* const* parts, const int64_t* part_rows, int n_parts,
-                         int64_t columns, int interleave8, int on_device, etc_qweight** out) {
-  const bool kquant = codec == ETC_CODEC_Q4_K || codec == ETC_CODEC_Q6_K;
-  if (codec != ETC_CODEC_Q4_0 && codec != ETC_CODEC_Q8_0 && !kquant)
-    return fail(ETC_UNSUPPORTED, std::string("tiled weights support Q4_0, Q8_0, Q4_K and Q6_K, got ") + codec_name(codec));
+                         int64_t columns, int interleave8, int on_device, etc_qweight** out, const int* part_codecs) {
   if (n_parts < 1 || n_parts > 4) return fail(ETC_INVALID_ARGUMENT, "qweight: between 1 and 4 parts are supported");
+  bool kquant = false, mixed = false;
+  for (int p = 0; p < n_parts; ++p) {
+    const int pc = part_codecs ? part_codecs[p] : codec;
+    if (pc != ETC_CODEC_Q4_0 && pc != ETC_CODEC_Q8_0 && !tiled_k_quant(pc))
+      return fail(ETC_UNSUPPORTED, std::string("tiled weights support Q4_0, Q8_0, Q3_K, Q4_K, Q5_K and Q6_K, got ") + codec_name(pc));
+    kquant = kquant || tiled_k_quant(pc);
+    mixed = mixed || pc != (part_codecs ? part_codecs[0] : codec);
+  }
+  if (part_codecs) codec = part_codecs[0];
   if (columns <= 0 || columns % 64 != 0 || (kquant && columns % 256 != 0))
     return fail(ETC_COMPILATION, "qweight: logical row width " + std::to_string(columns) + " must be a multiple of " + (kquant ? "256" : "64"));
-  if (interleave8 && (n_parts != 2 || part_rows[0] != part_rows[1] || part_rows[0] % 8 != 0))
-    return fail(ETC_COMPILATION, "qweight: interleave8 needs two parts of equal row count divisible by 8");
+  if (interleave8 && (n_parts != 2 || part_rows[0] != part_rows[1] || part_rows[0] % 8 != 0 || mixed))
+    return fail(ETC_COMPILATION, "qweight: interleave8 needs two parts of equal row count divisible by 8 and of one codec");
   int64_t rows = 0;
   for (int p = 0; p < n_parts; ++p) {
     if (part_rows[p] <= 0 || !parts[p]) return fail(ETC_INVALID_ARGUMENT, "qweight: empty part");
     rows += part_rows[p];
   }
-  const int64_t row_bytes = codec_row_bytes(codec, columns);
+  const int64_t row_tile = 128;
+  const int64_t kblocks = columns / 32;
   etc_qweight* w = new etc_qweight();
   w->rt = rt;
-  w->tiled.codec = codec;
-  const int64_t row_tile = 128;
-  w->tiled.rows = rows;
-  w->tiled.rows_padded = (rows + row_tile - 1) / row_tile * row_tile;
-  w->tiled.columns = columns;
-  w->tiled.interleave8 = interleave8;
-  const int64_t kblocks = columns / 32;
-  // K-quants are re-cut into 32-value blocks at load: Q4_K -> nibbles + (scale, min) per block, Q6_K -> int8 codes + one
-  // scale per 16 values; the small-batch matvec kernel (and its arrival tickets) serves the 32-value codecs only
-  const bool nibbles = codec == ETC_CODEC_Q4_0 || codec == ETC_CODEC_Q4_K;
-  w->tiled.quant_bytes = (size_t)w->tiled.rows_padded * kblocks * (nibbles ? 16 : 32);
-  w->tiled.scale_bytes = (size_t)w->tiled.rows_padded * kblocks * (kquant ? 4 : 2);
-  const size_t counter_bytes = kquant ? 0 : (size_t)(w->tiled.rows_padded / 128) * sizeof(int);
-  etc_status st = rt->device_alloc(w->tiled.quant_bytes, (void**)&w->tiled.quants);
-  if (st == ETC_OK && w->tiled.scale_bytes) st = rt->device_alloc(w->tiled.scale_bytes, (void**)&w->tiled.scales);
+  TiledWeight& t = w->tiled;
+  t.codec = codec;
+  t.rows = rows;
+  t.rows_padded = (rows + row_tile - 1) / row_tile * row_tile;
+  t.columns = columns;
+  t.interleave8 = interleave8;
+  // Segments: runs of parts with one codec. K-quants are re-cut into 32-value blocks at load: Q4_K -> nibbles + (scale, min)
+  // per block, Q5_K -> int8 codes + (scale, min) per block, Q3_K and Q6_K -> int8 codes + one scale per 16 values.
+  int seg_first_part[kMaxSegments] = {0}, seg_parts[kMaxSegments] = {0};
+  int n_segments = 0;
+  int64_t row_cursor = 0;
+  for (int p = 0; p < n_parts; ++p) {
+    const int pc = part_codecs ? part_codecs[p] : codec;
+    if (n_segments == 0 || t.segments[n_segments - 1].codec != pc) {
+      if (row_cursor % row_tile != 0) {
+        delete w;
+        return fail(ETC_COMPILATION, "qweight: parts of different codecs must meet on a multiple of 128 rows, got " + std::to_string(row_cursor));
+      }
+      TiledSegment& seg = t.segments[n_segments];
+      seg.codec = pc;
+      seg.tile0 = (int)(row_cursor / row_tile);
+      seg.quant_offset = t.quant_bytes;
+      seg.scale_offset = t.scale_bytes;
+      seg_first_part[n_segments] = p;
+      ++n_segments;
+    }
+    TiledSegment& seg = t.segments[n_segments - 1];
+    ++seg_parts[n_segments - 1];
+    row_cursor += part_rows[p];
+    const int64_t seg_rows_padded = (row_cursor + row_tile - 1) / row_tile * row_tile - (int64_t)seg.tile0 * row_tile;
+    seg.tiles = (int)(seg_rows_padded / row_tile);
+    t.quant_bytes = seg.quant_offset + (size_t)seg_rows_padded * kblocks * (tiled_nibbles(pc) ? 16 : 32);
+    t.scale_bytes = seg.scale_offset + (size_t)seg_rows_padded * kblocks * (tiled_k_quant(pc) ? 4 : 2);
+  }
+  t.n_segments = n_segments > 1 ? n_segments : 0;
+  // the small-batch matvec kernel (and its arrival tickets) serves single-codec Q4_0 / Q8_0 weights only
+  const size_t counter_bytes = (kquant || mixed) ? 0 : (size_t)(t.rows_padded / 128) * sizeof(int);
+  etc_status st = rt->device_alloc(t.quant_bytes, (void**)&t.quants);
+  if (st == ETC_OK && t.scale_bytes) st = rt->device_alloc(t.scale_bytes, (void**)&t.scales);
   if (st == ETC_OK && counter_bytes) {
-    st = rt->device_alloc(counter_bytes, (void**)&w->tiled.counters);
-    if (st == ETC_OK && cudaMemsetAsync(w->tiled.counters, 0, counter_bytes, rt->stream) != cudaSuccess)
+    st = rt->device_alloc(counter_bytes, (void**)&t.counters);
+    if (st == ETC_OK && cudaMemsetAsync(t.counters, 0, counter_bytes, rt->stream) != cudaSuccess)
       st = fail(ETC_EXECUTION, "qweight: clearing the arrival tickets failed");
   }
-  RepackParts rp;
-  std::memset(&rp, 0, sizeof(rp));
-  rp.n_parts = n_parts;
   std::vector<void*> staged;
+  const uint8_t* device_part[4] = {nullptr, nullptr, nullptr, nullptr};
   for (int p = 0; p < n_parts && st == ETC_OK; ++p) {
-    rp.rows[p] = part_rows[p];
     if (on_device) {
-      rp.ptr[p] = (const uint8_t*)parts[p];
+      device_part[p] = (const uint8_t*)parts[p];
     } else {
       void* d = nullptr;
-      const size_t bytes = (size_t)part_rows[p] * (size_t)row_bytes;
+      const size_t bytes = (size_t)part_rows[p] * (size_t)codec_row_bytes(part_codecs ? part_codecs[p] : codec, columns);
       st = rt->device_alloc(bytes, &d);
       if (st != ETC_OK) break;
       staged.push_back(d);
       cudaError_t e = cudaMemcpyAsync(d, parts[p], bytes, cudaMemcpyHostToDevice, rt->stream);
       if (e != cudaSuccess) st = fail(ETC_TRANSFER, std::string("qweight upload failed: ") + cudaGetErrorString(e));
-      rp.ptr[p] = (const uint8_t*)d;
+      device_part[p] = (const uint8_t*)d;
     }
   }
-  if (st == ETC_OK) {
-    cudaError_t e = launch_repack(w->tiled, rp, rt->stream);
+  for (int sgm = 0; sgm < n_segments && st == ETC_OK; ++sgm) {
+    // each segment is repacked as a weight of its own: its parts, its codec, its slice of the arrays
+    const TiledSegment& seg = t.segments[sgm];
+    RepackParts rp;
+    std::memset(&rp, 0, sizeof(rp));
+    rp.n_parts = seg_parts[sgm];
+    TiledWeight view;
+    view.codec = seg.codec;
+    view.columns = columns;
+    view.interleave8 = interleave8;
+    view.rows_padded = (int64_t)seg.tiles * row_tile;
+    for (int q = 0; q < rp.n_parts; ++q) {
+      rp.ptr[q] = device_part[seg_first_part[sgm] + q];
+      rp.rows[q] = part_rows[seg_first_part[sgm] + q];
+      view.rows += rp.rows[q];
+    }
+    view.quants = t.quants + seg.quant_offset;
+    view.scales = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(t.scales) + seg.scale_offset);
+    cudaError_t e = launch_repack(view, rp, rt->stream);
     rt->launches++;
-    if (e == cudaSuccess) e = cudaStreamSynchronize(rt->stream);
+    if (e != cudaSuccess) st = fail(ETC_EXECUTION, std::string("qweight repack failed: ") + cudaGetErrorString(e));
+  }
+  if (st == ETC_OK) {
+    const cudaError_t e = cudaStreamSynchronize(rt->stream);
     if (e != cudaSuccess) st = fail(ETC_EXECUTION, std::string("qweight repack failed: ") + cudaGetErrorString(e));
   }
   const std::string message = last_error();
   for (void* d : staged) rt->device_free(d);
   if (st != ETC_OK) {
-    rt->device_free(w->tiled.quants);
-    rt->device_free(w->tiled.scales);
-    rt->device_free(w->tiled.counters);
+    rt->device_free(t.quants);
+    rt->device_free(t.scales);
+    rt->device_free(t.counters);
     delete w;
     return fail(st, message);
   }

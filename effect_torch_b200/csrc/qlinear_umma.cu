@@ -70,6 +70,7 @@ struct UmmaArgs {
   __half* out_xh;         // optional: result additionally stored as xh8 f16 [cols/8][out_xh_nv][8] for the next linear
   int out_xh_nv;
   int vectors, rows, rows_padded, kblocks, blocks_per_split, epilogue;
+  int tile0;              // first row tile of this launch in the output (a segment of a weight fused from several codecs)
 };
 
 template <int CODEC, int NV>
@@ -77,8 +78,8 @@ __global__ void __launch_bounds__(UmmaCfg<NV>::kThreads) qlinear_umma_kernel(Umm
   using Cfg = UmmaCfg<NV>;
   constexpr int kGroups = Cfg::kGroups, kStageBlocks = Cfg::kStageBlocks, kStages = Cfg::kStages;
   constexpr int kAColsPerStage = Cfg::kAColsPerStage;
-  constexpr bool kNibbles = CODEC == 2 || CODEC == 12;      // 4-bit codes (Q4_0, re-cut Q4_K) or 8-bit (Q8_0, re-cut Q6_K)
-  constexpr bool kPair = CODEC == 12 || CODEC == 14;        // two f16 per (row, block): (scale, min) or the two half-block scales
+  constexpr bool kNibbles = CODEC == 2 || CODEC == 12;      // 4-bit codes (Q4_0, re-cut Q4_K) or 8-bit (Q8_0, re-cut Q3_K / Q5_K / Q6_K)
+  constexpr bool kPair = CODEC >= 12;                       // two f16 per (row, block): (scale, min) or the two half-block scales
   constexpr int QW = kNibbles ? 1 : 2;                      // uint4 words per (row, block)
   constexpr uint32_t kStageBBytes = Cfg::kStageBBytes;      // one stage of activations
   constexpr uint32_t kTmemCols = Cfg::kTmemCols;
@@ -175,7 +176,7 @@ __global__ void __launch_bounds__(UmmaCfg<NV>::kThreads) qlinear_umma_kernel(Umm
         for (int b = 0; b < kStageBlocks; ++b) {
           const uint32_t sraw = b < valid ? sbuf[p][b] : 0u;
           const __half2 pair = u2h(sraw);
-          // first f16 of the entry: the block scale (Q6_K: of values 0-15); second: Q4_K's min, Q6_K's scale of values 16-31
+          // first f16 of the entry: the block scale (codec 14: of values 0-15); second: the min (12, 13) or the scale of values 16-31 (14)
           const __half2 sc = __half2half2(__low2half(pair));
           const __half2 second = __half2half2(__high2half(pair));
           if (CODEC == 2) {
@@ -191,6 +192,13 @@ __global__ void __launch_bounds__(UmmaCfg<NV>::kThreads) qlinear_umma_kernel(Umm
             expand_q4k(q.y, sc, neg_min, regs[b] + 4);
             expand_q4k(q.z, sc, neg_min, regs[b] + 8);
             expand_q4k(q.w, sc, neg_min, regs[b] + 12);
+          } else if (CODEC == 13) {
+            const __half2 neg_min = __hneg2(second);
+            const uint4 q0 = qbuf[p][b][0], q1 = qbuf[p][b][QW - 1];
+            expand_q8k(q0.x, sc, neg_min, regs[b] + 0); expand_q8k(q0.y, sc, neg_min, regs[b] + 2);
+            expand_q8k(q0.z, sc, neg_min, regs[b] + 4); expand_q8k(q0.w, sc, neg_min, regs[b] + 6);
+            expand_q8k(q1.x, sc, neg_min, regs[b] + 8); expand_q8k(q1.y, sc, neg_min, regs[b] + 10);
+            expand_q8k(q1.z, sc, neg_min, regs[b] + 12); expand_q8k(q1.w, sc, neg_min, regs[b] + 14);
           } else {
             const __half2 sc_hi = CODEC == 14 ? second : sc;
             const uint4 q0 = qbuf[p][b][0], q1 = qbuf[p][b][QW - 1];
@@ -226,7 +234,7 @@ __global__ void __launch_bounds__(UmmaCfg<NV>::kThreads) qlinear_umma_kernel(Umm
     ok = __all_sync(0xffffffffu, ok);  // warp-uniform: the epilogue below shuffles across the warp
     if (ok) {
       tc_fence_after();
-      const int r = tile * kUmmaRows + row;
+      const int r = (a.tile0 + tile) * kUmmaRows + row;
 #pragma unroll 1
       for (int c0 = 0; c0 < NV; c0 += 32) {
         uint32_t acc[32];
@@ -347,8 +355,8 @@ __global__ void convert_xh8_kernel(const float* __restrict__ x, int vectors, int
 __global__ void repack_umma_kernel(RepackParts parts, int codec, int64_t rows, int64_t rows_padded, int64_t kblocks,
                                    int interleave8, uint32_t* __restrict__ quants, __half* __restrict__ scales) {
   const int64_t total = rows_padded * kblocks;
-  const bool kquant = codec == 12 || codec == 14;
-  const int bb = codec == 2 ? 18 : (codec == 8 ? 34 : (codec == 12 ? 144 : 210));  // bytes per source block
+  const bool kquant = codec >= 11;
+  const int bb = codec == 2 ? 18 : (codec == 8 ? 34 : (codec == 11 ? 110 : (codec == 12 ? 144 : (codec == 13 ? 176 : 210))));  // bytes per source block
   const int per_block = kquant ? 8 : 1;                                              // 32-value blocks per source block
   const int words = (codec == 2 || codec == 12) ? 4 : 8;
   const int64_t row_bytes = kblocks / per_block * bb;
@@ -386,6 +394,51 @@ __global__ void repack_umma_kernel(RepackParts parts, int codec, int64_t rows, i
         for (int j = 0; j < 8; ++j) {
           const int raw = blk[16 + (sub >> 1) * 32 + 8 * w + j];
           word |= (uint32_t)((sub & 1) ? (raw >> 4) : (raw & 0x0f)) << pos[j];
+        }
+        dst[w] = word;
+      }
+    } else if (codec == 11) {
+      // Q3_K (quantized.rs:142-176): block `sub` of the 256-value block is groups 2*sub and 2*sub+1 of 16 values,
+      // value = d*(scale6 - 32)*(low2 - (high bit clear ? 4 : 0)); stored as int8 codes with one f16 scale per group, the
+      // layout of the re-cut Q6_K
+      const uint8_t* blk = src_row + (kb >> 3) * bb;
+      const int sub = (int)(kb & 7), half = sub >> 2, lane = sub & 3;
+      const uint8_t* packed = blk + 96;
+      const float d = fp16_at(blk, 108);
+      auto group_scale = [&](int g) {
+        const int low = g < 8 ? (packed[g] & 0x0f) : (packed[g - 8] >> 4);
+        const int high = (packed[8 + g % 4] >> (2 * (g / 4))) & 3;
+        return __float2half_rn(__fmul_rn(d, (float)((low | (high << 4)) - 32)));
+      };
+      scale = group_scale(2 * sub);
+      second = group_scale(2 * sub + 1);
+      const uint8_t mask = (uint8_t)(1u << (half * 4 + lane));
+      for (int w = 0; w < 8; ++w) {
+        uint32_t word = 0;
+        for (int j = 0; j < 4; ++j) {
+          const int v = 4 * w + j;
+          const int code = ((blk[32 + half * 32 + v] >> (2 * lane)) & 3) - ((blk[v] & mask) == 0 ? 4 : 0);
+          word |= (uint32_t)(code & 0xff) << (8 * j);
+        }
+        dst[w] = word;
+      }
+    } else if (codec == 13) {
+      // Q5_K (quantized.rs:203-234): sub-block `sub`, value = d*sc*code - dmin*m with a 5-bit code (low nibble + one high
+      // bit); stored as int8 codes with (scale, min) per 32 values
+      const uint8_t* blk = src_row + (kb >> 3) * bb;
+      const int sub = (int)(kb & 7);
+      int sc, mn;
+      scale_min_k4(sub, blk + 4, sc, mn);
+      scale = __float2half_rn(__fmul_rn(fp16_at(blk, 0), (float)sc));
+      second = __float2half_rn(__fmul_rn(fp16_at(blk, 2), (float)mn));
+      const uint8_t* ql = blk + 48 + (sub >> 1) * 32;
+      const uint8_t mask = (uint8_t)(1u << sub);
+      for (int w = 0; w < 8; ++w) {
+        uint32_t word = 0;
+        for (int j = 0; j < 4; ++j) {
+          const int v = 4 * w + j;
+          const int code = ((sub & 1) ? (ql[v] >> 4) : (ql[v] & 0x0f)) + ((blk[16 + v] & mask) == 0 ? 0 : 16);
+          word |= (uint32_t)code << (8 * j);
         }
         dst[w] = word;
       }
@@ -523,23 +576,39 @@ cudaError_t launch_qlinear_umma(const TiledWeight& w, const float* x, const __ha
   args.kblocks = K / 32;
   args.blocks_per_split = plan.blocks_per_split;
   args.epilogue = epilogue;
+  args.tile0 = 0;
+  int codec = w.codec, tiles = plan.tiles;
   auto pass = [&](auto nv_tag) {
     constexpr int NV = decltype(nv_tag)::value;
-    switch (w.codec) {
-      case 2: return launch_umma_pass<2, NV>(args, plan.tiles, plan.splits, plan.chunks, stream);
-      case 8: return launch_umma_pass<8, NV>(args, plan.tiles, plan.splits, plan.chunks, stream);
-      case 12: return launch_umma_pass<12, NV>(args, plan.tiles, plan.splits, plan.chunks, stream);
-      default: return launch_umma_pass<14, NV>(args, plan.tiles, plan.splits, plan.chunks, stream);
+    switch (codec) {
+      case 2: return launch_umma_pass<2, NV>(args, tiles, plan.splits, plan.chunks, stream);
+      case 8: return launch_umma_pass<8, NV>(args, tiles, plan.splits, plan.chunks, stream);
+      case 12: return launch_umma_pass<12, NV>(args, tiles, plan.splits, plan.chunks, stream);
+      case 13: return launch_umma_pass<13, NV>(args, tiles, plan.splits, plan.chunks, stream);
+      default:  // 14, and 11 whose re-cut form is the same
+        return launch_umma_pass<14, NV>(args, tiles, plan.splits, plan.chunks, stream);
     }
   };
-  switch (plan.nv) {
-    case 32: e = pass(std::integral_constant<int, 32>()); break;
-    case 64: e = pass(std::integral_constant<int, 64>()); break;
-    case 128: e = pass(std::integral_constant<int, 128>()); break;
-    default: e = pass(std::integral_constant<int, 256>()); break;
+  // one launch per run of equal codecs; all of them share the plan (split count, partial layout) of the whole weight
+  const int n_segments = std::max(1, w.n_segments);
+  for (int sgm = 0; sgm < n_segments; ++sgm) {
+    if (w.n_segments > 0) {
+      const TiledSegment& seg = w.segments[sgm];
+      codec = seg.codec;
+      tiles = seg.tiles;
+      args.tile0 = seg.tile0;
+      args.quants = reinterpret_cast<const uint4*>(w.quants + seg.quant_offset);
+      args.scales = reinterpret_cast<const __half*>(reinterpret_cast<const uint8_t*>(w.scales) + seg.scale_offset);
+    }
+    switch (plan.nv) {
+      case 32: e = pass(std::integral_constant<int, 32>()); break;
+      case 64: e = pass(std::integral_constant<int, 64>()); break;
+      case 128: e = pass(std::integral_constant<int, 128>()); break;
+      default: e = pass(std::integral_constant<int, 256>()); break;
+    }
+    if (e != cudaSuccess) return e;
+    if (launches) ++*launches;
   }
-  if (e != cudaSuccess) return e;
-  if (launches) ++*launches;
   if (plan.splits > 1 && defer && plan.chunks == 1 && !bias && !out_xh && epilogue != ETC_EPILOGUE_SWIGLU) {
     // the consumer sums the partials itself (and adds the residual stream where the epilogue asks for it)
     defer->partials = scratch;

@@ -178,6 +178,14 @@ __device__ __forceinline__ void expand_q4k(uint32_t q, __half2 scale, __half2 ne
   out4[3] = h2u(__hfma2(__hfma2(u2h((qs & 0x00F000F0u) | magic), sixteenth, bias_hi), scale, neg_min));
 }
 
+// Q5_K block re-cut to 32 int8 codes: code * scale - min.
+__device__ __forceinline__ void expand_q8k(uint32_t w, __half2 scale, __half2 neg_min, uint32_t* out2) {
+  const uint32_t x = w ^ 0x80808080u;
+  const __half2 bias = __floats2half2_rn(1152.0f, 1152.0f);
+  out2[0] = h2u(__hfma2(__hsub2(u2h(__byte_perm(x, 0x64646464u, 0x4140)), bias), scale, neg_min));
+  out2[1] = h2u(__hfma2(__hsub2(u2h(__byte_perm(x, 0x64646464u, 0x4342)), bias), scale, neg_min));
+}
+
 __device__ __forceinline__ float silu_tanh(float x) { return x * (tanhf(x * 0.5f) * 0.5f + 0.5f); }
 
 // D[tmem] (+)= A[smem desc] * B[smem desc].

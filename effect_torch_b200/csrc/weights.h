@@ -12,7 +12,7 @@ struct etc_qweight {
 
 namespace etc {
 etc_status build_qweight(etc_runtime* rt, int codec, const void* const* parts, const int64_t* part_rows, int n_parts,
-                         int64_t columns, int interleave8, int on_device, etc_qweight** out);
+                         int64_t columns, int interleave8, int on_device, etc_qweight** out, const int* part_codecs = nullptr);
 void destroy_qweight(etc_qweight* w);
 // Loads the device module that holds the fixed scratch array of etc_qlinear_tiled_static_into and resolves the array's
 // address on the current device (static_scratch.cu); this is when the driver reserves the array's 16 MiB.

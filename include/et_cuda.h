@@ -160,10 +160,14 @@ ETC_API etc_status etc_qlinear_into(etc_runtime* rt, etc_codec codec, const floa
                                     float* d_out, const volatile int* cancelled);
 
 /* Constant weights (ExecutableCompileOptions.constantWeights, packages/core/src/Runtime.ts:249-256):
- * a packed matrix retained by the backend in a device-friendly tiling (same dequantised values,
- * same byte count). `parts` are raw packed row ranges concatenated along rows (e.g. q,k,v);
- * interleave8 != 0 interleaves two equal parts in groups of 8 rows (gate/up), which lets the
- * linear's epilogue compute silu(gate)*up. Q4_0 / Q8_0 only; columns must be a multiple of 64.
+ * a packed matrix retained by the backend in a device-friendly tiling. `parts` are raw packed row
+ * ranges concatenated along rows (e.g. q,k,v); interleave8 != 0 interleaves two equal parts in groups
+ * of 8 rows (gate/up), which lets the linear's epilogue compute silu(gate)*up.
+ * Q4_0 / Q8_0 (columns a multiple of 64): same bytes, same dequantised values, reordered.
+ * Q3_K / Q4_K / Q5_K / Q6_K (columns a multiple of 256): every 256-value block is re-cut into eight
+ * 32-value blocks whose effective scales (d*sc) and minima (dmin*m) are rounded to f16 once, at load
+ * (20 B per 32 values for Q4_K, 36 B for the others). Q2_K and F32 are refused (ETC_UNSUPPORTED): they
+ * run through etc_qlinear_into on the raw layout.
  * Pointers are device pointers when on_device != 0, host pointers otherwise. */
 ETC_API etc_status etc_qweight_create(etc_runtime* rt, etc_codec codec, const void* const* parts,
                                       const int64_t* part_rows, int n_parts, int64_t columns, int interleave8,

@@ -106,6 +106,47 @@ def test_quantized_model_on_the_tensor_core_path(codec, kv_dtype, okv, tol):
     assert gdec.diagnostics()["launches_per_step"] > 0
 
 
+K_MIXES = {
+    # what the GGUF "medium" recipes produce: v (and down) at more bits than q / k in some layers
+    "q4_k_m": dict(wq=orc.Q4_K, wk=orc.Q4_K, wv=orc.Q6_K, wo=orc.Q4_K, gate=orc.Q4_K, up=orc.Q4_K, down=orc.Q6_K, head=orc.Q6_K),
+    "q3_k_m": dict(wq=orc.Q3_K, wk=orc.Q3_K, wv=orc.Q5_K, wo=orc.Q4_K, gate=orc.Q3_K, up=orc.Q3_K, down=orc.Q5_K, head=orc.Q6_K),
+    "all_different": dict(wq=orc.Q5_K, wk=orc.Q3_K, wv=orc.Q4_K, wo=orc.Q5_K, gate=orc.Q5_K, up=orc.Q5_K, down=orc.Q3_K, head=orc.Q4_K),
+}
+
+
+@pytest.mark.parametrize("mix", sorted(K_MIXES))
+def test_k_quant_model_with_mixed_codecs_stays_on_the_tensor_core_path(mix):
+    """Projections of different K-quants in one model, q / k / v of a layer included: the fused q/k/v weight holds one
+    segment per codec and the step keeps its tiled kernels (one more launch per extra segment and layer than a model of a
+    single codec). Teacher-forced logits against the oracle decoding the same packed bytes, within 4e-3: the re-cut rounds
+    every effective scale d*sc and minimum dmin*m to f16 once, at load, which is systematic over 32 values (it alone moves
+    these logits by 7e-4 when the oracle is run on the rounded weights) and comes on top of the f16 rounding of weights
+    and activations that every tiled model has; random code bytes with sub-scales uniform over 0..63 are the worst case."""
+    cfg = helpers.TINY_Q
+    codecs = K_MIXES[mix]
+    w = helpers.make_mixed_weights(cfg, codecs, seed=6)
+    rng = np.random.default_rng(7)
+    B = 3
+    odec = helpers.oracle_decoder(cfg, w, batch=B)
+    gdec = gpu_decoder(cfg, w, batch=B, max_tokens=256, kv_dtype=et.KV_F16, exact=False, max_advance=8)
+    opool = orc.Pool(cfg["layers"], cfg["kv_heads"], cfg["head_dim"], 256, 16, orc.F16)
+    gpool = et.NativeKvPool(runtime(), cfg["layers"], cfg["kv_heads"], cfg["head_dim"], 256, 16, et.KV_F16)
+    oseqs = [opool.make_sequence() for _ in range(B)]
+    gseqs = [gpool.makeSequence() for _ in range(B)]
+    for advance in (8, 5, 1, 1, 1):
+        toks = rng.integers(0, cfg["vocab"], size=(B, advance)).astype(np.uint32)
+        ol, _ = odec.execute(opool, oseqs, toks)
+        gl = gdec.execute(gpool, gseqs, toks)
+        assert helpers.rel_err(gl, ol) <= 2 * LOGIT_TOL, f"advance {advance}"
+    uniform = gpu_decoder(cfg, helpers.make_mixed_weights(cfg, {name: orc.Q4_K for name in codecs}, seed=6), batch=B, max_tokens=256,
+                          kv_dtype=et.KV_F16, exact=False, max_advance=8)
+    upool = et.NativeKvPool(runtime(), cfg["layers"], cfg["kv_heads"], cfg["head_dim"], 256, 16, et.KV_F16)
+    useqs = [upool.makeSequence() for _ in range(B)]
+    uniform.execute(upool, useqs, toks)
+    segments = len({codecs["wq"], codecs["wk"]}) + (codecs["wv"] != codecs["wk"])
+    assert gdec.diagnostics()["launches_per_step"] == uniform.diagnostics()["launches_per_step"] + cfg["layers"] * (segments - 1)
+
+
 def test_device_resident_generation_equals_stepwise_execution():
     cfg = helpers.TINY_Q
     w = helpers.make_weights(cfg, seed=4, codec=orc.Q4_0)

@@ -182,7 +182,7 @@ def test_tiled_linear_epilogues(codec, vectors):
     assert helpers.rel_err(host(both), expected_both) <= REL_TOL
 
 
-@pytest.mark.parametrize("codec", [gv.Q4_K, gv.Q6_K])
+@pytest.mark.parametrize("codec", [gv.Q3_K, gv.Q4_K, gv.Q5_K, gv.Q6_K])
 def test_k_quant_tiling_preserves_every_weight(codec):
     """The 256-value K-quant blocks are re-cut into 32-value blocks at load (effective scales rounded to f16): x = identity
     picks out single weights, which must equal the reference decode to the f16 precision of the MMA operands."""
@@ -196,7 +196,7 @@ def test_k_quant_tiling_preserves_every_weight(codec):
     np.testing.assert_allclose(host(out).T, deq, rtol=2.0 ** -9, atol=scale * 2.0 ** -10)
 
 
-@pytest.mark.parametrize("codec", [gv.Q4_K, gv.Q6_K])
+@pytest.mark.parametrize("codec", [gv.Q3_K, gv.Q4_K, gv.Q5_K, gv.Q6_K])
 @pytest.mark.parametrize("rows,columns", [(256, 512), (200, 1024), (1024, 4096)])
 @pytest.mark.parametrize("vectors", [1, 8, 17, 32, 64, 300])
 def test_k_quant_tiled_linear_matches_the_oracle(codec, rows, columns, vectors):
@@ -210,7 +210,7 @@ def test_k_quant_tiled_linear_matches_the_oracle(codec, rows, columns, vectors):
     assert helpers.rel_err(host(out), expected) <= REL_TOL
 
 
-@pytest.mark.parametrize("codec", [gv.Q4_K, gv.Q6_K])
+@pytest.mark.parametrize("codec", [gv.Q3_K, gv.Q4_K, gv.Q5_K, gv.Q6_K])
 def test_k_quant_fused_gate_up_and_residual_epilogues(codec):
     rng = np.random.default_rng(21)
     d, ffn, vectors = 512, 256, 20
@@ -236,7 +236,7 @@ def test_tiled_weight_rejects_unsupported_geometry():
     raw = empty((16, 18 * 3), dtype=torch.uint8)
     with pytest.raises(et.BackendError, match="multiple of 64"):
         et.QWeight(rt, gv.Q4_0, [raw], [16], 96)
-    with pytest.raises(et.BackendError, match="Q4_0, Q8_0, Q4_K and Q6_K"):
-        et.QWeight(rt, gv.Q5_K, [empty((16, 176), dtype=torch.uint8)], [16], 256)
+    with pytest.raises(et.BackendError, match="Q4_0, Q8_0, Q3_K, Q4_K, Q5_K and Q6_K"):
+        et.QWeight(rt, gv.Q2_K, [empty((16, 84), dtype=torch.uint8)], [16], 256)
     with pytest.raises(et.BackendError, match="multiple of 256"):
         et.QWeight(rt, gv.Q4_K, [raw], [16], 128)
