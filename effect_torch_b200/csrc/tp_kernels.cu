@@ -4,8 +4,9 @@
 // Every rank owns one exported region (layout: kTp* in kernels.h): three flag arrays (one 32-bit epoch per peer,
 // written BY that peer), a table of (best logit, token) pairs, and two exchange buffers that the o and down projections
 // alternate between, each an inbox with one slot per sender and a table of totals. Data moves by plain STORES into the
-// peers' regions over NVLink (posted writes: no round trip is waited for), followed by a system-wide fence and a release
-// store of the epoch into the peer's flag array; all reads are local. Nothing here uses multicast.
+// peers' regions over NVLink (posted writes: no round trip is waited for), followed by a system-wide fence and a store
+// of the epoch into the peer's flag array; all reads are local: a warp polls all peers' flags at once with relaxed loads
+// and fences once when they have all arrived. Nothing here uses multicast.
 //
 //   one shot (up to 4 ranks, or forced): every rank stores its whole partial sum into slot `rank` of every rank's inbox; after
 //     one flag exchange every rank adds the slots in rank order onto its hidden state. (world - 1) x message bytes leave
@@ -20,10 +21,10 @@
 // split-K partials on the way out, so that projection needs no sum launch of its own. Two buffers suffice: a rank can
 // only store for the second next all-reduce after every peer entered the next one, i.e. finished reading this one.
 //
-// CTAs of one launch wait for one another at the phase boundaries (a slice's slots are filled by all CTAs); the grid is
-// at most one CTA of 256 threads per SM without shared memory, launched after the previous kernel of the stream has
-// ended, so all of them are resident. Every wait is bounded by `wait_cycles`: on expiry the kernel records status code 4
-// and returns.
+// CTAs of one launch never wait for one another: a thread only reads entries of this rank's own slot and of the hidden
+// state that it wrote itself, everything else comes from peers and is guarded by their flags; the last CTA to arrive at a
+// phase counter publishes this rank's flag. Every wait is bounded by `wait_cycles`: on expiry the kernel records status
+// code 4 and returns.
 #include <algorithm>
 
 #include "kernels.h"
@@ -32,19 +33,6 @@ namespace etc {
 
 namespace {
 
-__device__ __forceinline__ void store_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t load_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ uint32_t load_acquire_gpu(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
 // data a peer stored into this rank's region: never from a stale L1 line
 __device__ __forceinline__ float4 load_inbox4(const float4* p) {
   float4 v;
@@ -55,36 +43,56 @@ __device__ __forceinline__ void store_peer4(float4* p, const float4& v) {
   asm volatile("st.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
 
-// Thread 0 of a CTA: waits until every peer has published `epoch` into flag array `which` of this rank's region.
+__device__ __forceinline__ uint32_t load_relaxed_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void store_relaxed_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// All 32 lanes of a CTA's first warp: lane r watches peer r's entry of flag array `which` in this rank's region, all
+// peers at once, until every peer has published `epoch`; one system-wide fence then orders the inbox reads that follow
+// (relaxed polls + fence instead of one acquire load after another: the cost does not grow with the number of ranks).
 __device__ bool wait_for_peers(const PeerView& pv, int which, uint32_t epoch, long long start, long long wait_cycles) {
-  for (int r = 0; r < pv.world; ++r) {
-    if (r == pv.rank) continue;
-    while ((int32_t)(load_acquire_sys(pv.flags[pv.rank] + which * kTpFlagStride + r) - epoch) < 0) {
-      if (clock64() - start > wait_cycles) return false;
-      __nanosleep(100);
+  const int r = threadIdx.x & 31;
+  const bool mine = r < pv.world && r != pv.rank;
+  const uint32_t* flag = pv.flags[pv.rank] + which * kTpFlagStride + (mine ? r : pv.rank);
+  bool arrived = false;
+  for (;;) {
+    const bool ready = !mine || (int32_t)(load_relaxed_sys(flag) - epoch) >= 0;
+    if (__all_sync(0xffffffffu, ready)) {
+      arrived = true;
+      break;
     }
+    if (__any_sync(0xffffffffu, clock64() - start > wait_cycles)) break;
+    __nanosleep(40);
   }
-  return true;
-}
-__device__ void publish_to_peers(const PeerView& pv, int which, uint32_t epoch) {
-  for (int r = 0; r < pv.world; ++r)
-    if (r != pv.rank) store_release_sys(pv.flags[r] + which * kTpFlagStride + pv.rank, epoch);
-}
-// Thread 0 of a CTA, after a __syncthreads that follows the CTA's stores: fences them system-wide and arrives at phase
-// counter `bar`; the last CTA of the grid to arrive publishes flag array `which` to the peers.
-__device__ void arrive_and_publish(const PeerView& pv, uint32_t* bar, int which, uint32_t epoch) {
   __threadfence_system();
-  if (atomicAdd(bar, 1u) == gridDim.x - 1) {
+  __syncwarp();
+  return arrived;
+}
+// First warp of a CTA, after its lane 0 fenced what has to be visible: lane r stores the epoch into peer r's flag array.
+__device__ void publish_to_peers(const PeerView& pv, int which, uint32_t epoch) {
+  const int r = threadIdx.x & 31;
+  __syncwarp();
+  if (r < pv.world && r != pv.rank) {
     __threadfence_system();
-    publish_to_peers(pv, which, epoch);
+    store_relaxed_sys(pv.flags[r] + which * kTpFlagStride + pv.rank, epoch);
   }
 }
-__device__ bool wait_for_grid(const uint32_t* bar, long long start, long long wait_cycles) {
-  while (load_acquire_gpu(bar) < gridDim.x) {
-    if (clock64() - start > wait_cycles) return false;
-    __nanosleep(50);
+// First warp of a CTA, after a __syncthreads that follows the CTA's stores: lane 0 fences them system-wide and arrives at
+// phase counter `bar`; the warp of the last CTA of the grid to arrive publishes flag array `which` to the peers.
+__device__ void arrive_and_publish(const PeerView& pv, uint32_t* bar, int which, uint32_t epoch) {
+  int last = 0;
+  if ((threadIdx.x & 31) == 0) {
+    __threadfence_system();
+    last = atomicAdd(bar, 1u) == gridDim.x - 1;
+    if (last) __threadfence_system();
   }
-  return true;
+  last = __shfl_sync(0xffffffffu, last, 0);
+  if (last) publish_to_peers(pv, which, epoch);
 }
 
 // ctr: [0] epoch of the last completed all-reduce, [1] CTAs done, [2] / [3] phase arrivals, [4] epoch of the last pick exchange
@@ -127,10 +135,12 @@ __global__ void __launch_bounds__(256) tp_allreduce_kernel(PeerView pv, int buff
     }
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
+  if (threadIdx.x < 32) {
     arrive_and_publish(pv, ctr + 2, 0, epoch);
-    // the slots of this rank's inbox are filled by the peers and by every CTA of this grid
-    if (!wait_for_grid(ctr + 2, start, wait_cycles) || !wait_for_peers(pv, 0, epoch, start, wait_cycles)) ok_s = 0;
+    // the peers fill the other slots of this rank's inbox; the entries of its own slot that a thread adds up below are
+    // the ones that same thread stored above, so CTAs of this grid do not wait for one another
+    const bool arrived = wait_for_peers(pv, 0, epoch, start, wait_cycles);
+    if (threadIdx.x == 0 && !arrived) ok_s = 0;
   }
   __syncthreads();
   const float4* inbox = reinterpret_cast<const float4*>(pv.inbox[rank][buffer]);
@@ -147,7 +157,9 @@ __global__ void __launch_bounds__(256) tp_allreduce_kernel(PeerView pv, int buff
   } else {
     const size_t lo = slice * rank < count4 ? slice * rank : count4, hi = lo + slice < count4 ? lo + slice : count4;
     // ---- phase B: total of this rank's slice, onto its own hidden state and out to every peer's table of totals
-    for (size_t j = tid; lo + j < hi && ok_s; j += stride) {
+    for (size_t i = tid; i < hi && ok_s; i += stride) {  // the elements of the slice that this thread sent in phase A
+      if (i < lo) continue;
+      const size_t j = i - lo;
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
       for (int r = 0; r < world; ++r) {
         const float4 p = load_inbox4(inbox + (size_t)r * slice + j);
@@ -159,9 +171,11 @@ __global__ void __launch_bounds__(256) tp_allreduce_kernel(PeerView pv, int buff
         if (q != rank) store_peer4(reinterpret_cast<float4*>(pv.totals[q][buffer]) + lo + j, acc);
     }
     __syncthreads();
-    if (threadIdx.x == 0 && ok_s) {
+    if (threadIdx.x < 32 && ok_s) {  // ok_s is not written between the barriers around this block's predecessor and here
       arrive_and_publish(pv, ctr + 3, 1, epoch);
-      if (!wait_for_peers(pv, 1, epoch, start, wait_cycles)) ok_s = 0;
+      const bool arrived = wait_for_peers(pv, 1, epoch, start, wait_cycles);
+      __syncwarp();
+      if (threadIdx.x == 0 && !arrived) ok_s = 0;
     }
     __syncthreads();
     // ---- phase C: the other slices' totals onto the hidden state
@@ -194,10 +208,11 @@ __global__ void __launch_bounds__(256) tp_pick_kernel(PeerView pv, int batch, ui
                                                       long long wait_cycles, unsigned long long* status) {
   __shared__ int ok_s;
   const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(ctr + 4) + 1;
-  if (threadIdx.x == 0) {
-    __threadfence_system();  // the argmax kernel that wrote this rank's pairs finished before this kernel started
+  if (threadIdx.x < 32) {
+    if (threadIdx.x == 0) __threadfence_system();  // the argmax kernel that wrote this rank's pairs finished before this kernel started
     publish_to_peers(pv, 2, epoch);
-    ok_s = wait_for_peers(pv, 2, epoch, clock64(), wait_cycles) ? 1 : 0;
+    const bool arrived = wait_for_peers(pv, 2, epoch, clock64(), wait_cycles);
+    if (threadIdx.x == 0) ok_s = arrived ? 1 : 0;
   }
   __syncthreads();
   if (ok_s) {
