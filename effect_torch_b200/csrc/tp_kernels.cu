@@ -27,6 +27,9 @@
 // code 4 and returns.
 #include <algorithm>
 
+#include <cstdlib>
+
+#include "chain.cuh"
 #include "kernels.h"
 
 namespace etc {
@@ -99,9 +102,12 @@ __device__ void arrive_and_publish(const PeerView& pv, uint32_t* bar, int which,
 template <bool TWO_SHOT>
 __global__ void __launch_bounds__(256) tp_allreduce_kernel(PeerView pv, int buffer, float* __restrict__ hidden, size_t count4,
                                                            DeferredSum sum, int columns, const float* __restrict__ partial,
-                                                           uint32_t* ctr, long long wait_cycles, unsigned long long* status) {
+                                                           uint32_t* ctr, long long wait_cycles, unsigned long long* status,
+                                                           int chain) {
   __shared__ uint32_t epoch_s;
   __shared__ int ok_s;
+  if (chain >= 1) chain_release();  // the kernel after this one may be scheduled; it waits for this one to complete
+  if (chain >= 2) chain_wait();     // launched under the projection's tail: its partials are complete from here on
   const size_t tid = blockIdx.x * (size_t)blockDim.x + threadIdx.x, stride = (size_t)gridDim.x * blockDim.x;
   const long long start = clock64();
   if (threadIdx.x == 0) {
@@ -245,11 +251,21 @@ cudaError_t launch_tp_allreduce(const PeerView& view, int buffer, float* hidden,
   const size_t count4 = count / 4;
   // every thread has a few 16-byte stores in flight; no more CTAs than SMs, so that all of them are resident
   const unsigned grid = (unsigned)std::min<size_t>((size_t)std::max(1, sm_count), std::max<size_t>(1, (count4 + 1023) / 1024));
-  // launched the ordinary way: as a chained launch (scheduled under the projection's tail) the step measured 0.9 ms slower
-  // at 4 ranks, 160 all-reduces per step
+  // How the kernel sits in the stream's chain of programmatic launches (ETC_TP_CHAIN overrides, for measurements):
+  //   1 (default) launched the ordinary way, after the projection has ended, but it lets the kernel after it be
+  //     scheduled at once, so that kernel's launch hides behind the exchange: 16.85 ms per step at 4 ranks;
+  //   0 no early scheduling either: 17.0 ms;  2 also launched under the projection's tail: 18.05 ms (measured slower twice).
+  static const int chain = [] {
+    const char* v = std::getenv("ETC_TP_CHAIN");
+    return v ? std::atoi(v) : 1;
+  }();
   unsigned long long* code = &status->code;
-  if (two_shot) tp_allreduce_kernel<true><<<grid, 256, 0, stream>>>(view, buffer, hidden, count4, sum, columns, partial, counters, wait_cycles, code);
-  else tp_allreduce_kernel<false><<<grid, 256, 0, stream>>>(view, buffer, hidden, count4, sum, columns, partial, counters, wait_cycles, code);
+  if (chain >= 2) {
+    if (two_shot) return launch_chained(tp_allreduce_kernel<true>, dim3(grid), dim3(256), 0, stream, view, buffer, hidden, count4, sum, columns, partial, counters, wait_cycles, code, chain);
+    return launch_chained(tp_allreduce_kernel<false>, dim3(grid), dim3(256), 0, stream, view, buffer, hidden, count4, sum, columns, partial, counters, wait_cycles, code, chain);
+  }
+  if (two_shot) tp_allreduce_kernel<true><<<grid, 256, 0, stream>>>(view, buffer, hidden, count4, sum, columns, partial, counters, wait_cycles, code, chain);
+  else tp_allreduce_kernel<false><<<grid, 256, 0, stream>>>(view, buffer, hidden, count4, sum, columns, partial, counters, wait_cycles, code, chain);
   return cudaGetLastError();
 }
 
