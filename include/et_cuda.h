@@ -381,7 +381,9 @@ ETC_API etc_status etc_decoder_set_tensor_parallel(etc_decoder* dec, int rank, i
  * 64-byte handle of its exchange region, the host gathers the handles of all ranks into a table [world][64] (own slot
  * ignored) and every rank imports it. The kernel's wait for its peers is bounded: a rank that never arrives turns
  * into ETC_EXECUTION at the next synchronising call, not into a hang. ETC_TP_TWO_SHOT=0 or 1 in the environment of the
- * importing call forces the one-shot or the reduce-scatter + all-gather form (every rank must use the same).
+ * importing call forces the one-shot or the reduce-scatter + all-gather form (every rank must use the same);
+ * ETC_TP_CHAIN=0, 1 or 2 picks how the exchange kernel is launched relative to its neighbours (1, the default: after
+ * the projection has ended, releasing its successor early), a knob for measurements only.
  * Two duties stay with the host, because a rank only sees its own status. (1) After every step the ranks exchange
  * their step status over the host transport; when any rank failed, every rank treats the step as failed (a rank whose
  * own call returned ETC_OK has committed already: it releases the affected sequences and re-creates them, as it would
