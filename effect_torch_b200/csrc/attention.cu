@@ -734,11 +734,30 @@ __global__ void rope_append_kernel(PoolView pool, const float* __restrict__ qkv,
   const bool is_q = head < q_heads, is_k = !is_q && head < q_heads + pool.kv_heads;
   float r0, r1;
   if (sum.splits > 0) {  // the projection left its split-K partials unsummed: add them up here, in split order
+    // (a narrow shard of a tensor-parallel group has up to 32 splits: eight loads are in flight at a time)
     r0 = r1 = 0.f;
-    for (int s = 0; s < sum.splits; ++s) {
-      const float* p = sum.partials + ((size_t)s * sum.vpad + row) * sum.rows_padded + (size_t)head * D;
-      r0 += p[i0];
-      r1 += p[i1];
+    const float* p = sum.partials + row * sum.rows_padded + (size_t)head * D;
+    const size_t split_stride = (size_t)sum.vpad * sum.rows_padded;
+    if (sum.splits <= 8) {
+      for (int s = 0; s < sum.splits; ++s) {
+        r0 += p[(size_t)s * split_stride + i0];
+        r1 += p[(size_t)s * split_stride + i1];
+      }
+    } else for (int s0 = 0; s0 < sum.splits; s0 += 8) {
+      float first[8], second[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const bool live = s0 + u < sum.splits;
+        first[u] = live ? p[(size_t)(s0 + u) * split_stride + i0] : 0.f;
+        second[u] = live ? p[(size_t)(s0 + u) * split_stride + i1] : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (s0 + u < sum.splits) {
+          r0 += first[u];
+          r1 += second[u];
+        }
+      }
     }
   } else {
     r0 = src[i0];
