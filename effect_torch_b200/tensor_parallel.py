@@ -1,7 +1,7 @@
 """Host-side sharding for tensor parallelism: which part of every weight a rank holds, and the local geometry its
 decoder is built with. Column-parallel projections (wq, wk, wv, gate, up) split the ROWS of the reference's [N, K]
-weights; row-parallel ones (wo, down) split K, i.e. a range of 32-value blocks of every packed row (quantized rows are
-sequences of blocks: crates/runtime-cpu/src/quantized.rs:263-292). Embedding and norms are replicated; the head is
+weights; row-parallel ones (wo, down) split K, i.e. a range of whole blocks of every packed row (quantized rows are
+sequences of 32- or 256-value blocks: crates/runtime-cpu/src/quantized.rs:263-292). Embedding and norms are replicated; the head is
 replicated or, with shard_head, cut by rows (vocabulary parallel: every rank scores vocab / world tokens and the ranks
 exchange their best).
 
@@ -9,7 +9,9 @@ Works on numpy arrays and on torch tensors alike (only slicing, reshape and cont
 """
 from __future__ import annotations
 
-BLOCK_BYTES = {0: None, 2: 18, 8: 34}  # codec -> bytes per 32-value block (0 = dense f32)
+# codec -> (values, bytes) of one block; 0 = dense f32. Q4_0 / Q8_0 blocks hold 32 values, the K-quants 256
+# (crates/runtime/src/gguf.rs:245-291).
+BLOCKS = {2: (32, 18), 8: (32, 34), 10: (256, 84), 11: (256, 110), 12: (256, 144), 13: (256, 176), 14: (256, 210)}
 ROW_SPLIT = ("wq", "wk", "wv", "gate", "up")
 COLUMN_SPLIT = ("wo", "down")
 
@@ -56,8 +58,10 @@ def shard_rows(weight, rank: int, world: int):
 
 
 def shard_columns(weight, codec: int, rank: int, world: int):
-    """Columns [rank * K / world, (rank + 1) * K / world) of every row: f32 elements, or whole 32-value blocks."""
-    unit = 1 if codec == 0 else BLOCK_BYTES[codec]
+    """Columns [rank * K / world, (rank + 1) * K / world) of every row: f32 elements, or whole blocks of the codec."""
+    if codec != 0 and codec not in BLOCKS:
+        raise ValueError(f"unknown block codec {codec}")
+    unit = 1 if codec == 0 else BLOCKS[codec][1]
     width = weight.shape[1]
     if width % unit:
         raise ValueError("row width is not a whole number of blocks")
@@ -71,20 +75,21 @@ def shard_columns(weight, codec: int, rank: int, world: int):
 
 def shard_weights(weights: dict, cfg: dict, rank: int, world: int, shard_head: bool = False) -> dict:
     """One rank's share of a weight dictionary laid out like tests/helpers.make_weights: projections are either dense
-    [N, K] arrays or (packed, rows, columns) tuples."""
+    [N, K] arrays or (packed, rows, columns[, codec]) tuples."""
     check_geometry(cfg, world)
     codec = weights["codec"]
 
     def rows(value):
         if isinstance(value, tuple):
-            packed, n, k = value
-            return (shard_rows(packed, rank, world), n // world, k)
+            packed, n, k = value[:3]
+            return (shard_rows(packed, rank, world), n // world, k) + tuple(value[3:])
         return shard_rows(value, rank, world)
 
     def columns(value):
-        if isinstance(value, tuple):
-            packed, n, k = value
-            return (shard_columns(packed, codec, rank, world), n, k // world)
+        if isinstance(value, tuple):  # (packed, rows, columns) of the dictionary's codec, or with a codec of its own as 4th entry
+            packed, n, k = value[:3]
+            own = value[3] if len(value) > 3 else codec
+            return (shard_columns(packed, own, rank, world), n, k // world) + tuple(value[3:])
         return shard_columns(value, 0, rank, world)
 
     head = rows(weights["head"]) if shard_head and world > 1 else weights["head"]

@@ -43,6 +43,35 @@ def test_row_and_column_shards_recombine_to_the_full_linear(codec):
                                   orc.dequantize(codec, packed, n, k)[:, kk:])
 
 
+@pytest.mark.parametrize("codec", [gv.Q3_K, gv.Q4_K, gv.Q5_K, gv.Q6_K])
+def test_k_quant_shards_cut_whole_256_value_blocks(codec):
+    rng = np.random.default_rng(8)
+    n, k, world = 64, 1024, 2
+    packed = helpers.random_k_quant(codec, n, k, rng)
+    full = orc.dequantize(codec, packed, n, k)
+    kk = k // world
+    for r in range(world):
+        np.testing.assert_array_equal(orc.dequantize(codec, tp.shard_columns(packed, codec, r, world), n, kk), full[:, r * kk:(r + 1) * kk])
+        np.testing.assert_array_equal(orc.dequantize(codec, tp.shard_rows(packed, r, world), n // world, k), full[r * n // world:(r + 1) * n // world])
+    with pytest.raises(ValueError, match="not divisible"):
+        tp.shard_columns(helpers.random_k_quant(codec, 4, 768, rng), codec, 0, 2)  # three blocks per row
+
+
+def test_shard_weights_keeps_every_projections_own_codec():
+    cfg = helpers.TINY_Q
+    codecs = dict(wq=gv.Q4_K, wk=gv.Q4_K, wv=gv.Q6_K, wo=gv.Q4_K, gate=gv.Q4_K, up=gv.Q4_K, down=gv.Q6_K, head=gv.Q6_K)
+    cfg = dict(cfg, ffn=1024, q_heads=8)  # a rank's share of the columns of down and wo must be whole 256-value blocks
+    weights = helpers.make_mixed_weights(cfg, codecs, seed=3)
+    shards = [tp.shard_weights(weights, cfg, r, 2, shard_head=True) for r in range(2)]
+    for name in tp.ROW_SPLIT + tp.COLUMN_SPLIT:
+        packed, n, k, codec = weights["layers"][1][name]
+        axis = 0 if name in tp.ROW_SPLIT else 1
+        got = np.concatenate([s["layers"][1][name][0] for s in shards], axis=axis)
+        np.testing.assert_array_equal(got, packed)
+        assert shards[1]["layers"][1][name][1:] == ((n // 2, k, codec) if axis == 0 else (n, k // 2, codec))
+    assert shards[0]["head"][1:] == (cfg["vocab"] // 2, cfg["d_model"], gv.Q6_K)
+
+
 def test_shard_weights_covers_every_projection():
     cfg = helpers.TINY_Q
     weights = helpers.make_weights(cfg, seed=2, codec=gv.Q4_0)
