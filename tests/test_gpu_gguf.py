@@ -58,8 +58,8 @@ def _llama_file(cfg, weights, path):
     def add(name, value):
         nonlocal offset
         if isinstance(value, tuple):
-            packed, rows, cols = value
-            raw, dims, code = packed.tobytes(), [cols, rows], weights["codec"]
+            packed, rows, cols = value[:3]
+            raw, dims, code = packed.tobytes(), [cols, rows], value[3] if len(value) > 3 else weights["codec"]
         else:
             raw, dims, code = np.ascontiguousarray(value, dtype=np.float32).tobytes(), list(reversed(value.shape)), 0
         tensors.append((name, dims, code, offset, len(raw)))
@@ -108,3 +108,39 @@ def test_a_llama_shaped_decoder_loads_from_a_gguf_file(tmp_path):
         expected, _ = odec.execute(opool, oseqs, toks)
         np.testing.assert_array_equal(from_file, from_memory)  # same bytes, same kernels
         assert helpers.rel_err(from_file, expected) <= 2e-3
+
+
+def test_a_file_of_mixed_k_quants_loads_onto_the_tiled_kernels(tmp_path):
+    """What a "medium" K-quant recipe writes: attn_v and ffn_down at more bits than the other projections. Every tensor keeps
+    the codec the file gives it; q/k/v fuse as segments of one tiled weight. Same logits as a decoder fed the same packed
+    bytes from memory, and the oracle's within the tolerance of the re-cut K-quants."""
+    import effect_torch_b200 as et
+    from effect_torch_b200.gguf import load_llama_decoder
+
+    cfg = helpers.TINY_Q
+    codecs = dict(wq=gv.Q4_K, wk=gv.Q4_K, wv=gv.Q6_K, wo=gv.Q4_K, gate=gv.Q4_K, up=gv.Q4_K, down=gv.Q6_K, head=gv.Q6_K)
+    weights = helpers.make_mixed_weights(cfg, codecs, seed=9)
+    path = tmp_path / "tiny_q4_k_m.gguf"
+    _llama_file(cfg, weights, path)
+    rt = runtime()
+    B = 2
+    loaded, _ = load_llama_decoder(rt, str(path), batch=B, max_tokens=128, kv_dtype=et.KV_F16, max_advance=8)
+    direct = et.Executable(rt, layers=cfg["layers"], d_model=cfg["d_model"], q_heads=cfg["q_heads"], kv_heads=cfg["kv_heads"],
+                           head_dim=cfg["head_dim"], ffn=cfg["ffn"], vocab=cfg["vocab"], rms_eps=cfg["rms_eps"], rope_theta=cfg["rope_theta"],
+                           batch=B, max_tokens=128, block_size=16, kv_dtype=et.KV_F16, exact=False, max_advance=8)
+    helpers.load_into(direct, weights)
+    direct.finalize()
+    odec = helpers.oracle_decoder(cfg, weights, batch=B)
+    opool = orc.Pool(cfg["layers"], cfg["kv_heads"], cfg["head_dim"], 128, 16, orc.F16)
+    oseqs = [opool.make_sequence() for _ in range(B)]
+    pools = [et.NativeKvPool(rt, cfg["layers"], cfg["kv_heads"], cfg["head_dim"], 128, 16, et.KV_F16) for _ in range(2)]
+    seqs = [[p.makeSequence() for _ in range(B)] for p in pools]
+    rng = np.random.default_rng(10)
+    for advance in (8, 1, 1):
+        toks = rng.integers(0, cfg["vocab"], size=(B, advance)).astype(np.uint32)
+        from_file = loaded.execute(pools[0], seqs[0], toks)
+        from_memory = direct.execute(pools[1], seqs[1], toks)
+        expected, _ = odec.execute(opool, oseqs, toks)
+        np.testing.assert_array_equal(from_file, from_memory)
+        assert helpers.rel_err(from_file, expected) <= 4e-3
+    assert loaded.diagnostics()["launches_per_step"] == direct.diagnostics()["launches_per_step"] > 0
