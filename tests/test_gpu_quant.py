@@ -182,6 +182,39 @@ def test_tiled_linear_epilogues(codec, vectors):
     assert helpers.rel_err(host(both), expected_both) <= REL_TOL
 
 
+@pytest.mark.parametrize("codec,ffn,d,vectors", [(gv.Q4_0, 9728, 512, 20), (gv.Q4_0, 14336, 1024, 33), (gv.Q8_0, 9600, 256, 32)])
+def test_single_split_launch_with_more_tiles_than_sms(codec, ffn, d, vectors):
+    """More 128-row tiles than SMs and not a multiple of them (152, 224 and 150 tiles on 148 SMs), one split: the SwiGLU
+    epilogue over interleaved gate/up rows and bias + residual over plain rows, each run twice and bit-identical."""
+    rng = np.random.default_rng(ffn + d)
+    gate = rng.normal(0, 0.05, size=(ffn, d)).astype(np.float32)
+    up = rng.normal(0, 0.05, size=(ffn, d)).astype(np.float32)
+    pg, pu = orc.quantize(codec, gate), orc.quantize(codec, up)
+    x = rng.normal(size=(vectors, d)).astype(np.float32)
+    rt = runtime()
+    qgu = et.QWeight(rt, codec, [dev(pg), dev(pu)], [ffn, ffn], d, interleave8=True)
+    expected_act = orc.silu_mul(orc.qlinear(codec, x, pg, ffn, d, threads=8), orc.qlinear(codec, x, pu, ffn, d, threads=8))
+    runs = []
+    for _ in range(2):
+        act = empty((vectors, ffn))
+        qgu.linear_into(dev(x), vectors, act, epilogue=et.EPILOGUE_SWIGLU)
+        runs.append(host(act))
+        assert helpers.rel_err(runs[-1], expected_act) <= REL_TOL
+    np.testing.assert_array_equal(runs[0], runs[1])
+    plain = et.QWeight(rt, codec, [dev(pg), dev(pu)], [ffn, ffn], d)
+    bias = rng.normal(size=2 * ffn).astype(np.float32)
+    residual = rng.normal(size=(vectors, 2 * ffn)).astype(np.float32)
+    expected = residual + np.concatenate([orc.qlinear(codec, x, pg, ffn, d, bias[:ffn], threads=8),
+                                          orc.qlinear(codec, x, pu, ffn, d, bias[ffn:], threads=8)], axis=1)
+    runs = []
+    for _ in range(2):
+        out = empty((vectors, 2 * ffn))
+        plain.linear_into(dev(x), vectors, out, bias=dev(bias), residual=dev(residual), epilogue=et.EPILOGUE_RESIDUAL)
+        runs.append(host(out))
+        assert helpers.rel_err(runs[-1], expected) <= REL_TOL
+    np.testing.assert_array_equal(runs[0], runs[1])
+
+
 @pytest.mark.parametrize("codec", [gv.Q3_K, gv.Q4_K, gv.Q5_K, gv.Q6_K])
 def test_k_quant_tiling_preserves_every_weight(codec):
     """The 256-value K-quant blocks are re-cut into 32-value blocks at load (effective scales rounded to f16): x = identity
