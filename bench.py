@@ -238,8 +238,30 @@ def run_reference_arm(args, rank):
 
 
 # ------------------------------------------------------------------------------------------------ GPU arm
+# K-quants (256-value blocks): bytes per block in the file, byte offsets of the f16 block scales, and the bytes the tiled
+# form streams per 32 values (Q4_K: nibbles + two f16; the others: int8 codes + two f16)
+K_BLOCK_BYTES = {11: 110, 12: 144, 13: 176, 14: 210}
+K_SCALE_FIELDS = {11: (108,), 12: (0, 2), 13: (0, 2), 14: (208,)}
+K_TILED_BYTES_PER_32 = {11: 36, 12: 20, 13: 36, 14: 36}
+K_NAMES = {11: "Q3_K", 12: "Q4_K", 13: "Q5_K", 14: "Q6_K"}
+
+
+def device_random_k_quant(torch, codec, rows, cols, gen):
+    """Packed K-quant rows from random bytes with a small finite f16 block scale: every bit pattern of the code and
+    sub-scale bytes is legal, the library has no K-quant quantizer, and the kernel's time does not depend on the values."""
+    bb, blocks = K_BLOCK_BYTES[codec], cols // 256
+    packed = torch.randint(0, 256, (rows, blocks, bb), generator=gen, device="cuda", dtype=torch.uint8)
+    scale = torch.tensor([1e-4], dtype=torch.float16).view(torch.uint8).to("cuda")
+    for off in K_SCALE_FIELDS[codec]:
+        packed[:, :, off:off + 2] = scale
+    torch.cuda.synchronize()  # drawn on torch's stream, read on the library's
+    return packed.view(rows, blocks * bb)
+
+
 def device_quantized(rt, torch, codec, rows, cols, gen):
     """[rows, cols] ~ N(0, 0.02) drawn on the device in slabs and packed by the library's quantizer."""
+    if codec in K_BLOCK_BYTES:
+        return device_random_k_quant(torch, codec, rows, cols, gen)
     bb = 18 if codec == Q4_0 else 34
     packed = torch.empty((rows, cols // 32 * bb), dtype=torch.uint8, device="cuda")
     step = 32768
@@ -299,7 +321,8 @@ def time_linear(rt, et, torch, codec, rows, cols, vectors, interleave=False, epi
     """One tiled linear shape alone: CUDA events around replays of a graph that walks over more weight copies than L2
     holds. Returns (microseconds per call, algorithmic bytes per call). The call includes the linear's own f16 conversion
     of the activations and, above 16 vectors, its split-K sum launch."""
-    bb = 18 if codec == Q4_0 else 34
+    # bytes of weights one call streams: the file's encoding for Q4_0 / Q8_0, the re-cut tiled form for the K-quants
+    bb = K_TILED_BYTES_PER_32[codec] if codec in K_BLOCK_BYTES else (18 if codec == Q4_0 else 34)
     nparts = 2 if interleave else 1
     packed_bytes = rows * (cols // 32) * bb
     copies = max(3, int(np.ceil(target_bytes / packed_bytes)))
@@ -386,6 +409,23 @@ def linear_microbench_table(rt, et, torch, peaks):
                                  "gbs": round(algorithmic / us / 1e3, 1), "hbm_frac": round(algorithmic / us / 1e3 / peaks["hbm_gbs"], 3),
                                  "tflops": round(2.0 * m * n * k / us / 1e6, 1),
                                  "tensor_frac": round(2.0 * m * n * k / us / 1e6 / peaks["bf16_tflops"], 3)})
+    return rows_out
+
+
+def k_quant_microbench_table(rt, et, torch, peaks):
+    """One row per K-quant with a tiled form: the FFN up-projection shape [14336x4096] at 32 and 512 vectors through the
+    tcgen05 linear. `gbs` counts the bytes the re-cut form streams (20 B per 32 values for Q4_K, 36 B for the others)."""
+    rows_out = []
+    for codec in sorted(K_BLOCK_BYTES):
+        for m in (32, 512):
+            try:
+                us, algorithmic = time_linear(rt, et, torch, codec, 14336, 4096, m)
+                rows_out.append({"codec": K_NAMES[codec], "rows": 14336, "columns": 4096, "vectors": m, "us": round(us, 2),
+                                 "gbs": round(algorithmic / us / 1e3, 1), "hbm_frac": round(algorithmic / us / 1e3 / peaks["hbm_gbs"], 3),
+                                 "tflops": round(2.0 * m * 14336 * 4096 / us / 1e6, 1),
+                                 "tensor_frac": round(2.0 * m * 14336 * 4096 / us / 1e6 / peaks["bf16_tflops"], 3)})
+            except Exception as error:  # a row that cannot be timed is reported, it does not cost the line
+                rows_out.append({"codec": K_NAMES[codec], "rows": 14336, "columns": 4096, "vectors": m, "error": str(error)[:200]})
     return rows_out
 
 
@@ -753,6 +793,7 @@ def run_gpu_arm(args, rank, world):
                                                         pages, peaks, peak_kind, f"the decode step's launch: {BATCH} sequences at context {int(mean_ctx)}")
         if not args.no_microbench and world == 1:
             line["linear_microbench"] = linear_microbench_table(rt, et, torch, peaks)
+            line["k_quant_microbench"] = k_quant_microbench_table(rt, et, torch, peaks)
             rng_c2 = np.random.default_rng(1)
             ctx_c2 = rng_c2.integers(128, 4097, size=64)
             line["attention_microbench"] = time_attention(rt, et, torch, 64, 32, 8, 128, ctx_c2, 65536, peaks, peak_kind,
