@@ -38,7 +38,7 @@ const toBackendError = (operation: string, phase: Phase) => (error: unknown): Ru
   const head = cut > 0 ? text.slice(0, cut) : ""
   const known = reasons.find((r) => r === head)
   return new Runtime.BackendError({
-    reason: known ?? (head === "invalid-argument" ? "execution-failed" : "execution-failed"),
+    reason: known ?? "execution-failed", // "invalid-argument" has no class of its own in BackendError
     backend: "cuda",
     operation,
     phase,
