@@ -71,7 +71,6 @@ const tensor = (handle: Runtime.ConcreteTensorHandle): Native.NativeTensor => ha
 
 interface CompiledDecode {
   readonly executable: Native.Executable
-  readonly pool: () => Native.NativeKvPool
 }
 
 export const makeRuntime = (native: Native.NativeAddon): Runtime.RuntimeService => {
@@ -85,7 +84,17 @@ export const makeRuntime = (native: Native.NativeAddon): Runtime.RuntimeService 
     })
   }
   const identity = {}
-  let lastPool: Native.NativeKvPool | undefined
+  // Which pool a sequence was made from: a stateful invocation names sequences only, and all of them must share one pool
+  // (the CPU adapter keeps the same record beside each sequence handle, packages/backend-cpu/src/internal/adapter.ts:661-662).
+  const poolOf = new WeakMap<Native.NativeKvSequence, Native.NativeKvPool>()
+  const sharedPool = (operation: string, sequences: ReadonlyArray<Native.NativeKvSequence>): Native.NativeKvPool => {
+    const first = sequences.length > 0 ? poolOf.get(sequences[0]!) : undefined
+    if (first === undefined) throw new Error(`invalid-handle: ${operation}: the invocation names no sequence of this runtime`)
+    if (sequences.some((entry) => poolOf.get(entry) !== first)) {
+      throw new Error(`execution-failed: ${operation}: the sequences of one invocation must come from one pool`)
+    }
+    return first
+  }
 
   const decode: Runtime.DecodeRuntime = {
     makePool: (options) =>
@@ -93,17 +102,23 @@ export const makeRuntime = (native: Native.NativeAddon): Runtime.RuntimeService 
         if (options.kdaLayers !== 0 || options.convLayers !== 0) {
           throw new Error("unsupported-operation: recurrent state (KDA / short convolution) is not served by the CUDA decode backend")
         }
-        lastPool = new native.NativeKvPool(
-          options.layers,
-          options.kvHeads,
-          options.headDim,
-          options.maxTokens,
-          options.blockSize,
-          options.dtype as Native.NativeDType
+        return brand<Runtime.KvPoolHandle>(
+          new native.NativeKvPool(
+            options.layers,
+            options.kvHeads,
+            options.headDim,
+            options.maxTokens,
+            options.blockSize,
+            options.dtype as Native.NativeDType
+          )
         )
-        return brand<Runtime.KvPoolHandle>(lastPool)
       }),
-    makeSequence: (handle) => attempt("makeSequence", "execute", () => brand<Runtime.KvSequenceHandle>(pool(handle).makeSequence())),
+    makeSequence: (handle) =>
+      attempt("makeSequence", "execute", () => {
+        const made = pool(handle).makeSequence()
+        poolOf.set(made, pool(handle))
+        return brand<Runtime.KvSequenceHandle>(made)
+      }),
     prefillMatch: (handle, tokens) => attempt("prefillMatch", "execute", () => sequence(handle).prefillMatch([...tokens])),
     sequenceCursor: (handle) => attempt("sequenceCursor", "execute", () => sequence(handle).cursor),
     releaseSequence: (handle) => attempt("releaseSequence", "execute", () => sequence(handle).release())
@@ -133,7 +148,7 @@ export const makeRuntime = (native: Native.NativeAddon): Runtime.RuntimeService 
           window: request.state.window,
           batch: request.state.batch
         })
-        const entry: CompiledDecode = { executable, pool: () => lastPool! }
+        const entry: CompiledDecode = { executable }
         return brand<Runtime.ExecutableHandle>(entry)
       }),
     execute: (handle, invocation) =>
@@ -141,7 +156,7 @@ export const makeRuntime = (native: Native.NativeAddon): Runtime.RuntimeService 
         const entry = compiled(handle)
         const sequences = (invocation.sequences ?? []).map(sequence)
         const tokens = (invocation.tokens ?? []).map((chunk) => [...chunk])
-        const logits = await entry.executable.execute(entry.pool(), sequences, tokens)
+        const logits = await entry.executable.execute(sharedPool("execute", sequences), sequences, tokens)
         const bytes = new Uint8Array(logits.buffer, logits.byteOffset, logits.byteLength)
         return [brand<Runtime.ConcreteTensorHandle>(native.NativeTensor.fromBytes(bytes, [sequences.length, logits.length / sequences.length], "f32"))]
       }),
@@ -167,11 +182,12 @@ export const makeRuntime = (native: Native.NativeAddon): Runtime.RuntimeService 
             const entry = compiled(handle)
             const sequences = (invocation.sequences ?? []).map(sequence)
             const tokens = (invocation.tokens ?? []).map((chunk) => [...chunk])
+            const shared = sharedPool("executeDecode", sequences)
             if (options.every((o) => o.temperature === 0)) {
-              return entry.executable.executeSampled(entry.pool(), sequences, tokens)
+              return entry.executable.executeSampled(shared, sequences, tokens)
             }
-            // non-greedy draws: logits stay on the device, one sampling launch per row
-            const logits = await entry.executable.execute(entry.pool(), sequences, tokens)
+            // non-greedy draws: the logits come back once, one sampling launch per row
+            const logits = await entry.executable.execute(shared, sequences, tokens)
             const vocab = logits.length / sequences.length
             return Promise.all(
               options.map((o, row) => {
